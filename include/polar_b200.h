@@ -1,0 +1,193 @@
+/*
+ * polar_b200.h - C ABI of the B200 (sm_100a) builtin kernels for the PolarAI
+ * ("Athena") runtime.
+ *
+ * One entry point per builtin a PolarAI device runtime must provide.  Each is
+ * named after the builtin's native kernel name - the dispatch key a runtime
+ * receives in LaunchCommand::nativeKernelName
+ * (include/polarai/backend/generic/runtime/LaunchCommand.h:26-31 of the
+ * reference; the name table is src/backend/generic/runtime/sycl/SYCLDevice.cpp:57-96)
+ * - and takes the builtin's operands in the order of its LaunchCommand
+ * arguments, as plain device pointers and element counts.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer to dense row-major fp32 unless said
+ *    otherwise; nothing here allocates, copies to the host or synchronises
+ *    unless said otherwise;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *    stream); the launch is asynchronous on it;
+ *  - the return value is a polar_b200_status; no entry point aborts the
+ *    process (the reference's convention is std::terminate on a CUDA error,
+ *    src/backend/generic/runtime/cuda/utils.hpp:20-28);
+ *  - `out` may alias an input element-for-element (the reference updates
+ *    weights in place: src/core/graph/internal/GraphInternal.cpp:464-465);
+ *  - n == 0 (or an empty matrix) is a successful no-op.
+ */
+#ifndef POLAR_B200_H
+#define POLAR_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum polar_b200_status {
+  POLAR_B200_OK = 0,
+  POLAR_B200_ERR_INVALID = 1,     /* null pointer, bad flag, size overflow */
+  POLAR_B200_ERR_CUDA = 2,        /* a CUDA call failed; see polar_b200_last_error */
+  POLAR_B200_ERR_UNSUPPORTED = 3, /* unknown kernel name or argument pattern */
+  POLAR_B200_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up */
+  POLAR_B200_ERR_WORKSPACE = 5    /* caller's workspace is too small */
+} polar_b200_status;
+
+/* Text of the last error recorded by the calling thread ("" if none). */
+const char* polar_b200_last_error(void);
+/* Library version, and the compute capability it was built for (100). */
+int polar_b200_version(void);
+int polar_b200_built_for_sm(void);
+
+/* ---- elementwise builtins ------------------------------------------------ */
+
+/* ffill: out[i] = pattern, bit-exact.  LaunchCommand args: f32 pattern, T out.
+ * Replaces sycl/kernels/Fill.hpp:71-74 and opencl/kernels.h:21-30. */
+int polar_b200_ffill(float pattern, float* out, uint64_t n, void* stream);
+
+/* fcopy: out[i] = in[i], bit-exact.  Args: T in, T out.
+ * Replaces PolarGraph/kernels/CopyOp.cpp:21-23 and opencl/kernels.h:44-53. */
+int polar_b200_fcopy(const float* in, float* out, uint64_t n, void* stream);
+
+/* fadd: out[i] = a[i]*scaleA + b[i]*scaleB, two rounded products then a
+ * rounded sum (no fused multiply-add).  Args: T a, f32 scaleA, T b, f32 scaleB,
+ * T out.  Emitted by AddOperation (1,1) and CombineOperation (alpha,beta).
+ * Replaces PolarGraph/kernels/AddOp.cpp:36-48 and opencl/kernels.h:32-42. */
+int polar_b200_fadd(const float* a, float scaleA, const float* b, float scaleB,
+                    float* out, uint64_t n, void* stream);
+
+/* fmul: out[i] = a[i]*b[i].  Args: T a, T b, T out.
+ * Replaces PolarGraph/kernels/MulOp.cpp:36-43 and opencl/kernels.h:119-128. */
+int polar_b200_fmul(const float* a, const float* b, float* out, uint64_t n,
+                    void* stream);
+
+/* fdivide: out[i] = numerator[i]/denominator[i], IEEE round-to-nearest.
+ * Args: T numerator, T denominator, T out.
+ * Replaces PolarGraph/kernels/DivideOp.cpp:36-43 and opencl/kernels.h:55-64. */
+int polar_b200_fdivide(const float* numerator, const float* denominator,
+                       float* out, uint64_t n, void* stream);
+
+/* fsigmoid: r = 1/(1+exp(-x)); then |r-1| < 1e-5 -> 1-1e-5, else |r| < 1e-5
+ * -> 1e-5.  Args: T in, T out.
+ * Replaces sycl/kernels/Sigmoid.hpp:32-41 and opencl/kernels.h:141-156. */
+int polar_b200_fsigmoid(const float* in, float* out, uint64_t n, void* stream);
+
+/* The MLIR form of the same builtin, which has no clamp
+ * (PolarGraph/kernels/SigmoidOp.cpp:37-51). */
+int polar_b200_fsigmoid_unclamped(const float* in, float* out, uint64_t n,
+                                  void* stream);
+
+/* flogloss: out[i] = -y[i]*log(p[i]+eps) - (1-y[i])*log(1-p[i]+eps), eps=1e-5,
+ * elementwise (the output has the shape of `predicted`).
+ * Args: T predicted, T groundTruth, T out.
+ * Replaces sycl/kernels/LogLoss.hpp:33-37 and opencl/kernels.h:66-78. */
+int polar_b200_flogloss(const float* predicted, const float* groundTruth,
+                        float* out, uint64_t n, void* stream);
+
+/* fmulconcat: out[i] = gradient[0]*localDerivative[i].
+ * Args: T gradient, T localDerivative, T out.
+ * Replaces PolarGraph/kernels/MulConcatOp.cpp:37-46 and opencl/kernels.h:130-139. */
+int polar_b200_fmulconcat(const float* gradient, const float* localDerivative,
+                          float* out, uint64_t n, void* stream);
+
+/* ---- matmul -------------------------------------------------------------- */
+
+/* fmatmul_{f,t}_{f,t}: out[i,j] = sum_k L'[i,k]*R'[k,j] in fp32 accuracy.
+ * `left` is stored [m,k], or [k,m] when transLeft; `right` is stored [k,n], or
+ * [n,k] when transRight; `out` is [m,n] and is overwritten (no alpha/beta).
+ * Args of the builtin: T left, T right, T out; the transposes are part of the
+ * kernel NAME (utils/dialects/include/PolarGraph/PolarGraphOps.td:342-352).
+ * Replaces PolarGraph/kernels/MatMulOp.cpp:36-85 and opencl/kernels.h:80-117.
+ *
+ * `workspace` is device scratch of `workspace_bytes` bytes, 256-byte aligned;
+ * polar_b200_fmatmul_workspace_bytes gives the size this call needs (0 = none).
+ * With workspace == NULL the call takes the scratch it needs from the
+ * device's stream-ordered memory pool (cudaMallocAsync/cudaFreeAsync on
+ * `stream`). */
+int polar_b200_fmatmul(int transLeft, int transRight, uint64_t m, uint64_t n,
+                       uint64_t k, const float* left, const float* right,
+                       float* out, void* workspace, uint64_t workspace_bytes,
+                       void* stream);
+uint64_t polar_b200_fmatmul_workspace_bytes(int transLeft, int transRight,
+                                            uint64_t m, uint64_t n, uint64_t k);
+
+/* The same product on the CUDA cores: one FFMA per term, k ascending per
+ * output within a thread.  Kept only as a device-side cross-check of the
+ * tensor-core path; no dispatch reaches it unless a caller asks for it. */
+int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
+                            uint64_t n, uint64_t k, const float* left,
+                            const float* right, float* out, void* stream);
+
+/* The tensor-core path alone, with its tuning knobs exposed for tests and
+ * benchmarks: tile_n is 128 or 256; passes is 3 (fp32-accurate three-product
+ * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi != 0 makes the
+ * split warps store the masked high parts explicitly instead of relying on the
+ * tensor core ignoring the low 13 mantissa bits.  Fails with
+ * POLAR_B200_ERR_UNSUPPORTED when the operands cannot be described to TMA
+ * (bases not 16-byte aligned, or a contiguous extent that is not a multiple of
+ * 4 floats). */
+int polar_b200_fmatmul_tc(int transLeft, int transRight, uint64_t m, uint64_t n,
+                          uint64_t k, const float* left, const float* right,
+                          float* out, int tile_n, int passes, int write_hi,
+                          void* stream);
+
+/* Status word the kernels write when a bounded device-side wait gives up
+ * (0 = none; 101..105 = which wait of the tensor-core matmul).  It lives in
+ * pinned host memory, so reading it needs no CUDA call; read it after the
+ * stream has been synchronised. */
+int polar_b200_device_status(void);
+void polar_b200_device_status_clear(void);
+
+/* Which matmul path polar_b200_fmatmul would take for these sizes:
+ * 0 = tcgen05 tensor-core tiles, 1 = skinny (bandwidth-bound CUDA-core) path,
+ * 2 = FFMA tiles. */
+int polar_b200_fmatmul_path(int transLeft, int transRight, uint64_t m,
+                            uint64_t n, uint64_t k);
+
+/* ---- extended builtins (beside, never instead of, the ones above) -------- */
+
+/* Sum of n floats into *sum (a device double, ADDED to: clear it first), with
+ * warp-shuffle + one atomic per block.  Used to report the scalar mean of an
+ * elementwise flogloss output; the reference has no reduction builtin. */
+int polar_b200_fsum(const float* in, double* sum, uint64_t n, void* stream);
+
+/* ---- dispatch by native kernel name -------------------------------------- */
+
+typedef struct polar_b200_tensor {
+  float* data;            /* device pointer */
+  uint64_t dims;          /* number of dimensions (TensorInfo::dims) */
+  const uint64_t* shape;  /* host pointer to `dims` extents (TensorInfo::shape) */
+} polar_b200_tensor;
+
+typedef struct polar_b200_arg {
+  int is_tensor;            /* 1: ArgDesc::TENSOR, 0: ArgDesc::DATA (one f32) */
+  polar_b200_tensor tensor; /* when is_tensor */
+  float scalar;             /* when !is_tensor */
+} polar_b200_arg;
+
+/* Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
+ * on arguments in LaunchCommand order; this is what Device::launch forwards to
+ * once it has turned each TensorInfo into a device pointer.  Shapes are
+ * checked against the builtin's rules (equal element counts; matmul inner
+ * dimensions). */
+int polar_b200_launch_by_name(const char* nativeKernelName,
+                              const polar_b200_arg* args, uint64_t argsCount,
+                              void* workspace, uint64_t workspace_bytes,
+                              void* stream);
+
+/* Number of kernels this library has launched since it was loaded (all
+ * threads), for launch accounting in benchmarks. */
+uint64_t polar_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLAR_B200_H */

@@ -1,0 +1,118 @@
+"""Builds the native libraries of this package in-tree with nvcc for sm_100a.
+
+    python polarai-framework_b200/build.py            # everything
+    python polarai-framework_b200/build.py --force    # ignore timestamps
+
+libpolar_b200.so    - the builtin kernels and their C ABI (include/polar_b200.h)
+libpolar_rt_cuda.so - the PolarAI device-runtime plugin (initContext/closeContext)
+                      built against the reference's runtime headers when the
+                      reference tree is present (POLAR_REFERENCE_ROOT, default
+                      /root/reference); otherwise a prebuilt file is kept.
+"""
+import concurrent.futures
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build")
+LIB = os.path.join(HERE, "lib")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++"] + ARCH
+
+KERNEL_SOURCES = ["common.cu", "elementwise.cu", "gemm_ffma.cu", "gemm_tc.cu", "dispatch.cu"]
+
+
+def _newer(src, dst, extra=()):
+    if not os.path.exists(dst):
+        return True
+    t = os.path.getmtime(dst)
+    return any(os.path.getmtime(s) > t for s in (src,) + tuple(extra) if os.path.exists(s))
+
+
+def _run(cmd):
+    out = subprocess.run(cmd, capture_output=True, text=True)
+    if out.returncode != 0:
+        raise RuntimeError("command failed: " + " ".join(cmd) + "\n" + out.stdout + out.stderr)
+    return out.stdout + out.stderr
+
+
+def _headers():
+    hs = [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))]
+    hs += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".hpp", ".h"))]
+    return tuple(hs)
+
+
+def build_kernels(force=False, verbose=False):
+    os.makedirs(OBJ, exist_ok=True)
+    os.makedirs(LIB, exist_ok=True)
+    hdrs = _headers()
+    jobs = []
+    objs = []
+    for src in KERNEL_SOURCES:
+        s = os.path.join(CSRC, src)
+        o = os.path.join(OBJ, src.replace(".cu", ".o"))
+        objs.append(o)
+        if force or _newer(s, o, hdrs):
+            jobs.append([NVCC] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o])
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+        for log in ex.map(_run, jobs):
+            if verbose and log:
+                print(log)
+    lib = os.path.join(LIB, "libpolar_b200.so")
+    if force or jobs or not os.path.exists(lib):
+        _run([NVCC, "-shared", "-o", lib] + objs + ARCH + ["-ccbin", "/usr/bin/g++"])
+    return lib
+
+
+def reference_root():
+    r = os.environ.get("POLAR_REFERENCE_ROOT", "/root/reference")
+    return r if os.path.isdir(os.path.join(r, "include", "polarai")) else None
+
+
+def build_runtime(force=False):
+    """The device-runtime plugin.  Needs the reference's headers to compile."""
+    lib = os.path.join(LIB, "libpolar_rt_cuda.so")
+    rt_dir = os.path.join(CSRC, "rt")
+    if not os.path.isdir(rt_dir):
+        return None
+    ref = reference_root()
+    if ref is None:
+        if os.path.exists(lib):
+            return lib
+        raise RuntimeError("libpolar_rt_cuda.so is not built and the reference headers are absent")
+    srcs = [os.path.join(rt_dir, f) for f in sorted(os.listdir(rt_dir)) if f.endswith((".cpp", ".cu"))]
+    deps = tuple(os.path.join(rt_dir, f) for f in os.listdir(rt_dir)) + _headers()
+    if not (force or any(_newer(s, lib, deps) for s in srcs)):
+        return lib
+    stubs = os.path.join(OBJ, "export_stubs")
+    os.makedirs(stubs, exist_ok=True)
+    # The reference's CMake generates one <target>_export.h per library; an
+    # in-tree build of the plugin only needs the macros to exist.
+    for name in ["polar_core", "polar_utils", "polar_loaders", "polar_operation", "polar_backend_generic",
+                 "polar_rt_support", "polar_io", "polar_rt_cuda", "polar_generic_backend_driver"]:
+        with open(os.path.join(stubs, name + "_export.h"), "w") as fh:
+            macro = name.upper()
+            fh.write(f"#pragma once\n#define {macro}_EXPORT\n#define {macro}_NO_EXPORT\n")
+    cmd = [NVCC] + NVCC_FLAGS + ["-shared", "-o", lib, "-I", os.path.join(ref, "include"),
+                                 "-I", os.path.join(ref, "src", "backend", "generic"),
+                                 "-I", stubs, "-I", os.path.join(ROOT, "include"),
+                                 "-Xcompiler", "-fno-rtti", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN",
+                                 "-L", LIB, "-lpolar_b200"] + srcs
+    _run(cmd)
+    return lib
+
+
+def build_all(force=False, verbose=False):
+    libs = [build_kernels(force, verbose)]
+    rt = build_runtime(force)
+    if rt:
+        libs.append(rt)
+    return libs
+
+
+if __name__ == "__main__":
+    print("\n".join(build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)))

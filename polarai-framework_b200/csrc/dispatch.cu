@@ -1,0 +1,166 @@
+// fmatmul entry points and dispatch by native kernel name.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace polar_b200 {
+int launch_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                const float* right, float* out, cudaStream_t stream);
+int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+              const float* right, float* out, int bn, int passes, int write_hi, cudaStream_t stream);
+bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                 const float* right);
+int tc_status_word();
+void tc_status_clear();
+
+namespace {
+
+enum Path { kPathTc = 0, kPathSkinny = 1, kPathFfma = 2 };
+
+// Tensor-core tiles are 128 x 256 (or 128 x 128): below one tile in either
+// output dimension, or with a k extent shorter than a slab, the CUDA-core
+// kernel does less wasted work.
+int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                const float* right) {
+  if (tc_shape_ok(tl, tr, m, n, k, left, right) && m >= 64 && n >= 32 && k >= 32) return kPathTc;
+  return kPathFfma;
+}
+
+int check_mm(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+             const float* right, float* out) {
+  if ((tl != 0 && tl != 1) || (tr != 0 && tr != 1))
+    return fail(POLAR_B200_ERR_INVALID, "transpose flags must be 0 or 1");
+  if (m > (1ull << 31) || n > (1ull << 31) || k > (1ull << 31))
+    return fail(POLAR_B200_ERR_INVALID, "matrix dimension too large");
+  if (m * n != 0 && !out) return fail(POLAR_B200_ERR_INVALID, "null output pointer");
+  if (m * n != 0 && k != 0 && (!left || !right)) return fail(POLAR_B200_ERR_INVALID, "null operand pointer");
+  return POLAR_B200_OK;
+}
+
+}  // namespace
+}  // namespace polar_b200
+
+using namespace polar_b200;
+
+extern "C" {
+
+uint64_t polar_b200_fmatmul_workspace_bytes(int, int, uint64_t, uint64_t, uint64_t) { return 0; }
+
+int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
+  // Alignment of the operands is assumed (allocator buffers are 256-byte aligned).
+  return choose_path(tl, tr, m, n, k, reinterpret_cast<const float*>(256), reinterpret_cast<const float*>(256));
+}
+
+int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                       const float* right, float* out, void* workspace, uint64_t workspace_bytes,
+                       void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  clear_error();
+  int rc = check_mm(tl, tr, m, n, k, left, right, out);
+  if (rc) return rc;
+  if (m == 0 || n == 0) return POLAR_B200_OK;
+  if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);  // empty sum
+  switch (choose_path(tl, tr, m, n, k, left, right)) {
+    case kPathTc:
+      return launch_tc(tl, tr, m, n, k, left, right, out, 256, 3, 0, as_stream(stream));
+    default:
+      return launch_ffma(tl, tr, m, n, k, left, right, out, as_stream(stream));
+  }
+}
+
+int polar_b200_fmatmul_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                            const float* right, float* out, void* stream) {
+  clear_error();
+  int rc = check_mm(tl, tr, m, n, k, left, right, out);
+  if (rc) return rc;
+  if (m == 0 || n == 0) return POLAR_B200_OK;
+  if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);
+  return launch_ffma(tl, tr, m, n, k, left, right, out, as_stream(stream));
+}
+
+int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                          const float* right, float* out, int tile_n, int passes, int write_hi,
+                          void* stream) {
+  clear_error();
+  int rc = check_mm(tl, tr, m, n, k, left, right, out);
+  if (rc) return rc;
+  if (m == 0 || n == 0 || k == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "empty matrix");
+  if (tile_n != 128 && tile_n != 256) return fail(POLAR_B200_ERR_INVALID, "tile_n must be 128 or 256");
+  if (passes != 1 && passes != 3) return fail(POLAR_B200_ERR_INVALID, "passes must be 1 or 3");
+  if (!tc_shape_ok(tl, tr, m, n, k, left, right))
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
+  return launch_tc(tl, tr, m, n, k, left, right, out, tile_n, passes, write_hi, as_stream(stream));
+}
+
+int polar_b200_device_status(void) { return tc_status_word(); }
+void polar_b200_device_status_clear(void) { tc_status_clear(); }
+
+static uint64_t numel(const polar_b200_tensor& t) {
+  uint64_t n = 1;
+  for (uint64_t d = 0; d < t.dims; ++d) n *= t.shape[d];
+  return n;
+}
+
+int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_t argc,
+                              void* workspace, uint64_t workspace_bytes, void* stream) {
+  clear_error();
+  if (!name || (!a && argc)) return fail(POLAR_B200_ERR_INVALID, "null kernel name or argument list");
+  auto pattern = [&](const char* pat) {  // 'T' tensor, 'f' scalar
+    if (std::strlen(pat) != argc) return false;
+    for (uint64_t i = 0; i < argc; ++i) {
+      if ((pat[i] == 'T') != (a[i].is_tensor != 0)) return false;
+      if (a[i].is_tensor && a[i].tensor.dims && !a[i].tensor.shape) return false;
+    }
+    return true;
+  };
+  auto same = [&](uint64_t i, uint64_t j) { return numel(a[i].tensor) == numel(a[j].tensor); };
+  const int bad_args = POLAR_B200_ERR_UNSUPPORTED;
+  if (!std::strcmp(name, "ffill")) {
+    if (!pattern("fT")) return fail(bad_args, "ffill expects (f32 pattern, T out)");
+    return polar_b200_ffill(a[0].scalar, a[1].tensor.data, numel(a[1].tensor), stream);
+  }
+  if (!std::strcmp(name, "fcopy")) {
+    if (!pattern("TT") || !same(0, 1)) return fail(bad_args, "fcopy expects (T in, T out) of equal size");
+    return polar_b200_fcopy(a[0].tensor.data, a[1].tensor.data, numel(a[1].tensor), stream);
+  }
+  if (!std::strcmp(name, "fadd")) {
+    if (!pattern("TfTfT") || !same(0, 4) || !same(2, 4))
+      return fail(bad_args, "fadd expects (T a, f32 scaleA, T b, f32 scaleB, T out) of equal size");
+    return polar_b200_fadd(a[0].tensor.data, a[1].scalar, a[2].tensor.data, a[3].scalar,
+                           a[4].tensor.data, numel(a[4].tensor), stream);
+  }
+  if (!std::strcmp(name, "fmul") || !std::strcmp(name, "fdivide") || !std::strcmp(name, "flogloss")) {
+    if (!pattern("TTT") || !same(0, 2) || !same(1, 2))
+      return fail(bad_args, "binary builtin expects (T, T, T out) of equal size");
+    uint64_t n = numel(a[2].tensor);
+    if (name[1] == 'm') return polar_b200_fmul(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data, n, stream);
+    if (name[1] == 'd') return polar_b200_fdivide(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data, n, stream);
+    return polar_b200_flogloss(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data, n, stream);
+  }
+  if (!std::strcmp(name, "fsigmoid")) {
+    if (!pattern("TT") || !same(0, 1)) return fail(bad_args, "fsigmoid expects (T in, T out) of equal size");
+    return polar_b200_fsigmoid(a[0].tensor.data, a[1].tensor.data, numel(a[1].tensor), stream);
+  }
+  if (!std::strcmp(name, "fmulconcat")) {
+    if (!pattern("TTT") || !same(1, 2) || numel(a[0].tensor) < 1)
+      return fail(bad_args, "fmulconcat expects (T gradient, T localDerivative, T out)");
+    return polar_b200_fmulconcat(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data,
+                                 numel(a[2].tensor), stream);
+  }
+  if (!std::strncmp(name, "fmatmul_", 8) && std::strlen(name) == 11 && name[9] == '_' &&
+      (name[8] == 'f' || name[8] == 't') && (name[10] == 'f' || name[10] == 't')) {
+    if (!pattern("TTT")) return fail(bad_args, "fmatmul expects (T left, T right, T out)");
+    const polar_b200_tensor &l = a[0].tensor, &r = a[1].tensor, &o = a[2].tensor;
+    if (l.dims != 2 || r.dims != 2 || o.dims != 2) return fail(bad_args, "fmatmul operands must be 2-D");
+    int tl = name[8] == 't', tr = name[10] == 't';
+    // m = tl ? left.shape[1] : left.shape[0]; n = tr ? right.shape[0] : right.shape[1]
+    // (src/operation/internal/MatMulOperationInternal.cpp:39-40 of the reference)
+    uint64_t m = tl ? l.shape[1] : l.shape[0], k = tl ? l.shape[0] : l.shape[1];
+    uint64_t n = tr ? r.shape[0] : r.shape[1], k2 = tr ? r.shape[1] : r.shape[0];
+    if (k != k2 || o.shape[0] != m || o.shape[1] != n) return fail(bad_args, "fmatmul shapes do not agree");
+    return polar_b200_fmatmul(tl, tr, m, n, k, l.data, r.data, o.data, workspace, workspace_bytes, stream);
+  }
+  return fail(POLAR_B200_ERR_UNSUPPORTED, "unknown native kernel name");
+}
+
+}  // extern "C"

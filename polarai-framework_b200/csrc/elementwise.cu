@@ -1,0 +1,281 @@
+// Elementwise builtins for B200: ffill, fcopy, fadd, fmul, fdivide, fsigmoid,
+// flogloss, fmulconcat, and the fsum reduction.
+//
+// All of them are HBM-bound streams (4 to 12 bytes per element, a few to a few
+// tens of instructions).  One kernel template serves them: every thread moves
+// 128-bit vectors, UNROLL independent vectors per input are in flight per
+// thread before the first use, the grid is a multiple of the SM count and walks
+// the array with a grid-stride loop, loads and stores carry the streaming
+// (evict-first) cache hint because no element is touched twice.  Pointers that
+// are not 16-byte aligned take a scalar kernel of the same shape.
+//
+// Arithmetic follows the reference bit for bit where IEEE allows it: fadd is
+// two rounded multiplies and a rounded add (__fmul_rn/__fadd_rn forbid
+// contraction into FMA), fdivide is IEEE division, fsigmoid and flogloss use
+// the full-precision expf/logf (1 ulp), not the fast intrinsics.
+#include "common.cuh"
+
+namespace polar_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCtasPerSm = 4;   // 1024 threads/SM: 64 registers per thread available
+constexpr int kUnroll = 4;      // float4 vectors in flight per input per thread
+
+struct FillOp {
+  float v;
+  __device__ __forceinline__ float operator()(float, float) const { return v; }
+};
+struct CopyOp {
+  __device__ __forceinline__ float operator()(float a, float) const { return a; }
+};
+struct AddOp {
+  float sa, sb;
+  __device__ __forceinline__ float operator()(float a, float b) const {
+    return __fadd_rn(__fmul_rn(a, sa), __fmul_rn(b, sb));
+  }
+};
+struct MulOp {
+  __device__ __forceinline__ float operator()(float a, float b) const { return __fmul_rn(a, b); }
+};
+struct DivOp {
+  __device__ __forceinline__ float operator()(float a, float b) const { return __fdiv_rn(a, b); }
+};
+template <bool CLAMP>
+struct SigmoidOp {
+  __device__ __forceinline__ float operator()(float x, float) const {
+    const float eps = 1e-5f;
+    float r = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
+    if (CLAMP) {
+      if (fabsf(__fadd_rn(r, -1.0f)) < eps) {
+        r = __fadd_rn(1.0f, -eps);
+      } else if (fabsf(r) < eps) {
+        r = eps;
+      }
+    }
+    return r;
+  }
+};
+struct LogLossOp {
+  __device__ __forceinline__ float operator()(float p, float y) const {
+    const float eps = 1e-5f;
+    float t0 = __fmul_rn(-y, logf(__fadd_rn(p, eps)));
+    float t1 = __fmul_rn(__fadd_rn(1.0f, -y), logf(__fadd_rn(__fadd_rn(1.0f, -p), eps)));
+    return __fadd_rn(t0, -t1);
+  }
+};
+struct ScaleByFirstOp {  // fmulconcat: the scalar is read once per thread
+  float g;
+  __device__ __forceinline__ float operator()(float l, float) const { return __fmul_rn(g, l); }
+};
+
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+
+// NIN = number of input streams (0, 1 or 2).
+template <int NIN, class Op>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+ew_vec_kernel(Op op, const float* in0, const float* in1, float* out, uint64_t n) {
+  const uint64_t nvec = n >> 2;
+  const float4* v0 = reinterpret_cast<const float4*>(in0);
+  const float4* v1 = reinterpret_cast<const float4*>(in1);
+  float4* vo = reinterpret_cast<float4*>(out);
+  const uint64_t tile = (uint64_t)kThreads * kUnroll;
+  const uint64_t stride = (uint64_t)gridDim.x * tile;
+  for (uint64_t base = (uint64_t)blockIdx.x * tile; base < nvec; base += stride) {
+    float4 a[kUnroll], b[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      uint64_t i = base + (uint64_t)u * kThreads + threadIdx.x;
+      if (NIN >= 1 && i < nvec) a[u] = ld_stream(v0 + i);
+      if (NIN >= 2 && i < nvec) b[u] = ld_stream(v1 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      uint64_t i = base + (uint64_t)u * kThreads + threadIdx.x;
+      if (i < nvec) {
+        float4 r;
+        r.x = op(NIN >= 1 ? a[u].x : 0.f, NIN >= 2 ? b[u].x : 0.f);
+        r.y = op(NIN >= 1 ? a[u].y : 0.f, NIN >= 2 ? b[u].y : 0.f);
+        r.z = op(NIN >= 1 ? a[u].z : 0.f, NIN >= 2 ? b[u].z : 0.f);
+        r.w = op(NIN >= 1 ? a[u].w : 0.f, NIN >= 2 ? b[u].w : 0.f);
+        st_stream(vo + i, r);
+      }
+    }
+  }
+  // ragged tail: the last n % 4 elements
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    uint64_t i = (nvec << 2) + threadIdx.x;
+    out[i] = op(NIN >= 1 ? in0[i] : 0.f, NIN >= 2 ? in1[i] : 0.f);
+  }
+}
+
+template <int NIN, class Op>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+ew_scalar_kernel(Op op, const float* in0, const float* in1, float* out, uint64_t n) {
+  const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+  for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+    out[i] = op(NIN >= 1 ? in0[i] : 0.f, NIN >= 2 ? in1[i] : 0.f);
+  }
+}
+
+// fmulconcat reads its scalar from device memory inside the kernel.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+mulconcat_vec_kernel(const float* gradient, const float* local, float* out, uint64_t n) {
+  const float g = gradient[0];
+  ScaleByFirstOp op{g};
+  const uint64_t nvec = n >> 2;
+  const float4* v0 = reinterpret_cast<const float4*>(local);
+  float4* vo = reinterpret_cast<float4*>(out);
+  const uint64_t tile = (uint64_t)kThreads * kUnroll;
+  const uint64_t stride = (uint64_t)gridDim.x * tile;
+  for (uint64_t base = (uint64_t)blockIdx.x * tile; base < nvec; base += stride) {
+    float4 a[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      uint64_t i = base + (uint64_t)u * kThreads + threadIdx.x;
+      if (i < nvec) a[u] = ld_stream(v0 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      uint64_t i = base + (uint64_t)u * kThreads + threadIdx.x;
+      if (i < nvec) {
+        float4 r = {op(a[u].x, 0.f), op(a[u].y, 0.f), op(a[u].z, 0.f), op(a[u].w, 0.f)};
+        st_stream(vo + i, r);
+      }
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    uint64_t i = (nvec << 2) + threadIdx.x;
+    out[i] = op(local[i], 0.f);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+mulconcat_scalar_kernel(const float* gradient, const float* local, float* out, uint64_t n) {
+  const float g = gradient[0];
+  const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+  for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+    out[i] = __fmul_rn(g, local[i]);
+}
+
+// fsum: per-thread double partials, warp shuffle, one atomicAdd(double) per block.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+sum_kernel(const float* in, double* sum, uint64_t n, int vec_ok) {
+  double acc = 0.0;
+  if (vec_ok) {
+    const uint64_t nvec = n >> 2;
+    const float4* v = reinterpret_cast<const float4*>(in);
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += stride) {
+      float4 x = ld_stream(v + i);
+      acc += (double)((x.x + x.y) + (x.z + x.w));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) acc += (double)in[(nvec << 2) + threadIdx.x];
+  } else {
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+      acc += (double)in[i];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  __shared__ double warp_sums[kThreads / 32];
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    double w = threadIdx.x < kThreads / 32 ? warp_sums[threadIdx.x] : 0.0;
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) w += __shfl_xor_sync(0xffffffffu, w, off);
+    if (threadIdx.x == 0) atomicAdd(sum, w);
+  }
+}
+
+unsigned grid_for(uint64_t work_items, uint64_t per_cta) {
+  uint64_t need = (work_items + per_cta - 1) / per_cta;
+  uint64_t cap = (uint64_t)sm_count() * kCtasPerSm;
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
+template <int NIN, class Op>
+int launch_ew(const char* name, Op op, const float* in0, const float* in1, float* out,
+              uint64_t n, void* stream) {
+  clear_error();
+  if (n == 0) return POLAR_B200_OK;
+  if (!out || (NIN >= 1 && !in0) || (NIN >= 2 && !in1))
+    return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  if (n > (1ull << 40)) return fail(POLAR_B200_ERR_INVALID, "element count too large");
+  bool vec = aligned16(out) && (NIN < 1 || aligned16(in0)) && (NIN < 2 || aligned16(in1)) && n >= 4;
+  if (vec) {
+    unsigned grid = grid_for(n >> 2, (uint64_t)kThreads * kUnroll);
+    ew_vec_kernel<NIN, Op><<<grid, kThreads, 0, as_stream(stream)>>>(op, in0, in1, out, n);
+  } else {
+    unsigned grid = grid_for(n, kThreads);
+    ew_scalar_kernel<NIN, Op><<<grid, kThreads, 0, as_stream(stream)>>>(op, in0, in1, out, n);
+  }
+  return check_launch(name);
+}
+
+}  // namespace
+}  // namespace polar_b200
+
+using namespace polar_b200;
+
+extern "C" {
+
+int polar_b200_ffill(float pattern, float* out, uint64_t n, void* stream) {
+  return launch_ew<0>("ffill", FillOp{pattern}, nullptr, nullptr, out, n, stream);
+}
+int polar_b200_fcopy(const float* in, float* out, uint64_t n, void* stream) {
+  return launch_ew<1>("fcopy", CopyOp{}, in, nullptr, out, n, stream);
+}
+int polar_b200_fadd(const float* a, float scaleA, const float* b, float scaleB, float* out,
+                    uint64_t n, void* stream) {
+  return launch_ew<2>("fadd", AddOp{scaleA, scaleB}, a, b, out, n, stream);
+}
+int polar_b200_fmul(const float* a, const float* b, float* out, uint64_t n, void* stream) {
+  return launch_ew<2>("fmul", MulOp{}, a, b, out, n, stream);
+}
+int polar_b200_fdivide(const float* numerator, const float* denominator, float* out, uint64_t n,
+                       void* stream) {
+  return launch_ew<2>("fdivide", DivOp{}, numerator, denominator, out, n, stream);
+}
+int polar_b200_fsigmoid(const float* in, float* out, uint64_t n, void* stream) {
+  return launch_ew<1>("fsigmoid", SigmoidOp<true>{}, in, nullptr, out, n, stream);
+}
+int polar_b200_fsigmoid_unclamped(const float* in, float* out, uint64_t n, void* stream) {
+  return launch_ew<1>("fsigmoid_unclamped", SigmoidOp<false>{}, in, nullptr, out, n, stream);
+}
+int polar_b200_flogloss(const float* predicted, const float* groundTruth, float* out, uint64_t n,
+                        void* stream) {
+  return launch_ew<2>("flogloss", LogLossOp{}, predicted, groundTruth, out, n, stream);
+}
+
+int polar_b200_fmulconcat(const float* gradient, const float* localDerivative, float* out,
+                          uint64_t n, void* stream) {
+  clear_error();
+  if (n == 0) return POLAR_B200_OK;
+  if (!gradient || !localDerivative || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  if (n > (1ull << 40)) return fail(POLAR_B200_ERR_INVALID, "element count too large");
+  if (aligned16(localDerivative) && aligned16(out) && n >= 4) {
+    unsigned grid = grid_for(n >> 2, (uint64_t)kThreads * kUnroll);
+    mulconcat_vec_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(gradient, localDerivative, out, n);
+  } else {
+    unsigned grid = grid_for(n, kThreads);
+    mulconcat_scalar_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(gradient, localDerivative, out, n);
+  }
+  return check_launch("fmulconcat");
+}
+
+int polar_b200_fsum(const float* in, double* sum, uint64_t n, void* stream) {
+  clear_error();
+  if (!sum) return fail(POLAR_B200_ERR_INVALID, "null sum pointer");
+  if (n == 0) return POLAR_B200_OK;
+  if (!in) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  int vec_ok = aligned16(in) && n >= 4;
+  unsigned grid = grid_for(vec_ok ? (n >> 2) : n, (uint64_t)kThreads * 8);
+  sum_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(in, sum, n, vec_ok);
+  return check_launch("fsum");
+}
+
+}  // extern "C"

@@ -1,0 +1,492 @@
+// fmatmul on the 5th-generation tensor cores of B200 (sm_100a): TMA-staged,
+// tcgen05.mma with the accumulator in tensor memory, fp32 accuracy through a
+// three-product TF32 split.
+//
+//   C[128 x BN tile] = sum over k slabs of 32:  Ahi*Bhi + Ahi*Blo + Alo*Bhi
+//
+// where x_hi is the TF32 the tensor core sees when it reads an fp32 word (the
+// top 19 bits) and x_lo = x - x_hi, exact in fp32.  The dropped Alo*Blo term and
+// the truncation of x_lo to TF32 are each below 2^-21 relative to |a||b|.
+//
+// One CTA computes one 128 x BN output tile.  Warp roles:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of the fp32 A and B
+//              slabs into 128-byte-swizzled shared memory (no cluster multicast:
+//              every CTA fetches its own tiles from this GPU's memory / L2);
+//   warp 1     allocates tensor memory, issues tcgen05.mma (one elected lane),
+//              commits to mbarriers to free stages and to publish the tile;
+//   warps 2-9  split warps: read each landed slab, write the lo part
+//              (and, when kWriteHi, the masked hi part in place) for the async
+//              proxy, then act as the epilogue: tcgen05.ld the accumulator and
+//              store C rows with bounds checks.
+//
+// All four transpose forms run natively: a K-contiguous operand is a K-major
+// SWIZZLE_128B tile (rows of 32 floats), an M- or N-contiguous one is an
+// MN-major SWIZZLE_128B tile built from 32x32 boxes; only the shared-memory
+// descriptors, the instruction descriptor's major bits and the TMA boxes differ.
+//
+// Every wait on an mbarrier is bounded: after about two seconds of polling the
+// waiter records a code in the status word, raises the CTA's abort flag, and
+// every role leaves its loop; the CTA then lets copies in flight land, frees its
+// tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace polar_b200 {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                    // floats per slab row: 128 bytes
+constexpr int kSplitWarps = 8;
+constexpr int kThreads = 32 * (2 + kSplitWarps);
+constexpr uint32_t kABytes = BM * BK * 4;  // 16 KB
+
+template <int BN> struct Cfg {
+  static constexpr uint32_t kBBytes = BN * BK * 4;
+  static constexpr uint32_t kRawBytes = kABytes + kBBytes;
+  static constexpr uint32_t kStageBytes = 2 * kRawBytes;   // raw (hi) + lo
+  static constexpr int kStages = (BN == 256) ? 2 : 3;
+  static constexpr uint32_t kTileBytes = kStages * kStageBytes;
+  // tile buffers + 1 KB alignment slack + barriers/flags
+  static constexpr uint32_t kSmemBytes = kTileBytes + 1024 + 256;
+  static constexpr uint32_t kTmemCols = BN;  // fp32 accumulator: one column per n
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds
+
+// Bounded wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - start > kWaitLimitCycles) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread t gets row (lane base + t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (64 bit): start address, leading and stride
+// byte offsets in 16-byte units, version 1 (bits 46-47), SWIZZLE_128B (value 2 in
+// bits 61-63).  Tile buffers are 1024-byte aligned, so the base offset is 0.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32: fp32 accumulate (bits 4-5 = 1), A and B
+// formats TF32 (2 at bits 7-9 and 10-12), major bits 15/16 (1 = MN-major), N/8 at
+// bits 17-22, M/16 at bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) |
+         ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct Params {
+  uint64_t m, n, k;
+  float* out;
+  int a_mn_major;   // left operand stored [k,m]
+  int b_mn_major;   // right operand stored [k,n]
+  int passes;       // 3 = fp32-accurate split, 1 = plain TF32 (diagnostic)
+  int write_hi;     // split warps also store the masked hi part in place
+  int* status;      // device-visible status word
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  // barrier block after the tiles
+  const uint32_t bar_base = smem_base + C::kTileBytes;
+  auto full_raw = [&](int s) { return bar_base + 8u * s; };
+  auto full_lo = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+  auto empty = [&](int s) { return bar_base + 8u * (2 * C::kStages + s); };
+  const uint32_t accum_full = bar_base + 8u * (3 * C::kStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + C::kTileBytes + 8 * (3 * C::kStages + 1));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
+  const int m0 = (int)(blockIdx.y * BM);
+  const int n0 = (int)(blockIdx.x * BN);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_raw(s), 1);
+      mbar_init(full_lo(s), kSplitWarps * 32);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(accum_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % C::kStages;
+        const uint32_t ph = (kb / C::kStages) & 1u;
+        if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101)) break;
+        const uint32_t stage = smem_base + s * C::kStageBytes;
+        mbar_expect_tx(full_raw(s), C::kRawBytes);
+        const int k0 = (int)(kb * BK);
+        if (!p.a_mn_major) {
+          tma_load_2d(stage, &map_a, full_raw(s), k0, m0);          // box {32 k, 128 m}
+        } else {
+          for (int c = 0; c < BM / 32; ++c)                          // boxes {32 m, 32 k}
+            tma_load_2d(stage + c * 4096u, &map_a, full_raw(s), m0 + 32 * c, k0);
+        }
+        const uint32_t bdst = stage + kABytes;
+        if (!p.b_mn_major) {
+          tma_load_2d(bdst, &map_b, full_raw(s), k0, n0);            // box {32 k, BN n}
+        } else {
+          for (int c = 0; c < BN / 32; ++c)                          // boxes {32 n, 32 k}
+            tma_load_2d(bdst + c * 4096u, &map_b, full_raw(s), n0 + 32 * c, k0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN, p.a_mn_major, p.b_mn_major);
+      // K-major: 8-row groups 1024 B apart (SBO); k step of 8 floats = +32 B.
+      // MN-major: 32-element chunks 4096 B apart (LBO), 8-k groups 1024 B apart
+      // (SBO); k step of 8 = +1024 B.
+      const uint32_t a_lbo = p.a_mn_major ? 4096u : 16u, a_step = p.a_mn_major ? 1024u : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? 4096u : 16u, b_step = p.b_mn_major ? 1024u : 32u;
+      bool ok = true;
+      for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % C::kStages;
+        const uint32_t ph = (kb / C::kStages) & 1u;
+        ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102);
+        if (ok && p.passes == 3) ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_hi = smem_base + s * C::kStageBytes;
+        const uint32_t b_hi = a_hi + kABytes;
+        const uint32_t a_lo = a_hi + C::kRawBytes;
+        const uint32_t b_lo = b_hi + C::kRawBytes;
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, 1024u);
+          const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, 1024u);
+          const uint32_t first = (kb | (uint32_t)kk) ? 1u : 0u;
+          if (p.passes == 3) {
+            const uint64_t da_lo = make_desc(a_lo + kk * a_step, a_lbo, 1024u);
+            const uint64_t db_lo = make_desc(b_lo + kk * b_step, b_lbo, 1024u);
+            tc_mma_tf32(tmem_acc, da_lo, db_hi, idesc, first);
+            tc_mma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
+            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
+          } else {
+            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, first);
+          }
+        }
+        tc_commit(empty(s));   // frees the stage once these MMAs have read it
+      }
+      if (ok) tc_commit(accum_full);
+    }
+  } else {
+    // ---------------- split warps, then epilogue ----------------
+    const int t = threadIdx.x - 64;  // 0..255
+    if (p.passes == 3) {
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % C::kStages;
+        const uint32_t ph = (kb / C::kStages) & 1u;
+        if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) break;
+        float4* raw = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes);
+        float4* lo = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes + C::kRawBytes);
+        constexpr int kVecs = C::kRawBytes / 16;
+#pragma unroll 4
+        for (int i = t; i < kVecs; i += kSplitWarps * 32) {
+          float4 v = raw[i];
+          float4 h;
+          h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+          h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+          h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+          h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+          float4 l = {v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w};
+          lo[i] = l;
+          if (p.write_hi) raw[i] = h;
+        }
+        fence_async_smem();
+        mbar_arrive(full_lo(s));
+      }
+    }
+    // Epilogue: warp w may touch tensor-memory lanes [32*(w%4), 32*(w%4)+32).
+    if (num_kb > 0 && mbar_wait(accum_full, 0u, abort_flag, p.status, 105)) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int half = (warp - 2) >> 2;                   // two warps share a lane quarter
+      const uint64_t row = (uint64_t)m0 + q * 32 + lane;
+      const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+        if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
+        tmem_ld_wait();
+        if (row < p.m) {
+          float* dst = p.out + row * p.n + n0 + c;
+          if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                          __uint_as_float(r[j + 3])};
+              *reinterpret_cast<float4*>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if ((uint64_t)n0 + c + j < p.n) dst[j] = __uint_as_float(r[j]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // let copies and MMAs in flight finish before the tensor memory goes away
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, C::kTmemCols);
+  }
+}
+
+// ---- host side --------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows.
+static int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer,
+                    uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * 4};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  return POLAR_B200_OK;
+}
+
+// Status word: pinned host memory mapped into the device, one per process.
+static int* g_status_host = nullptr;
+static int* g_status_dev = nullptr;
+static int ensure_status() {
+  static std::once_flag once;
+  static cudaError_t err = cudaSuccess;
+  std::call_once(once, [] {
+    err = cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), 64, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (err == cudaSuccess) {
+      g_status_host[0] = 0;
+      err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0);
+    }
+  });
+  if (err != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "status word allocation", err);
+  return POLAR_B200_OK;
+}
+
+bool shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+              const float* right) {
+  // TMA: 16-byte aligned base, row pitch a multiple of 16 bytes.
+  if (!aligned16(left) || !aligned16(right)) return false;
+  uint64_t a_inner = tl ? m : k, b_inner = tr ? k : n;
+  if ((a_inner & 3) || (b_inner & 3)) return false;
+  if (m >= (1ull << 31) || n >= (1ull << 31) || k >= (1ull << 31)) return false;
+  return m > 0 && n > 0 && k > 0;
+}
+
+template <int BN>
+static int launch_bn(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                     const float* right, float* out, int passes, int write_hi, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  // (per process; every device runs the same binary)
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_done[64] = {false};
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    attr_err = cudaFuncSetAttribute(fmatmul_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)C::kSmemBytes);
+    if (attr_err != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(smem)", attr_err);
+    attr_done[dev] = true;
+  }
+  (void)attr_once;
+  int rc = ensure_status();
+  if (rc) return rc;
+  CUtensorMap map_a, map_b;
+  // left: stored [m,k] (K-major: inner k, box {32, 128}) or [k,m] (MN-major: inner m, box {32, 32})
+  rc = tl ? make_map(&map_a, left, m, k, 32, 32) : make_map(&map_a, left, k, m, 32, BM);
+  if (rc) return rc;
+  // right: stored [n,k] when transposed (K-major: inner k, box {32, BN}) or [k,n] (MN-major)
+  rc = tr ? make_map(&map_b, right, k, n, 32, BN) : make_map(&map_b, right, n, k, 32, 32);
+  if (rc) return rc;
+  Params p;
+  p.m = m; p.n = n; p.k = k; p.out = out;
+  p.a_mn_major = tl ? 1 : 0;
+  p.b_mn_major = tr ? 0 : 1;
+  p.passes = passes; p.write_hi = write_hi; p.status = g_status_dev;
+  uint64_t gx = (n + BN - 1) / BN, gy = (m + BM - 1) / BM;
+  if (gy > 65535 || gx > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  fmatmul_tc_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+  return check_launch("fmatmul_tc");
+}
+
+}  // namespace tc
+
+int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+              const float* right, float* out, int bn, int passes, int write_hi, cudaStream_t stream) {
+  if (bn == 128) return tc::launch_bn<128>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+  return tc::launch_bn<256>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+}
+
+bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                 const float* right) {
+  return tc::shape_ok(tl, tr, m, n, k, left, right);
+}
+
+int tc_status_word() { return tc::g_status_host ? *(volatile int*)tc::g_status_host : 0; }
+void tc_status_clear() { if (tc::g_status_host) *(volatile int*)tc::g_status_host = 0; }
+
+}  // namespace polar_b200
