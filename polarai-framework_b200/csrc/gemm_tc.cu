@@ -21,7 +21,8 @@
 //
 // All four transpose forms run natively: a K-contiguous operand is a K-major
 // SWIZZLE_128B tile (rows of 32 floats), an M- or N-contiguous one is an
-// MN-major SWIZZLE_128B tile built from 32x32 boxes; only the shared-memory
+// MN-major tile built from 32x32 boxes in the 128-byte swizzle with 32-byte base
+// (the only MN-major layout tcgen05 takes for 32-bit operands); only the shared-memory
 // descriptors, the instruction descriptor's major bits and the TMA boxes differ.
 //
 // Every wait on an mbarrier is bounded: after about two seconds of polling the
@@ -162,15 +163,18 @@ __device__ __forceinline__ void fence_async_smem() {
 }
 
 // Shared-memory matrix descriptor (64 bit): start address, leading and stride
-// byte offsets in 16-byte units, version 1 (bits 46-47), SWIZZLE_128B (value 2 in
-// bits 61-63).  Tile buffers are 1024-byte aligned, so the base offset is 0.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// byte offsets in 16-byte units, version 1 (bits 46-47), swizzle layout in bits
+// 61-63: 2 = SWIZZLE_128B (16-byte chunks, K-major tiles), 1 = 128-byte swizzle
+// with a 32-byte base, the only layout the tensor core accepts for MN-major
+// 32-bit operands.  Tile buffers are 1024-byte aligned, so the base offset is 0.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                             uint32_t layout_type) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout_type << 61;
   return d;
 }
 
@@ -263,11 +267,15 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, BN, p.a_mn_major, p.b_mn_major);
-      // K-major: 8-row groups 1024 B apart (SBO); k step of 8 floats = +32 B.
-      // MN-major: 32-element chunks 4096 B apart (LBO), 8-k groups 1024 B apart
-      // (SBO); k step of 8 = +1024 B.
+      // K-major (SWIZZLE_128B): 8-row groups 1024 B apart (SBO); a k step of 8
+      // floats is +32 B inside the swizzle span.
+      // MN-major (128B swizzle, 32B base): rows of 32 m/n-contiguous floats, one
+      // row per k; 4-row swizzle atoms 512 B apart along k (SBO); 32-element
+      // chunks of m/n 4096 B apart (LBO, one TMA box each); a k step of 8 = +1024 B.
       const uint32_t a_lbo = p.a_mn_major ? 4096u : 16u, a_step = p.a_mn_major ? 1024u : 32u;
       const uint32_t b_lbo = p.b_mn_major ? 4096u : 16u, b_step = p.b_mn_major ? 1024u : 32u;
+      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u, a_lt = p.a_mn_major ? 1u : 2u;
+      const uint32_t b_sbo = p.b_mn_major ? 512u : 1024u, b_lt = p.b_mn_major ? 1u : 2u;
       bool ok = true;
       for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % C::kStages;
@@ -282,12 +290,12 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t b_lo = b_hi + C::kRawBytes;
 #pragma unroll
         for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, 1024u);
-          const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, 1024u);
+          const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
+          const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
           const uint32_t first = (kb | (uint32_t)kk) ? 1u : 0u;
           if (p.passes == 3) {
-            const uint64_t da_lo = make_desc(a_lo + kk * a_step, a_lbo, 1024u);
-            const uint64_t db_lo = make_desc(b_lo + kk * b_step, b_lbo, 1024u);
+            const uint64_t da_lo = make_desc(a_lo + kk * a_step, a_lbo, a_sbo, a_lt);
+            const uint64_t db_lo = make_desc(b_lo + kk * b_step, b_lbo, b_sbo, b_lt);
             tc_mma_tf32(tmem_acc, da_lo, db_hi, idesc, first);
             tc_mma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
             tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
@@ -394,7 +402,7 @@ static EncodeTiledFn get_encode() {
 
 // 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows.
 static int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer,
-                    uint32_t box_inner, uint32_t box_outer) {
+                    uint32_t box_inner, uint32_t box_outer, bool mn_major) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {inner, outer};
@@ -402,7 +410,8 @@ static int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   return POLAR_B200_OK;
@@ -456,10 +465,10 @@ static int launch_bn(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const f
   if (rc) return rc;
   CUtensorMap map_a, map_b;
   // left: stored [m,k] (K-major: inner k, box {32, 128}) or [k,m] (MN-major: inner m, box {32, 32})
-  rc = tl ? make_map(&map_a, left, m, k, 32, 32) : make_map(&map_a, left, k, m, 32, BM);
+  rc = tl ? make_map(&map_a, left, m, k, 32, 32, true) : make_map(&map_a, left, k, m, 32, BM, false);
   if (rc) return rc;
   // right: stored [n,k] when transposed (K-major: inner k, box {32, BN}) or [k,n] (MN-major)
-  rc = tr ? make_map(&map_b, right, k, n, 32, BN) : make_map(&map_b, right, n, k, 32, 32);
+  rc = tr ? make_map(&map_b, right, k, n, 32, BN, false) : make_map(&map_b, right, n, k, 32, 32, true);
   if (rc) return rc;
   Params p;
   p.m = m; p.n = n; p.k = k; p.out = out;
