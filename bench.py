@@ -1,0 +1,506 @@
+#!/usr/bin/env python
+"""Benchmark of the PolarAI B200 runtime's hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload mlp|gemm|elementwise] [--no-graph] [--no-extras]
+
+Default workload (the one that shards over 1/2/4/8 GPUs): one training step of the
+2-layer MLP 784-4096-10 (Sigmoid hidden layer, LogLoss on one-hot targets, fp32,
+global batch 65536 batch-sharded over the ranks, gradient all-reduce over NCCL,
+SGD update at lr = 0.1), expressed as the reference's builtins
+(polarai-framework_b200/program.py).  Data is synthetic: X ~ N(0,1), uniform
+labels, Xavier-uniform weights, seed 0.
+
+One JSON line is printed by rank 0.  `value` is samples/s with the inputs already
+in HBM; `e2e` is samples/s when every step also copies its X and Y shard from
+pinned host memory and reads the mean loss back.  `roofline` describes the
+dominant kernel (the tcgen05 fmatmul), `cpu_baseline` the same builtin program
+timed on host cores on a bounded sample (rank 0, N=1 only).  With --workload gemm
+or elementwise the line reports fp32 MatMul TFLOP/s at 8192^3 or HBM GB/s of the
+elementwise builtins at 2^28 elements instead (single GPU).
+
+--impl reference times the reference's own CPU statement of the builtins (its
+OpenCL C kernels compiled as C when oracle/_ref was built, else the C restatement)
+on all host cores, on a bounded sample of the same workload per step.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_IN, N_HIDDEN, N_OUT, GLOBAL_BATCH, LR = 784, 4096, 10, 65536, 0.1
+FLOP_PER_SAMPLE = 2 * (2 * N_IN * N_HIDDEN + 3 * N_HIDDEN * N_OUT)   # 13,090,816
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2])), power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def mlp_inputs(rng, batch):
+    import numpy as np
+    X = rng.standard_normal((batch, N_IN), dtype=np.float32)
+    labels = rng.integers(0, N_OUT, batch)
+    Y = np.zeros((batch, N_OUT), np.float32)
+    Y[np.arange(batch), labels] = 1.0
+    return X, Y
+
+
+def mlp_weights(rng):
+    import numpy as np
+    a1, a2 = np.sqrt(6.0 / (N_IN + N_HIDDEN)), np.sqrt(6.0 / (N_HIDDEN + N_OUT))
+    W1 = rng.uniform(-a1, a1, (N_IN, N_HIDDEN)).astype(np.float32)
+    W2 = rng.uniform(-a2, a2, (N_HIDDEN, N_OUT)).astype(np.float32)
+    return W1, W2
+
+
+def cpu_impl():
+    """The CPU engine for baselines: the reference's kernels compiled as C when
+    oracle/_ref exists, else the C restatement; all host threads."""
+    from oracle import oracle as orc
+    if orc.RefOcl.available():
+        impl = orc.RefOcl()
+    else:
+        impl = orc.Oracle()
+    impl.set_threads(impl.max_threads())
+    return impl
+
+
+def cpu_mlp_baseline(sample_batch, steps=1, warmup=0):
+    """The MLP builtin program on host cores over `sample_batch` rows per step."""
+    import numpy as np
+    import __graft_entry__ as ge
+    ge.load_package()
+    from polarai_framework_b200.program import mlp_program
+    from oracle.program_executor import OracleExecutor
+    impl = cpu_impl()
+    rng = np.random.default_rng(0)
+    X, Y = mlp_inputs(rng, sample_batch)
+    W1, W2 = mlp_weights(rng)
+    ex = OracleExecutor(mlp_program(sample_batch, N_IN, N_HIDDEN, N_OUT, LR), impl)
+    ex.set_inputs(X=X, Y=Y, W1=W1, W2=W2)
+    for _ in range(warmup):
+        ex.run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ex.run()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": sample_batch / dt, "unit": "samples/s", "cores": impl.threads, "kind": impl.kind,
+            "sample": f"{steps} step(s) of the same MLP builtin program on {sample_batch} of the "
+                      f"{GLOBAL_BATCH} rows, {dt:.2f} s per step"}, dt
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 512
+    base, dt = cpu_mlp_baseline(sample, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    line = {"impl": "reference", "metric": "mlp_fwd_bwd_samples_per_s", "value": base["value"],
+            "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "mlp_784_4096_10_fwd_bwd_sgd", "global_batch": GLOBAL_BATCH,
+                       "sample_batch_per_step": sample, "parallelism": "host threads"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "samples/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_region(torch, fn, steps, dist, world):
+    """barrier + sync, `steps` calls of fn, sync + barrier; device time by CUDA
+    events on the launching stream; max over ranks."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def per_op_times(torch, ex, reps):
+    """Replays the program with an event pair around every launch."""
+    prog = ex.program
+    acc = [0.0] * len(prog.ops)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(reps):
+        evs = []
+        for i, (kernel, arr, n) in enumerate(ex._compiled):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            if kernel is None:
+                if ex.allreduce is not None:
+                    ex.allreduce(ex.t[arr])
+            else:
+                ex.lib.check(ex._fn(kernel, arr, n, None, 0, s))
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        for i, (a, b) in enumerate(evs):
+            acc[i] += a.elapsed_time(b)
+    return [x / reps for x in acc]
+
+
+def run_mlp(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    from polarai_framework_b200.data_parallel import init_from_env, make_allreduce, shard_rows
+    from polarai_framework_b200.program import DeviceExecutor, mlp_program
+
+    rank, world, local = init_from_env()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    lo, hi = shard_rows(GLOBAL_BATCH, rank, world)
+    per = hi - lo
+    rng = np.random.default_rng(0)
+    W1, W2 = mlp_weights(rng)                               # identical on every rank
+    Xs, Ys = mlp_inputs(np.random.default_rng(1000 + rank), per)   # this rank's rows
+    program = mlp_program(per, N_IN, N_HIDDEN, N_OUT, LR)
+    ex = DeviceExecutor(program, dev, make_allreduce(world))
+    x_host = torch.from_numpy(Xs).pin_memory()
+    y_host = torch.from_numpy(Ys).pin_memory()
+    w1, w2 = torch.from_numpy(W1).to(dev), torch.from_numpy(W2).to(dev)
+    ex.t["X"].copy_(x_host), ex.t["Y"].copy_(y_host)
+    loss_acc = torch.zeros(1, dtype=torch.float64, device=dev)
+    loss_host = torch.zeros(1, dtype=torch.float64).pin_memory()
+    lib = pkg.lib()
+
+    def reset_weights():
+        ex.t["W1"].copy_(w1), ex.t["W2"].copy_(w2)
+
+    def step():
+        ex.run()
+
+    use_graph = not args.no_graph
+    graph = None
+    reset_weights()
+    for _ in range(max(3, args.warmup)):                    # warm-up, eager (also primes NCCL)
+        step()
+    torch.cuda.synchronize()
+    if use_graph:
+        try:
+            cap_stream = torch.cuda.Stream()
+            cap_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(cap_stream):
+                step()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=cap_stream):
+                    step()
+            torch.cuda.synchronize()
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:                            # capture is an optimisation, not a requirement
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({exc}); running eagerly", file=sys.stderr)
+            graph = None
+    launches_per_step = program.launches()
+
+    def timed_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
+    # ---- device-resident throughput ----
+    reset_weights()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = lib.launch_count()
+    ms = time_region(torch, timed_step, args.steps, dist, world)
+    launched = lib.launch_count() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = GLOBAL_BATCH / (ms_per_step / 1e3)
+
+    # ---- end to end: host batch in, mean loss out, every step ----
+    def e2e_step():
+        ex.t["X"].copy_(x_host, non_blocking=True)
+        ex.t["Y"].copy_(y_host, non_blocking=True)
+        timed_step()
+        loss_acc.zero_()
+        ex.lib.call("polar_b200_fsum", ex.t["L"].data_ptr(), loss_acc.data_ptr(), ex.t["L"].numel(),
+                    torch.cuda.current_stream().cuda_stream)
+        loss_host.copy_(loss_acc, non_blocking=True)
+        torch.cuda.current_stream().synchronize()           # the caller reads the loss each step
+
+    reset_weights()
+    e2e_step()
+    e2e_ms = time_region(torch, e2e_step, args.steps, dist, world) / args.steps
+    e2e = {"value": GLOBAL_BATCH / (e2e_ms / 1e3), "unit": "samples/s",
+           "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 4) * world,
+           "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_ms,
+           "path": "pinned host X,Y shard -> cudaMemcpyAsync -> builtin program -> fsum -> 8-byte loss readback"}
+
+    # ---- first-step loss, for the record ----
+    reset_weights()
+    step()
+    loss_acc.zero_()
+    ex.lib.call("polar_b200_fsum", ex.t["L"].data_ptr(), loss_acc.data_ptr(), ex.t["L"].numel(),
+                torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    first_loss = float(loss_acc.item()) / (per * N_OUT)
+
+    # ---- roofline of the dominant kernel, measured live with events per launch ----
+    reset_weights()
+    times = per_op_times(torch, ex, reps=min(5, args.steps))
+    total_ops_ms = sum(times)
+    by_kernel = {}
+    for (kernel, a), t in zip(program.ops, times):
+        key = kernel if not kernel.startswith("fmatmul") else f"{kernel}:{a[2]}"
+        d = by_kernel.setdefault(key, {"launches": 0, "ms": 0.0})
+        d["launches"] += 1
+        d["ms"] += t
+    peaks = load_peaks()
+    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0        # dense TF32 = half the dense bf16 rate
+    tc_ops = [(i, k, a) for i, (k, a) in enumerate(program.ops)
+              if k.startswith("fmatmul") and lib.cdll.polar_b200_fmatmul_path(
+                  int(k[8] == "t"), int(k[10] == "t"), *mm_dims(program, k, a)) == 0]
+    tc_ms = sum(times[i] for i, _, _ in tc_ops)
+    tc_flops = sum(2.0 * np.prod(mm_dims(program, k, a)) for _, k, a in tc_ops)
+    achieved = tc_flops / (tc_ms / 1e3) / 1e12 if tc_ms > 0 else 0.0
+    roofline = {"kernel": "fmatmul_tc_kernel (tcgen05, 3xTF32)", "bound": "tensor",
+                "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
+                "pipe_frac": 3.0 * achieved / tf32_peak,
+                "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained / 2 ({peaks['source']}); "
+                               "fp32-accurate products issue 3 TF32 MMAs each, so frac <= 1/3 and "
+                               "pipe_frac = 3 x frac is the tensor-pipe utilisation",
+                "launches_per_step": len(tc_ops), "avg_launch_ms": tc_ms / max(1, len(tc_ops)),
+                "share_of_step": tc_ms / total_ops_ms if total_ops_ms else None,
+                "traffic": None}
+
+    line = {"metric": "mlp_fwd_bwd_samples_per_s", "value": value, "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "mlp_784_4096_10_fwd_bwd_sgd", "global_batch": GLOBAL_BATCH,
+                       "per_gpu_batch": per, "lr": LR, "parallelism": f"dp{world}",
+                       "cuda_graph": graph is not None,
+                       "l2": "per-step working set (X 205 MB/GPU-share, seven Bx4096 activations) "
+                             "exceeds the 126 MB L2 at every N"},
+            "flop_per_sample": FLOP_PER_SAMPLE, "tflops": value * FLOP_PER_SAMPLE / 1e12,
+            "first_step_mean_loss": first_loss,
+            "gpu_launches": int(launched) if graph is None else launches_per_step * args.steps,
+            "launches_per_step": launches_per_step,
+            "clocks": clocks, "e2e": e2e, "roofline": roofline,
+            "breakdown_ms": {k: round(v["ms"], 4) for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1]["ms"])}}
+    if rank == 0 and world == 1 and not args.no_extras:
+        line["cpu_baseline"] = cpu_mlp_baseline(2048, steps=1)[0]
+        line["extras"] = {"gemm_8192": gemm_numbers(torch, lib, 8192, reps=3),
+                          "elementwise_2pow28": elementwise_numbers(torch, lib, 1 << 28, peaks, reps=5)}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def mm_dims(program, kernel, args):
+    tl, tr = kernel[8] == "t", kernel[10] == "t"
+    ls, rs = program.tensors[args[0]], program.tensors[args[1]]
+    m = ls[1] if tl else ls[0]
+    k = ls[0] if tl else ls[1]
+    n = rs[0] if tr else rs[1]
+    return int(m), int(n), int(k)
+
+
+def event_time(torch, fn, reps, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / reps
+
+
+def gemm_numbers(torch, lib, n, reps):
+    st = torch.cuda.current_stream().cuda_stream
+    a = torch.empty((n, n), device="cuda").uniform_(-1, 1)
+    b = torch.empty((n, n), device="cuda").uniform_(-1, 1)
+    c = torch.empty((n, n), device="cuda")
+    out = {}
+    for tl in (0, 1):
+        for tr in (0, 1):
+            ms = event_time(torch, lambda: lib.call("polar_b200_fmatmul", tl, tr, n, n, n, a.data_ptr(),
+                                                    b.data_ptr(), c.data_ptr(), None, 0, st), reps)
+            out[f"fmatmul_{'t' if tl else 'f'}_{'t' if tr else 'f'}"] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
+    return out
+
+
+def elementwise_numbers(torch, lib, n, peaks, reps):
+    st = torch.cuda.current_stream().cuda_stream
+    a = torch.empty(n, device="cuda").uniform_(-1, 1)
+    b = torch.empty(n, device="cuda").uniform_(0.5, 2)
+    p = torch.empty(n, device="cuda").uniform_(0.01, 0.99)
+    y = (torch.rand(n, device="cuda") < 0.5).float()
+    o = torch.empty(n, device="cuda")
+    A, B, P, Y, O = (t.data_ptr() for t in (a, b, p, y, o))
+    ops = {
+        "ffill": (4, lambda: lib.call("polar_b200_ffill", 1.234, O, n, st)),
+        "fcopy": (8, lambda: lib.call("polar_b200_fcopy", A, O, n, st)),
+        "fsigmoid": (8, lambda: lib.call("polar_b200_fsigmoid", A, O, n, st)),
+        "fadd": (12, lambda: lib.call("polar_b200_fadd", A, 1.0, B, 1.0, O, n, st)),
+        "fmul": (12, lambda: lib.call("polar_b200_fmul", A, B, O, n, st)),
+        "fdivide": (12, lambda: lib.call("polar_b200_fdivide", A, B, O, n, st)),
+        "flogloss": (12, lambda: lib.call("polar_b200_flogloss", P, Y, O, n, st)),
+    }
+    out = {}
+    for name, (bpe, fn) in ops.items():
+        ms = event_time(torch, fn, reps)
+        gbs = bpe * n / ms / 1e6
+        out[name] = {"ms": ms, "gbs": gbs, "frac_of_measured_copy": gbs / peaks["hbm_gbs"], "frac_of_8tbs": gbs / 8000.0}
+    return out
+
+
+def run_single_kernel_workload(args):
+    """--workload gemm | elementwise: single-GPU lines for the other two parts of the metric."""
+    import torch
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    lib = pkg.lib()
+    peaks = load_peaks()
+    torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = lib.launch_count()
+    if args.workload == "gemm":
+        n = 8192
+        res = gemm_numbers(torch, lib, n, reps=max(1, args.steps))
+        ms = res["fmatmul_f_f"]["ms"]
+        tf = res["fmatmul_f_f"]["tflops"]
+        peak = peaks["bf16_tflops"] / 2.0
+        line = {"metric": "fp32_matmul_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "dtype": "f32",
+                "config": {"workload": "fmatmul_f_f_8192x8192x8192", "l2": "operands 805 MB > 126 MB L2"},
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                             "pipe_frac": 3 * tf / peak, "traffic": None,
+                             "peak_source": f"MEASURED_PEAKS.json bf16_tflops / 2 ({peaks['source']})"},
+                "variants": res}
+    else:
+        n = 1 << 28
+        res = elementwise_numbers(torch, lib, n, peaks, reps=max(3, args.steps))
+        gbs = res["fadd"]["gbs"]
+        line = {"metric": "elementwise_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": res["fadd"]["ms"],
+                "dtype": "f32",
+                "config": {"workload": "fadd_2pow28", "l2": "three 1 GiB streams > 126 MB L2"},
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                             "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peaks['source']})"},
+                "builtins": res}
+    line.update({"n_gpus": 1, "steps": args.steps, "warmup": 3, "higher_is_better": True, "scaling": "weak",
+                 "vs_baseline": None, "data": "synthetic", "gpu_launches": int(lib.launch_count() - n0),
+                 "clocks": sampler.stop()})
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "elementwise"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the runtime has no CPU path (use --impl reference "
+                         "for the CPU arm)")
+    if args.workload == "mlp":
+        run_mlp(args)
+    else:
+        run_single_kernel_workload(args)
+
+
+if __name__ == "__main__":
+    main()

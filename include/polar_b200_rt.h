@@ -1,0 +1,90 @@
+/*
+ * polar_b200_rt.h - what libpolar_rt_cuda.so exports.
+ *
+ * 1. The plugin interface a PolarAI RuntimeDriver binds with dlsym
+ *    (include/polarai/backend/generic/runtime/api.h:17-20 of the reference;
+ *    looked up in src/backend/generic/runtime/driver/RuntimeDriver.cpp:39-46):
+ *
+ *        polarai::backend::generic::Context* initContext();
+ *        void closeContext(polarai::backend::generic::Context*);
+ *
+ *    The returned Context lists one Device per sm_100 GPU; each Device implements
+ *    the reference's abstract classes Device, Event and AllocatorLayerBase
+ *    (Device.hpp:34-63, Event.hpp:19-25, AllocatorLayerBase.hpp:22-40) and
+ *    replaces src/backend/generic/runtime/cuda/{CudaContext,CudaDevice,
+ *    CudaAllocator,CudaEvent}.  These two symbols are C++-typed; C callers use
+ *    the handle functions below.
+ *
+ * 2. A flat C view of the same objects, for hosts that cannot call C++ virtuals
+ *    (ctypes, cgo, tests).  Every function forwards to the virtual methods the
+ *    executor's support routines would call
+ *    (src/backend/generic/runtime/support/routines.cpp:37-112: ath_allocate,
+ *    ath_lock, ath_launch, ath_release, ath_barrier, ath_load), through a
+ *    BackendAllocator built on the devices' stream-ordered pools.
+ *
+ * Return values are polar_b200_status codes (polar_b200.h); nothing aborts.
+ */
+#ifndef POLAR_B200_RT_H
+#define POLAR_B200_RT_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* LaunchCommand, ArgDesc and TensorInfo are the reference's own plain-C structs
+ * (include/polarai/backend/generic/runtime/LaunchCommand.h:19-31 and
+ * TensorInfo.h:17-22); they are only named here. */
+struct LaunchCommand;
+
+typedef struct polar_b200_rt polar_b200_rt;
+
+/* initContext() + a BackendAllocator with every device registered. */
+polar_b200_rt* polar_b200_rt_open(void);
+/* Releases devices, pools and pinned host memory, then closeContext(). */
+void polar_b200_rt_close(polar_b200_rt* rt);
+
+int polar_b200_rt_device_count(polar_b200_rt* rt);
+/* Device::getDeviceName(); unique per GPU ("NVIDIA B200 #0"). */
+const char* polar_b200_rt_device_name(polar_b200_rt* rt, int device);
+
+/* ath_allocate on a device: BackendAllocator::allocate(record, device). */
+int polar_b200_rt_allocate(polar_b200_rt* rt, int device, uint64_t virtAddr, uint64_t bytes);
+/* BackendAllocator::deallocate on every layer that holds the record. */
+int polar_b200_rt_deallocate(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes);
+
+/* What ath_load does with a MemcpyLoader: host READ_WRITE lock, copy `bytes`
+ * from `src` into the record's host memory, release.  The device copy becomes
+ * stale and is refreshed by the next device lock (one host-to-device copy). */
+int polar_b200_rt_write(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes, const void* src);
+/* What OutputNodeAccessor does: host READ lock (pulls the newest copy to the
+ * host: one device-to-host copy, after the device's stream has drained), copy
+ * out, release. */
+int polar_b200_rt_read(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes, void* dst);
+
+/* One builtin: READ_WRITE lock on the last tensor argument, READ locks on the
+ * others (as the operations' gen() methods emit), Device::launch, release.
+ * The launch is asynchronous; errors of the launch itself are returned. */
+int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cmd);
+/* ath_barrier over everything launched on the device so far. */
+int polar_b200_rt_barrier(polar_b200_rt* rt, int device);
+
+/* Device pointer of a record on a device (NULL if absent), and the device's
+ * stream, for callers that mix their own CUDA work in. */
+void* polar_b200_rt_device_ptr(polar_b200_rt* rt, int device, uint64_t virtAddr, uint64_t bytes);
+void* polar_b200_rt_stream(polar_b200_rt* rt, int device);
+
+/* Bytes currently held by a device's pool layer, and an optional cap on them
+ * (0 = none): past the cap, unlocked records are offloaded to host memory and
+ * freed, oldest first. */
+uint64_t polar_b200_rt_bytes_in_use(polar_b200_rt* rt, int device);
+int polar_b200_rt_set_memory_limit(polar_b200_rt* rt, int device, uint64_t bytes);
+
+/* Text of the last error seen through this handle. */
+const char* polar_b200_rt_last_error(polar_b200_rt* rt);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLAR_B200_RT_H */

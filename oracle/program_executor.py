@@ -1,0 +1,53 @@
+"""Runs a builtin Program (polarai-framework_b200/program.py) on the CPU oracle.
+TEST INFRASTRUCTURE ONLY: used by the tests, the smoke check and the bench's
+CPU-baseline legs to execute the identical builtin sequence on host cores."""
+import numpy as np
+
+
+class OracleExecutor:
+    def __init__(self, program, impl, allreduce=None):
+        self.program = program
+        self.impl = impl
+        self.allreduce = allreduce
+        self.t = {n: np.zeros(s, np.float32) for n, s in program.tensors.items()}
+        for name, v in program.constants.items():
+            self.t[name] = impl.ffill(v, int(np.prod(program.tensors[name]))).reshape(program.tensors[name])
+
+    def set_inputs(self, **arrays):
+        for name, a in arrays.items():
+            self.t[name] = np.ascontiguousarray(a, np.float32).reshape(self.program.tensors[name])
+
+    def run(self):
+        t, o = self.t, self.impl
+        for kernel, args in self.program.ops:
+            g = lambda i: t[args[i]]
+            if kernel == "ALLREDUCE":
+                if self.allreduce is not None:
+                    t[args[0]] = self.allreduce(t[args[0]])
+                continue
+            out = args[-1]
+            shape = self.program.tensors[out]
+            if kernel == "fadd":
+                r = o.fadd(g(0).ravel(), args[1], g(2).ravel(), args[3])
+            elif kernel == "fmul":
+                r = o.fmul(g(0).ravel(), g(1).ravel())
+            elif kernel == "fdivide":
+                r = o.fdivide(g(0).ravel(), g(1).ravel())
+            elif kernel == "fsigmoid":
+                r = o.fsigmoid(g(0).ravel())
+            elif kernel == "flogloss":
+                r = o.flogloss(g(0).ravel(), g(1).ravel())
+            elif kernel == "fcopy":
+                r = o.fcopy(g(0).ravel())
+            elif kernel == "ffill":
+                r = o.ffill(args[0], int(np.prod(shape)))
+            elif kernel == "fmulconcat":
+                r = o.fmulconcat(g(0).ravel(), g(1).ravel())
+            elif kernel.startswith("fmatmul_"):
+                r = o.fmatmul(kernel[8] == "t", kernel[10] == "t", g(0), g(1))
+            else:
+                raise KeyError(kernel)
+            t[out] = np.asarray(r, np.float32).reshape(shape)
+
+    def output(self, name):
+        return self.t[name]

@@ -14,7 +14,7 @@ PoolBackendAllocator::~PoolBackendAllocator() {
 }
 
 void PoolBackendAllocator::registerDevice(Device& device) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   for (auto& l : mLayers)
     if (l.device == &device) return;
   if (!device.hasAllocator()) return;
@@ -22,7 +22,7 @@ void PoolBackendAllocator::registerDevice(Device& device) {
   // When a device layer is short of memory it asks us to save the block first
   // (the reference's offload hook, LayerAllocator.cpp:238-249).
   layer->registerMemoryOffloadCallback([this](MemoryRecord rec, AllocatorLayerBase& from) {
-    std::unique_lock<std::mutex> g(mMutex);
+    std::unique_lock<std::recursive_mutex> g(mMutex);
     auto it = mEntries.find(rec.virtualAddress);
     if (it == mEntries.end()) return;
     if (from.getTag(rec) == it->second.tag) {   // the evicted copy is the newest one
@@ -88,7 +88,7 @@ void PoolBackendAllocator::updateHost(const MemoryRecord& record) {
 // ---- allocate
 
 void PoolBackendAllocator::allocate(const MemoryRecord& record, Device& device) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   DeviceLayer* l = layerOf(device);
   if (!l) return fail(POLAR_B200_ERR_INVALID, "allocate: device is not registered");
   if (l->layer->isAllocated(record)) return;   // double allocation is a no-op
@@ -100,7 +100,7 @@ void PoolBackendAllocator::allocate(const MemoryRecord& record, Device& device) 
 }
 
 void PoolBackendAllocator::allocate(const MemoryRecord& record) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   if (mHost.count(record.virtualAddress)) return;
   for (auto& l : mLayers)
     if (l.layer->isAllocated(record)) return;
@@ -120,7 +120,7 @@ void PoolBackendAllocator::allocate(const TensorInternal& tensor) {
 }
 
 void PoolBackendAllocator::deallocate(const MemoryRecord& record) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   auto it = mEntries.find(record.virtualAddress);
   if (it != mEntries.end() && !it->second.locks.empty())
     return fail(POLAR_B200_ERR_INVALID, "deallocate: record is locked");
@@ -141,7 +141,7 @@ void PoolBackendAllocator::deallocate(const TensorInternal& tensor) {
 // ---- lock / release
 
 void PoolBackendAllocator::lock(const MemoryRecord& record, Device& device, LockType type) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   DeviceLayer* l = layerOf(device);
   if (!l) return fail(POLAR_B200_ERR_INVALID, "lock: device is not registered");
   Entry& e = mEntries[record.virtualAddress];
@@ -179,7 +179,7 @@ void PoolBackendAllocator::lock(const MemoryRecord& record, Device& device, Lock
 }
 
 void PoolBackendAllocator::lock(const MemoryRecord& record, LockType type) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   Entry& e = mEntries[record.virtualAddress];
   if (type == LockType::READ_WRITE && !e.locks.empty())
     return fail(POLAR_B200_ERR_INVALID, "READ_WRITE lock requested for a record that is already locked");
@@ -205,7 +205,7 @@ void PoolBackendAllocator::lock(const TensorInternal& tensor, LockType type) {
 }
 
 void PoolBackendAllocator::release(const MemoryRecord& record, Device& device) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   auto it = mEntries.find(record.virtualAddress);
   if (it == mEntries.end()) return;
   auto& locks = it->second.locks;
@@ -219,7 +219,7 @@ void PoolBackendAllocator::release(const MemoryRecord& record, Device& device) {
 }
 
 void PoolBackendAllocator::release(const MemoryRecord& record) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   auto it = mEntries.find(record.virtualAddress);
   if (it == mEntries.end()) return;
   auto& locks = it->second.locks;
@@ -238,7 +238,7 @@ void PoolBackendAllocator::release(const TensorInternal& tensor) {
 // ---- get
 
 void* PoolBackendAllocator::get(const MemoryRecord& record) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   auto hit = mHost.find(record.virtualAddress);
   return hit == mHost.end() ? nullptr : hit->second.ptr;
 }
@@ -247,7 +247,7 @@ void* PoolBackendAllocator::get(const TensorInternal& tensor) {
   return toRecord(tensor, r) ? get(r) : nullptr;
 }
 void* PoolBackendAllocator::getImpl(const MemoryRecord& record, Device& device) {
-  std::unique_lock<std::mutex> guard(mMutex);
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
   DeviceLayer* l = layerOf(device);
   return l ? l->layer->getPtr(record) : nullptr;
 }

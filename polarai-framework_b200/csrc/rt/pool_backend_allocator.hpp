@@ -80,7 +80,7 @@ private:
   std::unordered_map<size_t, HostBlock> mHost;
   std::unordered_map<size_t, Entry> mEntries;
   TensorToRecord mToRecord;
-  std::mutex mMutex;
+  std::recursive_mutex mMutex;
   int mStatus = 0;
   const char* mError = "";
 };

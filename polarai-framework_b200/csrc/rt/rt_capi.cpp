@@ -1,0 +1,195 @@
+// Flat C view of the runtime plugin (include/polar_b200_rt.h).
+#include "b200_runtime.hpp"
+#include "pool_backend_allocator.hpp"
+
+#include <polarai/backend/generic/runtime/LaunchCommand.h>
+#include <polarai/backend/generic/runtime/TensorInfo.h>
+#include <polarai/backend/generic/runtime/api.h>
+
+#include <polar_b200.h>
+#include <polar_b200_rt.h>
+
+#include <cstring>
+#include <string>
+
+using namespace polarai::backend::generic;
+using polarai::core::internal::LockType;
+
+struct polar_b200_rt {
+  Context* ctx = nullptr;
+  std::vector<std::shared_ptr<Device>> devices;
+  std::shared_ptr<PoolBackendAllocator> allocator;
+  std::vector<std::string> names;
+  std::string error;
+};
+
+namespace {
+B200Device* dev(polar_b200_rt* rt, int i) {
+  if (!rt || i < 0 || i >= (int)rt->devices.size()) return nullptr;
+  return static_cast<B200Device*>(rt->devices[i].get());
+}
+int fail(polar_b200_rt* rt, int status, const std::string& msg) {
+  if (rt) rt->error = msg;
+  return status;
+}
+int allocator_status(polar_b200_rt* rt) {
+  int s = rt->allocator->lastStatus();
+  if (s) {
+    rt->error = rt->allocator->lastError();
+    rt->allocator->clearError();
+  }
+  return s;
+}
+}  // namespace
+
+extern "C" {
+
+polar_b200_rt* polar_b200_rt_open(void) {
+  auto* rt = new polar_b200_rt();
+  rt->ctx = initContext();
+  rt->devices = rt->ctx->getDevices();
+  rt->allocator = std::make_shared<PoolBackendAllocator>();
+  for (auto& d : rt->devices) {
+    rt->allocator->registerDevice(*d);
+    rt->names.push_back(d->getDeviceName());
+  }
+  return rt;
+}
+
+void polar_b200_rt_close(polar_b200_rt* rt) {
+  if (!rt) return;
+  for (auto& d : rt->devices) static_cast<B200Device*>(d.get())->synchronize();
+  rt->allocator.reset();
+  rt->devices.clear();
+  closeContext(rt->ctx);
+  delete rt;
+}
+
+int polar_b200_rt_device_count(polar_b200_rt* rt) { return rt ? (int)rt->devices.size() : 0; }
+
+const char* polar_b200_rt_device_name(polar_b200_rt* rt, int device) {
+  return dev(rt, device) ? rt->names[device].c_str() : "";
+}
+
+int polar_b200_rt_allocate(polar_b200_rt* rt, int device, uint64_t va, uint64_t bytes) {
+  B200Device* d = dev(rt, device);
+  if (!d) return fail(rt, POLAR_B200_ERR_INVALID, "no such device");
+  rt->allocator->allocate(MemoryRecord{va, bytes}, *d);
+  return allocator_status(rt);
+}
+
+int polar_b200_rt_deallocate(polar_b200_rt* rt, uint64_t va, uint64_t bytes) {
+  if (!rt) return POLAR_B200_ERR_INVALID;
+  rt->allocator->deallocate(MemoryRecord{va, bytes});
+  return allocator_status(rt);
+}
+
+int polar_b200_rt_write(polar_b200_rt* rt, uint64_t va, uint64_t bytes, const void* src) {
+  if (!rt || (!src && bytes)) return fail(rt, POLAR_B200_ERR_INVALID, "null source");
+  MemoryRecord rec{va, bytes};
+  rt->allocator->lock(rec, LockType::READ_WRITE);
+  if (int s = allocator_status(rt)) return s;
+  void* host = rt->allocator->get(rec);
+  if (!host) {
+    rt->allocator->release(rec);
+    return fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
+  }
+  std::memcpy(host, src, bytes);
+  rt->allocator->release(rec);
+  return POLAR_B200_OK;
+}
+
+int polar_b200_rt_read(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void* dst) {
+  if (!rt || (!dst && bytes)) return fail(rt, POLAR_B200_ERR_INVALID, "null destination");
+  MemoryRecord rec{va, bytes};
+  rt->allocator->lock(rec, LockType::READ);
+  if (int s = allocator_status(rt)) return s;
+  void* host = rt->allocator->get(rec);
+  if (!host) {
+    rt->allocator->release(rec);
+    return fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
+  }
+  std::memcpy(dst, host, bytes);
+  rt->allocator->release(rec);
+  for (auto& d : rt->devices) {
+    auto* bd = static_cast<B200Device*>(d.get());
+    if (bd->lastStatus()) return fail(rt, bd->lastStatus(), bd->lastError());
+  }
+  return POLAR_B200_OK;
+}
+
+int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cmd) {
+  B200Device* d = dev(rt, device);
+  if (!d || !cmd) return fail(rt, POLAR_B200_ERR_INVALID, "no such device or null command");
+  // Locks as the operations' gen() methods take them: the output (last tensor
+  // argument) READ_WRITE, every other tensor READ.
+  int64_t out_idx = -1;
+  for (uint64_t i = 0; i < cmd->argsCount; ++i)
+    if (cmd->args[i].type == ArgDesc::TENSOR) out_idx = (int64_t)i;
+  auto record_of = [](TensorInfo* t) {
+    MemoryRecord r{t->virtAddr, 4};
+    for (uint64_t k = 0; k < t->dims; ++k) r.allocationSize *= t->shape[k];
+    return r;
+  };
+  std::vector<MemoryRecord> locked;
+  auto unlock_all = [&] { for (auto& r : locked) rt->allocator->release(r, *d); };
+  auto is_locked = [&](const MemoryRecord& r) {
+    for (auto& l : locked) if (l == r) return true;
+    return false;
+  };
+  if (out_idx >= 0) {
+    MemoryRecord r = record_of(static_cast<TensorInfo*>(cmd->args[out_idx].arg));
+    rt->allocator->lock(r, *d, LockType::READ_WRITE);
+    if (int s = allocator_status(rt)) return s;
+    locked.push_back(r);
+  }
+  for (uint64_t i = 0; i < cmd->argsCount; ++i) {
+    if (cmd->args[i].type != ArgDesc::TENSOR || (int64_t)i == out_idx) continue;
+    MemoryRecord r = record_of(static_cast<TensorInfo*>(cmd->args[i].arg));
+    if (is_locked(r)) continue;   // an in-place update reads what it writes
+    rt->allocator->lock(r, *d, LockType::READ);
+    if (int s = allocator_status(rt)) { unlock_all(); return s; }
+    locked.push_back(r);
+  }
+  Event* evt = d->launch(*rt->allocator, *cmd, nullptr);
+  int status = static_cast<B200Event*>(evt)->status();
+  if (status) rt->error = d->lastError();
+  // Stream order protects the buffers; the locks can go as soon as the work is queued.
+  unlock_all();
+  delete evt;
+  return status;
+}
+
+int polar_b200_rt_barrier(polar_b200_rt* rt, int device) {
+  B200Device* d = dev(rt, device);
+  if (!d) return fail(rt, POLAR_B200_ERR_INVALID, "no such device");
+  d->synchronize();
+  if (d->lastStatus()) return fail(rt, d->lastStatus(), d->lastError());
+  return POLAR_B200_OK;
+}
+
+void* polar_b200_rt_device_ptr(polar_b200_rt* rt, int device, uint64_t va, uint64_t bytes) {
+  B200Device* d = dev(rt, device);
+  return d ? d->getAllocator()->getPtr(MemoryRecord{va, bytes}) : nullptr;
+}
+
+void* polar_b200_rt_stream(polar_b200_rt* rt, int device) {
+  B200Device* d = dev(rt, device);
+  return d ? (void*)d->stream() : nullptr;
+}
+
+uint64_t polar_b200_rt_bytes_in_use(polar_b200_rt* rt, int device) {
+  B200Device* d = dev(rt, device);
+  return d ? static_cast<B200Allocator*>(d->getAllocator().get())->bytesInUse() : 0;
+}
+
+int polar_b200_rt_set_memory_limit(polar_b200_rt* rt, int device, uint64_t bytes) {
+  B200Device* d = dev(rt, device);
+  if (!d) return fail(rt, POLAR_B200_ERR_INVALID, "no such device");
+  static_cast<B200Allocator*>(d->getAllocator().get())->setLimit(bytes);
+  return POLAR_B200_OK;
+}
+
+const char* polar_b200_rt_last_error(polar_b200_rt* rt) { return rt ? rt->error.c_str() : ""; }
+
+}  // extern "C"

@@ -1,0 +1,198 @@
+"""Builtin programs: the flat list of builtin launches a PolarAI graph compiles to.
+
+The reference's GraphCompiler walks a graph and emits, per node, one builtin call
+(src/core/graph/internal/GraphCompiler.cpp:21-110; the operations' gen() methods
+under src/operation/internal/ choose the builtin and its argument order).  A
+`Program` is that list, with tensors named instead of numbered.  The same program
+object is executed by the CUDA runtime (DeviceExecutor below) and, in the tests and
+the CPU baseline, by the CPU oracle - both sides run the identical sequence.
+
+Programs for the benchmark configurations are built here from the reference's
+operations: MatMul -> fmatmul_{f,t}_{f,t}, Sigmoid -> fsigmoid, LogLoss -> flogloss,
+Add/Combine -> fadd, Mul -> fmul, Divide -> fdivide; derivatives are composed as
+the operations' genDerivative() methods compose them
+(SigmoidOperationInternal.cpp:107-135, LogLossOperationInternal.cpp:127-170).
+"ALLREDUCE" is the one step the reference has no counterpart for: the sum of a
+gradient over data-parallel ranks.
+"""
+import ctypes
+from dataclasses import dataclass, field
+
+import torch
+
+from .capi import Arg, lib
+
+
+@dataclass
+class Program:
+    name: str
+    tensors: dict = field(default_factory=dict)      # name -> shape
+    ops: list = field(default_factory=list)          # (native kernel name, [tensor names / floats])
+    inputs: list = field(default_factory=list)       # tensors the caller fills
+    constants: dict = field(default_factory=dict)    # name -> fill value (ConstantLoader)
+    outputs: list = field(default_factory=list)
+
+    def tensor(self, name, *shape):
+        self.tensors[name] = tuple(int(s) for s in shape)
+        return name
+
+    def op(self, kernel, *args):
+        self.ops.append((kernel, list(args)))
+
+    def launches(self):
+        return sum(1 for k, _ in self.ops if k != "ALLREDUCE")
+
+
+def elementwise_chain_program(n):
+    """out = sigmoid((a + b) * c / d): Add -> Mul -> Divide -> Sigmoid."""
+    p = Program("elementwise_chain")
+    for t in "abcd":
+        p.tensor(t, n)
+    p.inputs = list("abcd")
+    p.tensor("t1", n), p.tensor("t2", n), p.tensor("t3", n), p.tensor("out", n)
+    p.op("fadd", "a", 1.0, "b", 1.0, "t1")
+    p.op("fmul", "t1", "c", "t2")
+    p.op("fdivide", "t2", "d", "t3")
+    p.op("fsigmoid", "t3", "out")
+    p.outputs = ["out"]
+    return p
+
+
+def _logloss_sigmoid_backward(p, P, Y, ones, dZ, tag):
+    """dZ = dL/dP * dP/dZ with the reference's derivative chains:
+    LogLoss' = (p - y) / (p - p*p)   (LogLossOperationInternal.cpp:127-170)
+    Sigmoid' = (1 - p) * p           (SigmoidOperationInternal.cpp:107-135)."""
+    shape = p.tensors[P]
+    t = lambda s: p.tensor(f"{tag}_{s}", *shape)
+    p.op("fadd", P, 1.0, Y, -1.0, t("pmy"))
+    p.op("fmul", P, P, t("pp"))
+    p.op("fadd", P, 1.0, f"{tag}_pp", -1.0, t("den"))
+    p.op("fdivide", f"{tag}_pmy", f"{tag}_den", t("dLdP"))
+    p.op("fadd", ones, 1.0, P, -1.0, t("omp"))
+    p.op("fmul", f"{tag}_omp", P, t("sp"))
+    p.op("fmul", f"{tag}_dLdP", f"{tag}_sp", dZ)
+
+
+def logreg_program(batch=256, n_in=784, lr=0.1):
+    """Logistic-regression step: MatMul -> Sigmoid -> LogLoss, batch gradient,
+    one SGD update W <- W - lr * X^T dZ."""
+    p = Program("logreg_step")
+    p.tensor("X", batch, n_in), p.tensor("W", n_in, 1), p.tensor("Y", batch, 1)
+    p.inputs = ["X", "W", "Y"]
+    p.tensor("ones", batch, 1)
+    p.constants["ones"] = 1.0
+    p.tensor("Z", batch, 1), p.tensor("P", batch, 1), p.tensor("L", batch, 1)
+    p.tensor("dZ", batch, 1), p.tensor("dW", n_in, 1)
+    p.op("fmatmul_f_f", "X", "W", "Z")
+    p.op("fsigmoid", "Z", "P")
+    p.op("flogloss", "P", "Y", "L")
+    _logloss_sigmoid_backward(p, "P", "Y", "ones", "dZ", "b")
+    p.op("fmatmul_t_f", "X", "dZ", "dW")
+    p.op("ALLREDUCE", "dW")
+    p.op("fadd", "W", 1.0, "dW", -lr, "W")
+    p.outputs = ["L", "W", "dW"]
+    return p
+
+
+def mlp_program(batch, n_in=784, n_hidden=4096, n_out=10, lr=0.1):
+    """2-layer MLP forward + backward + SGD update on `batch` rows (the rows one
+    rank holds).  No biases (the reference has no broadcasting add); gradients are
+    batch sums (it has no mean)."""
+    p = Program("mlp_step")
+    p.tensor("X", batch, n_in), p.tensor("Y", batch, n_out)
+    p.tensor("W1", n_in, n_hidden), p.tensor("W2", n_hidden, n_out)
+    p.inputs = ["X", "Y", "W1", "W2"]
+    p.tensor("ones_h", batch, n_hidden), p.tensor("ones_o", batch, n_out)
+    p.constants = {"ones_h": 1.0, "ones_o": 1.0}
+    for t in ("Z1", "H", "dH", "omh", "sh", "dZ1"):
+        p.tensor(t, batch, n_hidden)
+    for t in ("Z2", "P", "L", "dZ2"):
+        p.tensor(t, batch, n_out)
+    p.tensor("dW1", n_in, n_hidden), p.tensor("dW2", n_hidden, n_out)
+    # forward
+    p.op("fmatmul_f_f", "X", "W1", "Z1")
+    p.op("fsigmoid", "Z1", "H")
+    p.op("fmatmul_f_f", "H", "W2", "Z2")
+    p.op("fsigmoid", "Z2", "P")
+    p.op("flogloss", "P", "Y", "L")
+    # backward
+    _logloss_sigmoid_backward(p, "P", "Y", "ones_o", "dZ2", "o")
+    p.op("fmatmul_t_f", "H", "dZ2", "dW2")
+    p.op("ALLREDUCE", "dW2")
+    p.op("fmatmul_f_t", "dZ2", "W2", "dH")
+    p.op("fadd", "ones_h", 1.0, "H", -1.0, "omh")
+    p.op("fmul", "omh", "H", "sh")
+    p.op("fmul", "dH", "sh", "dZ1")
+    p.op("fmatmul_t_f", "X", "dZ1", "dW1")
+    p.op("ALLREDUCE", "dW1")
+    # update
+    p.op("fadd", "W2", 1.0, "dW2", -lr, "W2")
+    p.op("fadd", "W1", 1.0, "dW1", -lr, "W1")
+    p.outputs = ["L", "W1", "W2", "dW1", "dW2"]
+    return p
+
+
+class DeviceExecutor:
+    """Runs a Program on one GPU: one device tensor per program tensor, every op
+    through polar_b200_launch_by_name on torch's current stream.  Argument
+    structs are built once, so replaying the program costs one ctypes call per
+    launch.  `allreduce` is a callable taking a tensor (torch.distributed over
+    NCCL in the data-parallel runs; None = single rank, no-op)."""
+
+    def __init__(self, program, device="cuda:0", allreduce=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: programs have no CPU path in this package")
+        self.program = program
+        self.device = torch.device(device)
+        self.lib = lib()
+        self.allreduce = allreduce
+        self.t = {n: torch.empty(s, dtype=torch.float32, device=self.device)
+                  for n, s in program.tensors.items()}
+        self._keep = []
+        self._compiled = []
+        fn = self.lib.cdll.polar_b200_launch_by_name
+        for kernel, args in program.ops:
+            if kernel == "ALLREDUCE":
+                self._compiled.append((None, args[0], 0))
+                continue
+            arr = (Arg * len(args))()
+            for i, a in enumerate(args):
+                if isinstance(a, str):
+                    tt = self.t[a]
+                    shp = (ctypes.c_uint64 * tt.dim())(*tt.shape)
+                    self._keep.append(shp)
+                    arr[i].is_tensor = 1
+                    arr[i].tensor.data = tt.data_ptr()
+                    arr[i].tensor.dims = tt.dim()
+                    arr[i].tensor.shape = shp
+                else:
+                    arr[i].is_tensor = 0
+                    arr[i].scalar = float(a)
+            self._keep.append(arr)
+            self._compiled.append((kernel.encode(), arr, len(args)))
+        self._fn = fn
+        self.fill_constants()
+
+    def fill_constants(self):
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        for name, value in self.program.constants.items():
+            self.lib.call("polar_b200_ffill", float(value), self.t[name].data_ptr(), self.t[name].numel(), s)
+
+    def set_inputs(self, **arrays):
+        for name, a in arrays.items():
+            self.t[name].copy_(a if isinstance(a, torch.Tensor) else torch.from_numpy(a))
+
+    def run(self):
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        for kernel, arr, n in self._compiled:
+            if kernel is None:
+                if self.allreduce is not None:
+                    self.allreduce(self.t[arr])
+                continue
+            rc = self._fn(kernel, arr, n, None, 0, s)
+            if rc != 0:
+                self.lib.check(rc)
+
+    def output(self, name):
+        torch.cuda.synchronize(self.device)
+        return self.t[name].cpu().numpy()

@@ -67,3 +67,16 @@ def test_matmul_path_selection(library):
     assert c.polar_b200_fmatmul_path(1, 0, 784, 4096, 65536) == 0
     assert c.polar_b200_fmatmul_path(0, 0, 65536, 10, 4096) != 0      # row pitch 40 B: no TMA
     assert c.polar_b200_fmatmul_path(0, 0, 256, 1, 784) != 0
+
+
+def test_runtime_plugin_exports_and_opens_without_a_gpu(library):
+    from polarai_framework_b200 import runtime
+    cdll = runtime.load_rt_library()           # resolves every declared symbol + initContext/closeContext
+    assert sorted(runtime.RT_SIGNATURES) == declared("polar_b200_rt.h")
+    import torch
+    if not torch.cuda.is_available():
+        rt = runtime.Runtime()
+        assert rt.device_count() == 0          # no sm_100 device: an empty context, not a crash
+        with pytest.raises(Exception):
+            rt.tensor((4,))
+        rt.close()

@@ -1,0 +1,165 @@
+"""GPU parity of fmatmul (all four transpose forms) against the CPU oracle.
+
+Error metric: |c - ref| / sum_k |a||b| with ref accumulated in double; the bound
+is 1e-4 (the fp32-sequential reference order itself lies within it).  Small
+integer cases are bit-exact."""
+import numpy as np
+import pytest
+
+from conftest import expected_of, run_kat
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import __graft_entry__ as ge
+    ge.load_package()
+    from polarai_framework_b200.device_builtins import HostBuiltins
+    return HostBuiltins("cuda:0")
+
+
+@pytest.fixture(scope="module")
+def par_oracle():
+    from oracle import oracle as orc
+    o = orc.Oracle()
+    o.set_threads(o.max_threads())
+    return o
+
+
+def operands(rng, tl, tr, m, n, k):
+    left = rng.uniform(-1, 1, (k, m) if tl else (m, k)).astype(np.float32)
+    right = rng.uniform(-1, 1, (n, k) if tr else (k, n)).astype(np.float32)
+    return left, right
+
+
+def rel_err(got, ref, mag):
+    return float(np.max(np.abs(got.astype(np.float64) - ref) / mag))
+
+
+def test_reference_kats_bit_exact(gpu, kats):
+    for case in kats:
+        if case["builtin"] != "fmatmul":
+            continue
+        got = run_kat(gpu, case)
+        assert np.array_equal(got.ravel(), expected_of(case)), case["name"]
+
+
+@pytest.mark.parametrize("tl", [0, 1])
+@pytest.mark.parametrize("tr", [0, 1])
+def test_seeded_fixture(gpu, seeded, par_oracle, tl, tr):
+    tag = f"mm_{'t' if tl else 'f'}_{'t' if tr else 'f'}"
+    l, r = seeded[tag + "_left"], seeded[tag + "_right"]
+    ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
+    for which in ("auto", "ffma"):
+        assert rel_err(gpu.fmatmul(tl, tr, l, r, which=which), ref, mag) <= TOL
+    assert rel_err(seeded[tag + "_out"], ref, mag) <= TOL
+
+
+SHAPES = [
+    (128, 256, 32), (128, 128, 64), (64, 32, 32),          # one tile, one or two slabs
+    (200, 300, 100), (260, 516, 36), (1000, 40, 2000),      # ragged m/n/k tails (multiples of 4)
+    (512, 512, 512), (256, 784, 128), (784, 128, 256),      # sizes from the logistic-regression / MLP configs
+    (1024, 1024, 1024),
+]
+
+
+@pytest.mark.parametrize("tl", [0, 1])
+@pytest.mark.parametrize("tr", [0, 1])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tensor_core_path(gpu, par_oracle, tl, tr, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(m * 7 + n * 3 + k + tl * 2 + tr)
+    l, r = operands(rng, tl, tr, m, n, k)
+    ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
+    got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=256)
+    assert rel_err(got, ref, mag) <= TOL
+    assert rel_err(got, ref, mag) <= 5e-6          # what the three-product split actually delivers
+    got128 = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=128)
+    assert rel_err(got128, ref, mag) <= 5e-6
+    auto = gpu.fmatmul(tl, tr, l, r)
+    assert rel_err(auto, ref, mag) <= TOL
+    assert gpu.d.device_status() == 0
+
+
+@pytest.mark.parametrize("tl,tr,m,n,k", [
+    (0, 0, 256, 1, 784),      # logistic regression forward
+    (1, 0, 784, 1, 256),      # X^T dZ
+    (0, 0, 1024, 10, 4096),   # hidden -> 10 outputs
+    (1, 0, 4096, 10, 1024),   # H^T dZ2
+    (0, 1, 1024, 4096, 10),   # dZ2 W2^T
+    (0, 0, 33, 17, 5), (1, 1, 7, 9, 1027), (0, 1, 1, 1, 1),
+])
+def test_shapes_tma_cannot_describe(gpu, par_oracle, tl, tr, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    l, r = operands(rng, tl, tr, m, n, k)
+    ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
+    assert rel_err(gpu.fmatmul(tl, tr, l, r), ref, mag) <= TOL
+
+
+def test_empty_dimensions(gpu):
+    assert gpu.fmatmul(0, 0, np.empty((0, 8), np.float32), np.empty((8, 4), np.float32)).shape == (0, 4)
+    out = gpu.fmatmul(0, 0, np.empty((3, 0), np.float32), np.empty((0, 4), np.float32))
+    assert np.array_equal(out, np.zeros((3, 4), np.float32))
+
+
+def test_plain_tf32_is_not_enough(gpu, par_oracle):
+    # the single-product mode misses the tolerance the split meets: the split is needed
+    rng = np.random.default_rng(9)
+    l, r = operands(rng, 0, 1, 256, 256, 1024)
+    ref, mag = par_oracle.fmatmul_f64(0, 1, l, r)
+    e1 = rel_err(gpu.fmatmul(0, 1, l, r, which="tc", passes=1), ref, mag)
+    e3 = rel_err(gpu.fmatmul(0, 1, l, r, which="tc", passes=3), ref, mag)
+    assert e1 > 2e-5 and e3 < 5e-6
+
+
+@pytest.mark.parametrize("tl,tr", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_large_sampled_against_f64(gpu, par_oracle, tl, tr):
+    # 4096^3 and the skinny 65536 x 784 x 1024 case: sampled entries, full rows and columns
+    import torch
+    for (m, n, k) in ((4096, 4096, 4096), (65536, 1024, 784)):
+        torch.manual_seed(m + tl * 2 + tr)
+        L = torch.empty((k, m) if tl else (m, k), device="cuda").uniform_(-1, 1)
+        R = torch.empty((n, k) if tr else (k, n), device="cuda").uniform_(-1, 1)
+        out = torch.empty((m, n), device="cuda")
+        gpu.d.fmatmul(tl, tr, L, R, out)
+        torch.cuda.synchronize()
+        assert gpu.d.device_status() == 0
+        l, r, got = L.cpu().numpy(), R.cpu().numpy(), out.cpu().numpy()
+        rng = np.random.default_rng(1)
+        rows = rng.integers(0, m, 4096).astype(np.uint64)
+        cols = rng.integers(0, n, 4096).astype(np.uint64)
+        # plus 8 full rows and 8 full columns, first/last included
+        fr = np.array([0, m - 1] + list(rng.integers(0, m, 6)), np.uint64)
+        fc = np.array([0, n - 1] + list(rng.integers(0, n, 6)), np.uint64)
+        rows = np.concatenate([rows, np.repeat(fr, n), np.tile(np.arange(m, dtype=np.uint64), 8)])
+        cols = np.concatenate([cols, np.tile(np.arange(n, dtype=np.uint64), 8), np.repeat(fc, m)])
+        ref, mag = par_oracle.fmatmul_entries_f64(tl, tr, l, r, rows, cols)
+        g = got[rows.astype(np.int64), cols.astype(np.int64)].astype(np.float64)
+        assert float(np.max(np.abs(g - ref) / mag)) <= TOL
+
+
+def test_linearity_at_8192(gpu):
+    # full-size property check: (A1 + A2) B == A1 B + A2 B within the tolerance, and the
+    # tensor-core result agrees with the FFMA kernel on a strip of rows
+    import torch
+    d = gpu.d
+    n = 8192
+    torch.manual_seed(0)
+    A1 = torch.empty((n, n), device="cuda").uniform_(-1, 1)
+    A2 = torch.empty((n, n), device="cuda").uniform_(-1, 1)
+    B = torch.empty((n, n), device="cuda").uniform_(-1, 1)
+    C1, C2, C12 = (torch.empty((n, n), device="cuda") for _ in range(3))
+    d.fmatmul(0, 0, A1, B, C1)
+    d.fmatmul(0, 0, A2, B, C2)
+    d.fmatmul(0, 0, A1 + A2, B, C12)
+    torch.cuda.synchronize()
+    scale = float(n) * 0.25 * 2                     # E|a||b| summed over k, both terms
+    assert float((C12 - (C1 + C2)).abs().max()) / scale <= TOL
+    strip = torch.empty((256, n), device="cuda")
+    d.fmatmul_ffma(0, 0, A1[:256].contiguous(), B, strip)
+    torch.cuda.synchronize()
+    assert float((strip - C1[:256]).abs().max()) / (n * 0.25) <= TOL
+    assert d.device_status() == 0
