@@ -65,7 +65,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -208,7 +208,7 @@ def per_op_times(torch, ex, reps):
                 if ex.allreduce is not None:
                     ex.allreduce(ex.t[arr])
             else:
-                ex.lib.check(ex._fn(kernel, arr, n, None, 0, s))
+                ex.lib.check(ex._fn(kernel, arr, n, ex._ws_ptr, ex._ws_bytes, s))
             b.record()
             evs.append((a, b))
         torch.cuda.synchronize()

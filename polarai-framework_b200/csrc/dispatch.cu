@@ -10,6 +10,11 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
               const float* right, float* out, int bn, int passes, int write_hi, cudaStream_t stream);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
+int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                const float* right, const float* out);
+uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k);
+int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                  const float* right, float* out, float* ws, cudaStream_t st);
 int tc_status_word();
 void tc_status_clear();
 
@@ -21,7 +26,8 @@ enum Path { kPathTc = 0, kPathSkinny = 1, kPathFfma = 2 };
 // output dimension, or with a k extent shorter than a slab, the CUDA-core
 // kernel does less wasted work.
 int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                const float* right) {
+                const float* right, const float* out) {
+  if (skinny_kind(tl, tr, m, n, k, left, right, out)) return kPathSkinny;
   if (tc_shape_ok(tl, tr, m, n, k, left, right) && m >= 64 && n >= 32 && k >= 32) return kPathTc;
   return kPathFfma;
 }
@@ -44,25 +50,48 @@ using namespace polar_b200;
 
 extern "C" {
 
-uint64_t polar_b200_fmatmul_workspace_bytes(int, int, uint64_t, uint64_t, uint64_t) { return 0; }
+uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
+  const float* al = reinterpret_cast<const float*>(256);
+  int kind = skinny_kind(tl, tr, m, n, k, al, al, al);
+  return kind ? skinny_workspace_bytes(kind, m, n, k) : 0;
+}
 
 int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
   // Alignment of the operands is assumed (allocator buffers are 256-byte aligned).
-  return choose_path(tl, tr, m, n, k, reinterpret_cast<const float*>(256), reinterpret_cast<const float*>(256));
+  const float* al = reinterpret_cast<const float*>(256);
+  return choose_path(tl, tr, m, n, k, al, al, al);
 }
 
 int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                        const float* right, float* out, void* workspace, uint64_t workspace_bytes,
                        void* stream) {
-  (void)workspace; (void)workspace_bytes;
   clear_error();
   int rc = check_mm(tl, tr, m, n, k, left, right, out);
   if (rc) return rc;
   if (m == 0 || n == 0) return POLAR_B200_OK;
   if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);  // empty sum
-  switch (choose_path(tl, tr, m, n, k, left, right)) {
+  switch (choose_path(tl, tr, m, n, k, left, right, out)) {
     case kPathTc:
       return launch_tc(tl, tr, m, n, k, left, right, out, 256, 3, 0, as_stream(stream));
+    case kPathSkinny: {
+      const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
+      const uint64_t need = skinny_workspace_bytes(kind, m, n, k);
+      if (need == 0) return launch_skinny(kind, tl, tr, m, n, k, left, right, out, nullptr, as_stream(stream));
+      if (workspace) {
+        if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+          return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
+        return launch_skinny(kind, tl, tr, m, n, k, left, right, out, static_cast<float*>(workspace),
+                             as_stream(stream));
+      }
+      // No workspace from the caller: take it from the stream-ordered pool.
+      void* ws = nullptr;
+      cudaError_t e = cudaMallocAsync(&ws, need, as_stream(stream));
+      if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+      rc = launch_skinny(kind, tl, tr, m, n, k, left, right, out, static_cast<float*>(ws), as_stream(stream));
+      e = cudaFreeAsync(ws, as_stream(stream));
+      if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+      return rc;
+    }
     default:
       return launch_ffma(tl, tr, m, n, k, left, right, out, as_stream(stream));
   }

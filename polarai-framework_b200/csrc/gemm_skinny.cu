@@ -1,0 +1,346 @@
+// fmatmul for shapes with one tiny dimension - the MLP's 10-wide output layer and
+// the logistic regression's single column.  A 128 x 256 tensor-core tile would be
+// more than 90 % padding there, and the work is bound by streaming the one large
+// operand (or the large result) through HBM once, so these run on the CUDA cores
+// with 128-bit coalesced accesses of the large matrix and the small one in shared
+// memory or registers.
+//
+//   small_n, left K-contiguous  (left stored [m,k]):   C[m, n<=16] = L . R
+//       one warp per group of 4 rows; lanes walk k four floats at a time; the
+//       k-slab of R sits transposed in shared memory; warp-shuffle reduction.
+//   small_n, left M-contiguous  (left stored [k,m]):   C[m, n<=16] = L^T . R
+//       the sum runs over the long (batch) dimension: the k range is split over
+//       CTAs, each thread owns 4 consecutive m and n accumulators each, partial
+//       sums go to scratch memory [split][m][n] and a second kernel adds the
+//       splits in a fixed order (deterministic; no atomics).
+//   small_k (k <= 16):                                  C[m,n] = L . R, result-bound
+//       each thread keeps its 4 columns of R in registers and streams rows.
+//
+// Accumulation is fp32 with fmaf; the order of the k sum differs from the
+// reference's sequential order, within the fp32 tolerance used for fmatmul.
+#include "common.cuh"
+
+namespace polar_b200 {
+namespace skinny {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------- small n, K-major left
+
+constexpr int KT = 1024;          // k-slab staged in shared memory
+constexpr int KT_PAD = KT + 4;    // keeps float4 alignment, staggers banks between columns
+constexpr int ROWS_PER_WARP = 4;
+
+template <int NP>
+__global__ void __launch_bounds__(kThreads)
+small_n_kmajor_kernel(const float* __restrict__ left, const float* __restrict__ right,
+                      float* __restrict__ out, uint64_t m, uint64_t n, uint64_t k, uint64_t rsk,
+                      uint64_t rsj) {
+  extern __shared__ float bs[];   // [NP][KT_PAD], k contiguous
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t rows_per_cta = (kThreads / 32) * ROWS_PER_WARP;
+  const uint64_t row0 = (uint64_t)blockIdx.x * rows_per_cta + (uint64_t)warp * ROWS_PER_WARP;
+  float acc[ROWS_PER_WARP][NP];
+#pragma unroll
+  for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+    for (int j = 0; j < NP; ++j) acc[r][j] = 0.f;
+
+  for (uint64_t k0 = 0; k0 < k; k0 += KT) {
+    const int kt = (int)((k - k0 < KT) ? (k - k0) : KT);
+    __syncthreads();
+    for (int e = threadIdx.x; e < NP * KT; e += kThreads) {
+      int j = e % NP, kk = e / NP;
+      float v = 0.f;
+      if (kk < kt && (uint64_t)j < n) v = right[(k0 + kk) * rsk + (uint64_t)j * rsj];
+      bs[j * KT_PAD + kk] = v;
+    }
+    __syncthreads();
+    for (int kk = lane * 4; kk < kt; kk += 128) {   // k is a multiple of 4: no ragged vector
+      float4 a[ROWS_PER_WARP];
+#pragma unroll
+      for (int r = 0; r < ROWS_PER_WARP; ++r) {
+        uint64_t row = row0 + r;
+        a[r] = row < m ? __ldcs(reinterpret_cast<const float4*>(left + row * k + k0 + kk))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        float4 b = *reinterpret_cast<const float4*>(&bs[j * KT_PAD + kk]);
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_WARP; ++r) {
+          acc[r][j] = fmaf(a[r].x, b.x, acc[r][j]);
+          acc[r][j] = fmaf(a[r].y, b.y, acc[r][j]);
+          acc[r][j] = fmaf(a[r].z, b.z, acc[r][j]);
+          acc[r][j] = fmaf(a[r].w, b.w, acc[r][j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < ROWS_PER_WARP; ++r) {
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      float v = acc[r][j];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      acc[r][j] = v;
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < ROWS_PER_WARP; ++r) {
+      uint64_t row = row0 + r;
+      if (row < m)
+#pragma unroll
+        for (int j = 0; j < NP; ++j)
+          if ((uint64_t)j < n) out[row * n + j] = acc[r][j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- small n, MN-major left (split k)
+
+constexpr int KS = 128;   // rows of R staged per pass
+
+template <int NP>
+__global__ void __launch_bounds__(kThreads)
+small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__ right,
+                       float* __restrict__ partial, uint64_t m, uint64_t n, uint64_t k, uint64_t rsk,
+                       uint64_t rsj, uint64_t k_per_split) {
+  __shared__ float bs[KS][NP];
+  const uint64_t m0 = ((uint64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
+  const uint64_t kbeg = (uint64_t)blockIdx.y * k_per_split;
+  const uint64_t kend = (kbeg + k_per_split < k) ? kbeg + k_per_split : k;
+  float acc[4][NP];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < NP; ++j) acc[i][j] = 0.f;
+  const bool live = m0 < m;   // m is a multiple of 4
+  for (uint64_t k0 = kbeg; k0 < kend; k0 += KS) {
+    const int ks = (int)((kend - k0 < KS) ? (kend - k0) : KS);
+    __syncthreads();
+    for (int e = threadIdx.x; e < KS * NP; e += kThreads) {
+      int j = e % NP, kk = e / NP;
+      float v = 0.f;
+      if (kk < ks && (uint64_t)j < n) v = right[(k0 + kk) * rsk + (uint64_t)j * rsj];
+      bs[kk][j] = v;
+    }
+    __syncthreads();
+    if (live) {
+      int kk = 0;
+      for (; kk + 4 <= ks; kk += 4) {
+        float4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          a[u] = __ldcs(reinterpret_cast<const float4*>(left + (k0 + kk + u) * m + m0));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int j = 0; j < NP; ++j) {
+            float b = bs[kk + u][j];
+            acc[0][j] = fmaf(a[u].x, b, acc[0][j]);
+            acc[1][j] = fmaf(a[u].y, b, acc[1][j]);
+            acc[2][j] = fmaf(a[u].z, b, acc[2][j]);
+            acc[3][j] = fmaf(a[u].w, b, acc[3][j]);
+          }
+      }
+      for (; kk < ks; ++kk) {
+        float4 a = __ldcs(reinterpret_cast<const float4*>(left + (k0 + kk) * m + m0));
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+          float b = bs[kk][j];
+          acc[0][j] = fmaf(a.x, b, acc[0][j]);
+          acc[1][j] = fmaf(a.y, b, acc[1][j]);
+          acc[2][j] = fmaf(a.z, b, acc[2][j]);
+          acc[3][j] = fmaf(a.w, b, acc[3][j]);
+        }
+      }
+    }
+  }
+  if (live) {
+    float* dst = partial + ((uint64_t)blockIdx.y * m + m0) * n;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NP; ++j)
+        if ((uint64_t)j < n) dst[(uint64_t)i * n + j] = acc[i][j];
+  }
+}
+
+// out[e] = sum over splits, ascending split index: a fixed order.
+__global__ void __launch_bounds__(kThreads)
+reduce_splits_kernel(const float* __restrict__ partial, float* __restrict__ out, uint64_t elems,
+                     uint32_t splits) {
+  const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+  for (uint64_t e = (uint64_t)blockIdx.x * kThreads + threadIdx.x; e < elems; e += stride) {
+    float s = 0.f;
+    for (uint32_t sp = 0; sp < splits; ++sp) s += partial[(uint64_t)sp * elems + e];
+    out[e] = s;
+  }
+}
+
+// ---------------------------------------------------------------- small k
+
+constexpr int RK = 64;   // rows of the left operand staged per CTA
+
+// L'(i,kk) = left[i*lsi + kk*lsk]; R'(kk,j) = right[kk*rsk + j*rsj]; k <= KP.
+template <int KP>
+__global__ void __launch_bounds__(kThreads)
+small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, float* __restrict__ out,
+               uint64_t m, uint64_t n, uint64_t k, uint64_t lsi, uint64_t lsk, uint64_t rsk,
+               uint64_t rsj, int vec_store) {
+  __shared__ float as[RK][KP];
+  const uint64_t j0 = ((uint64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
+  const uint64_t row0 = (uint64_t)blockIdx.y * RK;
+  const int rows = (int)((m - row0 < RK) ? (m - row0) : RK);
+  for (int e = threadIdx.x; e < RK * KP; e += kThreads) {
+    int kk = e % KP, r = e / KP;
+    float v = 0.f;
+    if (r < rows && (uint64_t)kk < k) v = left[(row0 + r) * lsi + (uint64_t)kk * lsk];
+    as[r][kk] = v;
+  }
+  float b[4][KP];
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int kk = 0; kk < KP; ++kk)
+      b[c][kk] = (j0 + c < n && (uint64_t)kk < k) ? right[(uint64_t)kk * rsk + (j0 + c) * rsj] : 0.f;
+  __syncthreads();
+  if (j0 >= n) return;
+  for (int r = 0; r < rows; ++r) {
+    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KP; ++kk) {
+      float a = as[r][kk];
+      c0 = fmaf(a, b[0][kk], c0);
+      c1 = fmaf(a, b[1][kk], c1);
+      c2 = fmaf(a, b[2][kk], c2);
+      c3 = fmaf(a, b[3][kk], c3);
+    }
+    float* dst = out + (row0 + r) * n + j0;
+    if (vec_store && j0 + 4 <= n) {
+      __stcs(reinterpret_cast<float4*>(dst), make_float4(c0, c1, c2, c3));
+    } else {
+      dst[0] = c0;
+      if (j0 + 1 < n) dst[1] = c1;
+      if (j0 + 2 < n) dst[2] = c2;
+      if (j0 + 3 < n) dst[3] = c3;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- host side
+
+inline int round_np(uint64_t n) { return n <= 1 ? 1 : n <= 2 ? 2 : n <= 4 ? 4 : n <= 8 ? 8 : n <= 10 ? 10 : 16; }
+
+uint32_t splits_for(uint64_t m, uint64_t k) {
+  uint64_t m_blocks = (m / 4 + kThreads - 1) / kThreads;
+  uint64_t want = ((uint64_t)sm_count() * 2 + m_blocks - 1) / m_blocks;   // about two CTAs per SM
+  uint64_t max_by_k = (k + KS - 1) / KS;
+  uint64_t s = want < max_by_k ? want : max_by_k;
+  if (s < 1) s = 1;
+  if (s > 4096) s = 4096;
+  return (uint32_t)s;
+}
+
+template <int NP>
+int launch_small_n_k(const float* l, const float* r, float* out, uint64_t m, uint64_t n, uint64_t k,
+                     uint64_t rsk, uint64_t rsj, cudaStream_t st) {
+  const size_t smem = (size_t)NP * KT_PAD * sizeof(float);
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(small_n_kmajor_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(small_n)", e);
+    attr_done[dev] = true;
+  }
+  uint64_t rows_per_cta = (kThreads / 32) * ROWS_PER_WARP;
+  uint64_t grid = (m + rows_per_cta - 1) / rows_per_cta;
+  if (grid > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many rows");
+  small_n_kmajor_kernel<NP><<<(unsigned)grid, kThreads, smem, st>>>(l, r, out, m, n, k, rsk, rsj);
+  return check_launch("fmatmul_small_n");
+}
+
+template <int NP>
+int launch_small_n_mn(const float* l, const float* r, float* out, float* ws, uint32_t splits, uint64_t m,
+                      uint64_t n, uint64_t k, uint64_t rsk, uint64_t rsj, cudaStream_t st) {
+  uint64_t m_blocks = (m / 4 + kThreads - 1) / kThreads;
+  uint64_t k_per_split = (k + splits - 1) / splits;
+  k_per_split = (k_per_split + 3) & ~3ull;
+  dim3 grid((unsigned)m_blocks, splits);
+  float* dst = splits > 1 ? ws : out;
+  small_n_mnmajor_kernel<NP><<<grid, kThreads, 0, st>>>(l, r, dst, m, n, k, rsk, rsj, k_per_split);
+  int rc = check_launch("fmatmul_small_n_split");
+  if (rc || splits == 1) return rc;
+  uint64_t elems = m * n;
+  uint64_t g = (elems + kThreads - 1) / kThreads;
+  uint64_t cap = (uint64_t)sm_count() * 4;
+  reduce_splits_kernel<<<(unsigned)(g < cap ? g : cap), kThreads, 0, st>>>(ws, out, elems, splits);
+  return check_launch("fmatmul_reduce_splits");
+}
+
+}  // namespace skinny
+
+// Which skinny kernel, if any, serves this shape: 1 = small n with K-major left,
+// 2 = small n with MN-major left (needs scratch), 3 = small k, 0 = none.
+int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                const float* right, const float* out) {
+  (void)tr; (void)right;
+  if (n <= 16 && k >= 32) {
+    if (!tl && (k & 3) == 0 && aligned16(left)) return 1;
+    if (tl && (m & 3) == 0 && aligned16(left)) return 2;
+  }
+  if (k <= 16 && n >= 32) return 3;
+  (void)out;
+  return 0;
+}
+
+uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k) {
+  if (kind != 2) return 0;
+  uint32_t s = skinny::splits_for(m, k);
+  return s > 1 ? (uint64_t)s * m * n * sizeof(float) : 0;
+}
+
+int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                  const float* right, float* out, float* ws, cudaStream_t st) {
+  using namespace skinny;
+  const uint64_t rsk = tr ? 1 : n, rsj = tr ? k : 1;
+  if (kind == 1 || kind == 2) {
+    const int np = round_np(n);
+    const uint32_t splits = kind == 2 ? splits_for(m, k) : 1;
+#define POLAR_SKINNY_N(NP)                                                                   \
+  case NP:                                                                                   \
+    return kind == 1 ? launch_small_n_k<NP>(left, right, out, m, n, k, rsk, rsj, st)          \
+                     : launch_small_n_mn<NP>(left, right, out, ws, splits, m, n, k, rsk, rsj, st);
+    switch (np) {
+      POLAR_SKINNY_N(1)
+      POLAR_SKINNY_N(2)
+      POLAR_SKINNY_N(4)
+      POLAR_SKINNY_N(8)
+      POLAR_SKINNY_N(10)
+      POLAR_SKINNY_N(16)
+    }
+#undef POLAR_SKINNY_N
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "skinny matmul: unsupported n");
+  }
+  // small k
+  const uint64_t lsi = tl ? 1 : k, lsk = tl ? m : 1;
+  uint64_t gx = ((n + 3) / 4 + kThreads - 1) / kThreads, gy = (m + RK - 1) / RK;
+  if (gy > 65535) {
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "skinny matmul: more than 65535 row blocks");
+  }
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  int vec = ((n & 3) == 0) && aligned16(out);
+  if (k <= 4)
+    small_k_kernel<4><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec);
+  else if (k <= 10)
+    small_k_kernel<10><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec);
+  else
+    small_k_kernel<16><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec);
+  return check_launch("fmatmul_small_k");
+}
+
+}  // namespace polar_b200

@@ -119,6 +119,8 @@ public:
   int ordinal() const { return mOrdinal; }
   cudaStream_t stream() const { return mStream; }
   int lastStatus() const { return mLastStatus; }
+  // Returns the last error status and clears it, so that one failure is reported once.
+  int takeStatus() { int s = mLastStatus; mLastStatus = 0; return s; }
   const std::string& lastError() const { return mLastError; }
   void synchronize() const;
   cudaEvent_t takeEvent();

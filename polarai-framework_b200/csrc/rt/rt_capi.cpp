@@ -113,7 +113,7 @@ int polar_b200_rt_read(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void* dst
   rt->allocator->release(rec);
   for (auto& d : rt->devices) {
     auto* bd = static_cast<B200Device*>(d.get());
-    if (bd->lastStatus()) return fail(rt, bd->lastStatus(), bd->lastError());
+    if (int s = bd->takeStatus()) return fail(rt, s, bd->lastError());
   }
   return POLAR_B200_OK;
 }
@@ -153,7 +153,10 @@ int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cm
   }
   Event* evt = d->launch(*rt->allocator, *cmd, nullptr);
   int status = static_cast<B200Event*>(evt)->status();
-  if (status) rt->error = d->lastError();
+  if (status) {
+    rt->error = d->lastError();
+    d->takeStatus();   // reported here
+  }
   // Stream order protects the buffers; the locks can go as soon as the work is queued.
   unlock_all();
   delete evt;
@@ -164,7 +167,7 @@ int polar_b200_rt_barrier(polar_b200_rt* rt, int device) {
   B200Device* d = dev(rt, device);
   if (!d) return fail(rt, POLAR_B200_ERR_INVALID, "no such device");
   d->synchronize();
-  if (d->lastStatus()) return fail(rt, d->lastStatus(), d->lastError());
+  if (int s = d->takeStatus()) return fail(rt, s, d->lastError());
   return POLAR_B200_OK;
 }
 

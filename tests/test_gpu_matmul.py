@@ -91,6 +91,10 @@ def test_tensor_core_path(gpu, par_oracle, tl, tr, shape):
     (1, 0, 4096, 10, 1024),   # H^T dZ2
     (0, 1, 1024, 4096, 10),   # dZ2 W2^T
     (0, 0, 33, 17, 5), (1, 1, 7, 9, 1027), (0, 1, 1, 1, 1),
+    # one tiny dimension: the bandwidth-bound CUDA-core kernels
+    (0, 0, 1000, 3, 512), (0, 1, 1000, 16, 260), (0, 0, 5, 10, 4096), (0, 0, 4099, 10, 2052),
+    (1, 0, 1028, 5, 1000), (1, 1, 516, 2, 300), (1, 0, 4096, 10, 30000), (1, 0, 4, 1, 33),
+    (0, 0, 100, 300, 16), (1, 1, 100, 302, 7), (1, 0, 64, 4096, 4), (0, 1, 70000, 64, 10),
 ])
 def test_shapes_tma_cannot_describe(gpu, par_oracle, tl, tr, m, n, k):
     rng = np.random.default_rng(m + n + k)
