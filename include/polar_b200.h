@@ -119,6 +119,38 @@ int polar_b200_fmatmul(int transLeft, int transRight, uint64_t m, uint64_t n,
 uint64_t polar_b200_fmatmul_workspace_bytes(int transLeft, int transRight,
                                             uint64_t m, uint64_t n, uint64_t k);
 
+/* fmatmul_t_f / fmatmul_t_t for a narrow result, without any allocation.
+ * No counterpart in the reference: it exists for hosts that cannot call
+ * cudaMalloc while they run - an application that has already handed all device
+ * memory to its own allocator (any further cudaMalloc or pool growth fails), or
+ * one on a path where the device-wide synchronisation of cudaMalloc/cudaFree is
+ * not acceptable.  polar_b200_fmatmul needs scratch memory for this shape (the
+ * sum over the long k dimension is split over CTAs) and takes it from the caller
+ * or from the stream-ordered pool; this variant computes the same product,
+ *     out[m,n] = sum_k left[k,m] * R'[k,n]      (left stored [k,m]; right stored
+ *                                                [k,n], or [n,k] when transRight)
+ * with the partial sums in an array that is part of the library image
+ * (polar_b200_static_scratch_bytes() = 16 MiB, held by every GPU that loads the
+ * library until the process exits).  The caller still owns left, right and out.
+ *  - Shapes: n <= 16, k >= 32, m a multiple of 4, left 16-byte aligned; the
+ *    scratch needed is splits*m*n*4 bytes with splits about 2*SMs/ceil(m/1024)
+ *    (12 MiB for m=4096, n=10).  A product that needs more returns
+ *    POLAR_B200_ERR_WORKSPACE; other shapes return POLAR_B200_ERR_UNSUPPORTED.
+ *  - The first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    outside any stream capture.
+ *  - All calls share the one array per device and it keeps the last call's
+ *    contents.  Nothing in it has to start at zero (each call overwrites every
+ *    value it later reads).  Two calls whose kernels overlap on the GPU - different
+ *    streams, or different host threads - race on it: keep them on one stream or
+ *    order them with events.
+ *  - Calls no cudaMalloc, cudaFree, or any allocating library routine. */
+int polar_b200_fmatmul_tn_small_n_static(int transRight, uint64_t m, uint64_t n,
+                                         uint64_t k, const float* left,
+                                         const float* right, float* out,
+                                         void* stream);
+uint64_t polar_b200_static_scratch_bytes(void);
+
 /* The same product on the CUDA cores: one FFMA per term, k ascending per
  * output within a thread.  Kept only as a device-side cross-check of the
  * tensor-core path; no dispatch reaches it unless a caller asks for it. */

@@ -18,6 +18,8 @@
 //
 // Accumulation is fp32 with fmaf; the order of the k sum differs from the
 // reference's sequential order, within the fp32 tolerance used for fmatmul.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace polar_b200 {
@@ -343,4 +345,73 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
   return check_launch("fmatmul_small_k");
 }
 
+
+// ---------------------------------------------------------------- entry point that allocates nothing
+
+// Scratch for polar_b200_fmatmul_tn_small_n_static: the per-split partial sums of
+// the split-k kernel above.  It is part of the library image, so every GPU that
+// loads the library holds these 16 MiB until the process exits.
+constexpr uint64_t kStaticScratchBytes = 16ull << 20;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+namespace {
+// In host code `g_static_scratch` is only a handle for the runtime; the address the
+// kernels need comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+float* static_scratch_for_current_device(int* status) {
+  static std::mutex mu;
+  static float* cached[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *status = fail(POLAR_B200_ERR_CUDA, "cudaGetDevice", e);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> guard(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      *status = fail(POLAR_B200_ERR_CUDA, "cudaGetSymbolAddress(static scratch)", e);
+      return nullptr;
+    }
+    cached[dev] = static_cast<float*>(p);
+  }
+  *status = POLAR_B200_OK;
+  return cached[dev];
+}
+}  // namespace
+
 }  // namespace polar_b200
+
+extern "C" {
+
+uint64_t polar_b200_static_scratch_bytes(void) { return polar_b200::kStaticScratchBytes; }
+
+int polar_b200_fmatmul_tn_small_n_static(int transRight, uint64_t m, uint64_t n, uint64_t k,
+                                         const float* left, const float* right, float* out,
+                                         void* stream) {
+  using namespace polar_b200;
+  clear_error();
+  if (transRight != 0 && transRight != 1) return fail(POLAR_B200_ERR_INVALID, "transRight must be 0 or 1");
+  if (m == 0 || n == 0) return POLAR_B200_OK;
+  if (!left || !right || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  if (n > 16 || k < 32 || (m & 3) != 0 || !aligned16(left))
+    return fail(POLAR_B200_ERR_UNSUPPORTED,
+                "static-scratch fmatmul serves left stored [k,m] with m a multiple of 4, a 16-byte aligned "
+                "left pointer, n <= 16 and k >= 32");
+  if (m > (1ull << 31) || k > (1ull << 31)) return fail(POLAR_B200_ERR_INVALID, "matrix dimension too large");
+  const uint64_t need = skinny_workspace_bytes(2, m, n, k);
+  if (need > kStaticScratchBytes)
+    return fail(POLAR_B200_ERR_WORKSPACE,
+                "this product needs more than the 16 MiB of built-in scratch; use polar_b200_fmatmul with a "
+                "caller workspace");
+  int rc = POLAR_B200_OK;
+  float* scratch = static_scratch_for_current_device(&rc);
+  if (!scratch) return rc;
+  // Every partial sum the reduction reads is written by the first kernel of this
+  // call, so nothing in the scratch has to be cleared beforehand.
+  return launch_skinny(2, 1, transRight, m, n, k, left, right, out, scratch, as_stream(stream));
+}
+
+}  // extern "C"
