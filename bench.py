@@ -297,23 +297,46 @@ def run_mlp(args):
     value = GLOBAL_BATCH / (ms_per_step / 1e3)
 
     # ---- end to end: host batch in, mean loss out, every step ----
+    # Each step consumes a batch that was copied from pinned host memory into a
+    # staging buffer on a copy stream while the previous step computed, moves it
+    # into the program's X and Y (device to device), starts the copy of the next
+    # batch, runs the program and reads the mean loss back.  One host-to-device
+    # copy of a full X,Y shard and one 8-byte device-to-host read per step.
+    copy_stream = torch.cuda.Stream()
+    stage_x, stage_y = torch.empty_like(ex.t["X"]), torch.empty_like(ex.t["Y"])
+    ev_staged, ev_consumed = torch.cuda.Event(), torch.cuda.Event()
+
+    def prefetch():
+        with torch.cuda.stream(copy_stream):
+            stage_x.copy_(x_host, non_blocking=True)
+            stage_y.copy_(y_host, non_blocking=True)
+            ev_staged.record(copy_stream)
+
     def e2e_step():
-        ex.t["X"].copy_(x_host, non_blocking=True)
-        ex.t["Y"].copy_(y_host, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        cur.wait_event(ev_staged)
+        ex.t["X"].copy_(stage_x, non_blocking=True)
+        ex.t["Y"].copy_(stage_y, non_blocking=True)
+        ev_consumed.record(cur)
+        copy_stream.wait_event(ev_consumed)
+        prefetch()
         timed_step()
         loss_acc.zero_()
         ex.lib.call("polar_b200_fsum", ex.t["L"].data_ptr(), loss_acc.data_ptr(), ex.t["L"].numel(),
-                    torch.cuda.current_stream().cuda_stream)
+                    cur.cuda_stream)
         loss_host.copy_(loss_acc, non_blocking=True)
-        torch.cuda.current_stream().synchronize()           # the caller reads the loss each step
+        cur.synchronize()                                   # the caller reads the loss each step
 
     reset_weights()
+    prefetch()
     e2e_step()
     e2e_ms = time_region(torch, e2e_step, args.steps, dist, world) / args.steps
+    copy_stream.synchronize()
     e2e = {"value": GLOBAL_BATCH / (e2e_ms / 1e3), "unit": "samples/s",
            "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 4) * world,
            "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_ms,
-           "path": "pinned host X,Y shard -> cudaMemcpyAsync -> builtin program -> fsum -> 8-byte loss readback"}
+           "path": "pinned host X,Y shard -> cudaMemcpyAsync on a copy stream (overlaps the previous step) -> "
+                   "device-to-device into the program's inputs -> builtin program -> fsum -> 8-byte loss readback"}
 
     # ---- first-step loss, for the record ----
     reset_weights()
@@ -451,24 +474,25 @@ def run_single_kernel_workload(args):
     sampler.start()
     n0 = lib.launch_count()
     if args.workload == "gemm":
-        n = 8192
+        n = args.size or 8192
         res = gemm_numbers(torch, lib, n, reps=max(1, args.steps))
         ms = res["fmatmul_f_f"]["ms"]
         tf = res["fmatmul_f_f"]["tflops"]
         peak = peaks["bf16_tflops"] / 2.0
         line = {"metric": "fp32_matmul_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "dtype": "f32",
-                "config": {"workload": "fmatmul_f_f_8192x8192x8192", "l2": "operands 805 MB > 126 MB L2"},
+                "config": {"workload": f"fmatmul_f_f_{n}x{n}x{n}",
+                           "l2": f"operands and result {12 * n * n / 1e6:.0f} MB vs 126 MB L2"},
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
                              "pipe_frac": 3 * tf / peak, "traffic": None,
                              "peak_source": f"MEASURED_PEAKS.json bf16_tflops / 2 ({peaks['source']})"},
                 "variants": res}
     else:
-        n = 1 << 28
+        n = 1 << (args.size or 28)
         res = elementwise_numbers(torch, lib, n, peaks, reps=max(3, args.steps))
         gbs = res["fadd"]["gbs"]
         line = {"metric": "elementwise_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": res["fadd"]["ms"],
                 "dtype": "f32",
-                "config": {"workload": "fadd_2pow28", "l2": "three 1 GiB streams > 126 MB L2"},
+                "config": {"workload": f"fadd_{n}_elements", "l2": f"three {4 * n / 2**20:.0f} MiB streams vs 126 MB L2"},
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": gbs / peaks["hbm_gbs"], "traffic": None,
                              "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peaks['source']})"},
@@ -486,6 +510,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "elementwise"])
+    ap.add_argument("--size", type=int, default=0,
+                    help="gemm: m=n=k (default 8192); elementwise: log2 of the element count (default 28)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

@@ -159,7 +159,8 @@ int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
                             const float* right, float* out, void* stream);
 
 /* The tensor-core path alone, with its tuning knobs exposed for tests and
- * benchmarks: tile_n is 128 or 256; passes is 3 (fp32-accurate three-product
+ * benchmarks: tile_n is 128 or 256; slab_k is 16 or 32 (floats of k staged per
+ * pipeline stage); passes is 3 (fp32-accurate three-product
  * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi != 0 makes the
  * split warps store the masked high parts explicitly instead of relying on the
  * tensor core ignoring the low 13 mantissa bits.  Fails with
@@ -168,11 +169,11 @@ int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
  * 4 floats). */
 int polar_b200_fmatmul_tc(int transLeft, int transRight, uint64_t m, uint64_t n,
                           uint64_t k, const float* left, const float* right,
-                          float* out, int tile_n, int passes, int write_hi,
-                          void* stream);
+                          float* out, int tile_n, int slab_k, int passes,
+                          int write_hi, void* stream);
 
 /* Status word the kernels write when a bounded device-side wait gives up
- * (0 = none; 101..105 = which wait of the tensor-core matmul).  It lives in
+ * (0 = none; 101..106 = which wait of the tensor-core matmul).  It lives in
  * pinned host memory, so reading it needs no CUDA call; read it after the
  * stream has been synchronised. */
 int polar_b200_device_status(void);

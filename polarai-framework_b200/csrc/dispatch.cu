@@ -7,7 +7,7 @@ namespace polar_b200 {
 int launch_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                 const float* right, float* out, cudaStream_t stream);
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-              const float* right, float* out, int bn, int passes, int write_hi, cudaStream_t stream);
+              const float* right, float* out, int bn, int bk, int passes, int write_hi, cudaStream_t stream);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
 int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -72,7 +72,7 @@ int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const
   if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);  // empty sum
   switch (choose_path(tl, tr, m, n, k, left, right, out)) {
     case kPathTc:
-      return launch_tc(tl, tr, m, n, k, left, right, out, 256, 3, 0, as_stream(stream));
+      return launch_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, as_stream(stream));
     case kPathSkinny: {
       const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
       const uint64_t need = skinny_workspace_bytes(kind, m, n, k);
@@ -108,17 +108,19 @@ int polar_b200_fmatmul_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
 }
 
 int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                          const float* right, float* out, int tile_n, int passes, int write_hi,
-                          void* stream) {
+                          const float* right, float* out, int tile_n, int slab_k, int passes,
+                          int write_hi, void* stream) {
   clear_error();
   int rc = check_mm(tl, tr, m, n, k, left, right, out);
   if (rc) return rc;
   if (m == 0 || n == 0 || k == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "empty matrix");
   if (tile_n != 128 && tile_n != 256) return fail(POLAR_B200_ERR_INVALID, "tile_n must be 128 or 256");
-  if (passes != 1 && passes != 3) return fail(POLAR_B200_ERR_INVALID, "passes must be 1 or 3");
+  if (slab_k != 16 && slab_k != 32) return fail(POLAR_B200_ERR_INVALID, "slab_k must be 16 or 32");
+  if (passes != 1 && passes != 3 && passes != 13)
+    return fail(POLAR_B200_ERR_INVALID, "passes must be 1 or 3 (13: issue-rate diagnostic)");
   if (!tc_shape_ok(tl, tr, m, n, k, left, right))
     return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
-  return launch_tc(tl, tr, m, n, k, left, right, out, tile_n, passes, write_hi, as_stream(stream));
+  return launch_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, as_stream(stream));
 }
 
 int polar_b200_device_status(void) { return tc_status_word(); }

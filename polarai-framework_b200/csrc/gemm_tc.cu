@@ -8,16 +8,20 @@
 // top 19 bits) and x_lo = x - x_hi, exact in fp32.  The dropped Alo*Blo term and
 // the truncation of x_lo to TF32 are each below 2^-21 relative to |a||b|.
 //
-// One CTA computes one 128 x BN output tile.  Warp roles:
+// One persistent CTA per SM walks 128 x BN output tiles; two accumulators in
+// tensor memory let the epilogue of one tile overlap the k loop of the next.
+// Warp roles:
 //   warp 0     TMA producer: cp.async.bulk.tensor loads of the fp32 A and B
-//              slabs into 128-byte-swizzled shared memory (no cluster multicast:
+//              slabs into 128-byte-swizzled shared memory (plain per-CTA loads:
 //              every CTA fetches its own tiles from this GPU's memory / L2);
 //   warp 1     allocates tensor memory, issues tcgen05.mma (one elected lane),
 //              commits to mbarriers to free stages and to publish the tile;
 //   warps 2-9  split warps: read each landed slab, write the lo part
-//              (and, when kWriteHi, the masked hi part in place) for the async
-//              proxy, then act as the epilogue: tcgen05.ld the accumulator and
-//              store C rows with bounds checks.
+//              (and, when asked, the masked hi part in place) for the async proxy;
+//   warps 10-13 epilogue: tcgen05.ld the finished accumulator and store C rows
+//              with bounds checks, then hand the accumulator back.
+// The hi*hi product of a slab is issued as soon as TMA has delivered it, so the
+// split warps' pass over the slab is hidden behind tensor-core work.
 //
 // All four transpose forms run natively: a K-contiguous operand is a K-major
 // SWIZZLE_128B tile (rows of 32 floats), an M- or N-contiguous one is an
@@ -39,20 +43,24 @@ namespace polar_b200 {
 namespace tc {
 
 constexpr int BM = 128;
-constexpr int BK = 32;                    // floats per slab row: 128 bytes
-constexpr int kSplitWarps = 8;
-constexpr int kThreads = 32 * (2 + kSplitWarps);
-constexpr uint32_t kABytes = BM * BK * 4;  // 16 KB
+constexpr int kSplitWarps = 8;                                  // warps 2..9
+constexpr int kEpilogueWarps = 4;                               // warps 10..13
+constexpr int kThreads = 32 * (2 + kSplitWarps + kEpilogueWarps);
+constexpr int kGroupM = 16;                                     // tile raster: 16 row tiles share their column tiles
 
-template <int BN> struct Cfg {
+// BN: tile width (256 or 128).  BK: floats per k slab (32 -> 128-byte rows, 16 ->
+// 64-byte rows); a shallower slab halves the stage and doubles the pipeline depth.
+template <int BN, int BK> struct Cfg {
+  static constexpr uint32_t kABytes = BM * BK * 4;
   static constexpr uint32_t kBBytes = BN * BK * 4;
   static constexpr uint32_t kRawBytes = kABytes + kBBytes;
   static constexpr uint32_t kStageBytes = 2 * kRawBytes;   // raw (hi) + lo
-  static constexpr int kStages = (BN == 256) ? 2 : 3;
+  static constexpr int kStages = (int)((200u * 1024u) / kStageBytes);
   static constexpr uint32_t kTileBytes = kStages * kStageBytes;
   // tile buffers + 1 KB alignment slack + barriers/flags
   static constexpr uint32_t kSmemBytes = kTileBytes + 1024 + 256;
-  static constexpr uint32_t kTmemCols = BN;  // fp32 accumulator: one column per n
+  static constexpr uint32_t kTmemCols = 2 * BN;            // two fp32 accumulators
+  static constexpr uint32_t kBoxBytes = 32 * BK * 4;       // one MN-major TMA box {32 m/n, BK k}
 };
 
 // ---- PTX wrappers -----------------------------------------------------------
@@ -194,38 +202,56 @@ struct Params {
   int passes;       // 3 = fp32-accurate split, 1 = plain TF32 (diagnostic)
   int write_hi;     // split warps also store the masked hi part in place
   int* status;      // device-visible status word
+  uint32_t tiles_m, tiles_n;
 };
 
-template <int BN>
+// Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
+// CTAs running at the same time share A row panels and B column panels in L2.
+__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, int bn,
+                                            int* m0, int* n0) {
+  const uint32_t per_group = kGroupM * tiles_n;
+  const uint32_t g = t / per_group;
+  const uint32_t first_m = g * kGroupM;
+  const uint32_t rows = (tiles_m - first_m < (uint32_t)kGroupM) ? tiles_m - first_m : (uint32_t)kGroupM;
+  const uint32_t r = t - g * per_group;
+  *m0 = (int)((first_m + r % rows) * BM);
+  *n0 = (int)((r / rows) * bn);
+}
+
+template <int BN, int BK>
 __global__ void __launch_bounds__(kThreads, 1)
 fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const Params p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, BK>;
+  constexpr int S = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   // barrier block after the tiles
   const uint32_t bar_base = smem_base + C::kTileBytes;
   auto full_raw = [&](int s) { return bar_base + 8u * s; };
-  auto full_lo = [&](int s) { return bar_base + 8u * (C::kStages + s); };
-  auto empty = [&](int s) { return bar_base + 8u * (2 * C::kStages + s); };
-  const uint32_t accum_full = bar_base + 8u * (3 * C::kStages);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + C::kTileBytes + 8 * (3 * C::kStages + 1));
+  auto full_lo = [&](int s) { return bar_base + 8u * (S + s); };
+  auto empty = [&](int s) { return bar_base + 8u * (2 * S + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (3 * S + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (3 * S + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + C::kTileBytes + 8 * (3 * S + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
-  const int m0 = (int)(blockIdx.y * BM);
-  const int n0 = (int)(blockIdx.x * BN);
+  const uint32_t num_tiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(full_raw(s), 1);
       mbar_init(full_lo(s), kSplitWarps * 32);
       mbar_init(empty(s), 1);
     }
-    mbar_init(accum_full, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full(a), 1);
+      mbar_init(acc_empty(a), kEpilogueWarps * 32);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -236,30 +262,36 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % C::kStages;
-        const uint32_t ph = (kb / C::kStages) & 1u;
-        if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101)) break;
-        const uint32_t stage = smem_base + s * C::kStageBytes;
-        mbar_expect_tx(full_raw(s), C::kRawBytes);
-        const int k0 = (int)(kb * BK);
-        if (!p.a_mn_major) {
-          tma_load_2d(stage, &map_a, full_raw(s), k0, m0);          // box {32 k, 128 m}
-        } else {
-          for (int c = 0; c < BM / 32; ++c)                          // boxes {32 m, 32 k}
-            tma_load_2d(stage + c * 4096u, &map_a, full_raw(s), m0 + 32 * c, k0);
-        }
-        const uint32_t bdst = stage + kABytes;
-        if (!p.b_mn_major) {
-          tma_load_2d(bdst, &map_b, full_raw(s), k0, n0);            // box {32 k, BN n}
-        } else {
-          for (int c = 0; c < BN / 32; ++c)                          // boxes {32 n, 32 k}
-            tma_load_2d(bdst + c * 4096u, &map_b, full_raw(s), n0 + 32 * c, k0);
+      uint32_t it = 0;   // k slabs issued so far, over all tiles of this CTA
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m0, n0;
+        tile_coords(t, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+        for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101)) { ok = false; break; }
+          const uint32_t stage = smem_base + s * C::kStageBytes;
+          mbar_expect_tx(full_raw(s), C::kRawBytes);
+          const int k0 = (int)(kb * BK);
+          if (!p.a_mn_major) {
+            tma_load_2d(stage, &map_a, full_raw(s), k0, m0);          // box {BK k, 128 m}
+          } else {
+            for (int c = 0; c < BM / 32; ++c)                          // boxes {32 m, BK k}
+              tma_load_2d(stage + c * C::kBoxBytes, &map_a, full_raw(s), m0 + 32 * c, k0);
+          }
+          const uint32_t bdst = stage + C::kABytes;
+          if (!p.b_mn_major) {
+            tma_load_2d(bdst, &map_b, full_raw(s), k0, n0);            // box {BK k, BN n}
+          } else {
+            for (int c = 0; c < BN / 32; ++c)                          // boxes {32 n, BK k}
+              tma_load_2d(bdst + c * C::kBoxBytes, &map_b, full_raw(s), n0 + 32 * c, k0);
+          }
         }
       }
     }
@@ -267,84 +299,126 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, BN, p.a_mn_major, p.b_mn_major);
-      // K-major (SWIZZLE_128B): 8-row groups 1024 B apart (SBO); a k step of 8
-      // floats is +32 B inside the swizzle span.
-      // MN-major (128B swizzle, 32B base): rows of 32 m/n-contiguous floats, one
-      // row per k; 4-row swizzle atoms 512 B apart along k (SBO); 32-element
-      // chunks of m/n 4096 B apart (LBO, one TMA box each); a k step of 8 = +1024 B.
-      const uint32_t a_lbo = p.a_mn_major ? 4096u : 16u, a_step = p.a_mn_major ? 1024u : 32u;
-      const uint32_t b_lbo = p.b_mn_major ? 4096u : 16u, b_step = p.b_mn_major ? 1024u : 32u;
-      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u, a_lt = p.a_mn_major ? 1u : 2u;
-      const uint32_t b_sbo = p.b_mn_major ? 512u : 1024u, b_lt = p.b_mn_major ? 1u : 2u;
+      // K-major: rows of BK floats (128 or 64 bytes, swizzled over that span:
+      // layout 2 or 4), 8-row groups 8*BK*4 bytes apart (SBO); a k step of 8 floats
+      // is +32 B inside the swizzle span.
+      // MN-major (128B swizzle, 32B base: layout 1): rows of 32 m/n-contiguous
+      // floats, one row per k; 4-row swizzle atoms 512 B apart along k (SBO);
+      // 32-element chunks of m/n one TMA box apart (LBO); a k step of 8 = +1024 B.
+      constexpr uint32_t kRowGroup = 8u * BK * 4u;
+      constexpr uint32_t kKMajorLayout = (BK == 32) ? 2u : 4u;
+      const uint32_t a_lbo = p.a_mn_major ? C::kBoxBytes : 16u, a_step = p.a_mn_major ? 1024u : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? C::kBoxBytes : 16u, b_step = p.b_mn_major ? 1024u : 32u;
+      const uint32_t a_sbo = p.a_mn_major ? 512u : kRowGroup, a_lt = p.a_mn_major ? 1u : kKMajorLayout;
+      const uint32_t b_sbo = p.b_mn_major ? 512u : kRowGroup, b_lt = p.b_mn_major ? 1u : kKMajorLayout;
+      uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      for (uint32_t kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % C::kStages;
-        const uint32_t ph = (kb / C::kStages) & 1u;
-        ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102);
-        if (ok && p.passes == 3) ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103);
+      for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+        const uint32_t as = tile_iter & 1u;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        ok = mbar_wait(acc_empty(as), ((tile_iter >> 1) & 1u) ^ 1u, abort_flag, p.status, 106);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_hi = smem_base + s * C::kStageBytes;
-        const uint32_t b_hi = a_hi + kABytes;
-        const uint32_t a_lo = a_hi + C::kRawBytes;
-        const uint32_t b_lo = b_hi + C::kRawBytes;
+        const uint32_t tmem_acc = tmem_base + as * BN;
+        for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_hi = smem_base + s * C::kStageBytes;
+          const uint32_t b_hi = a_hi + C::kABytes;
+          const uint32_t a_lo = a_hi + C::kRawBytes;
+          const uint32_t b_lo = b_hi + C::kRawBytes;
+          // hi*hi needs only what TMA delivered: issue it while the split warps work
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
-          const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
-          const uint32_t first = (kb | (uint32_t)kk) ? 1u : 0u;
-          if (p.passes == 3) {
-            const uint64_t da_lo = make_desc(a_lo + kk * a_step, a_lbo, a_sbo, a_lt);
-            const uint64_t db_lo = make_desc(b_lo + kk * b_step, b_lbo, b_sbo, b_lt);
-            tc_mma_tf32(tmem_acc, da_lo, db_hi, idesc, first);
-            tc_mma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
-            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
-          } else {
-            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, first);
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
+            const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
+            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, (kb | (uint32_t)kk) ? 1u : 0u);
           }
+          if (p.passes == 3) {
+            ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < BK / 8; ++kk) {
+              const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
+              const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
+              const uint64_t da_lo = make_desc(a_lo + kk * a_step, a_lbo, a_sbo, a_lt);
+              const uint64_t db_lo = make_desc(b_lo + kk * b_step, b_lbo, b_sbo, b_lt);
+              tc_mma_tf32(tmem_acc, da_lo, db_hi, idesc, 1u);
+              tc_mma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
+            }
+          }
+          if (p.passes == 13) {
+            // diagnostic: the issue rate of three products per slab with no split
+            // pass at all (the result is 3 x the plain TF32 product)
+#pragma unroll
+            for (int kk = 0; kk < BK / 8; ++kk) {
+              const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
+              const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
+              tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
+              tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
+            }
+          }
+          tc_commit(empty(s));   // frees the stage once these MMAs have read it
         }
-        tc_commit(empty(s));   // frees the stage once these MMAs have read it
+        if (ok) tc_commit(acc_full(as));
       }
-      if (ok) tc_commit(accum_full);
+    }
+  } else if (warp < 2 + kSplitWarps) {
+    // ---------------- split warps ----------------
+    const int tid = threadIdx.x - 64;  // 0..255
+    if (p.passes == 3) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) { ok = false; break; }
+          float4* raw = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes);
+          float4* lo = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes + C::kRawBytes);
+          constexpr int kVecs = C::kRawBytes / 16;
+          static_assert(kVecs % (kSplitWarps * 32) == 0, "slab must divide over the split warps");
+#pragma unroll
+          for (int i = 0; i < kVecs / (kSplitWarps * 32); ++i) {
+            const int e = tid + i * kSplitWarps * 32;
+            float4 v = raw[e];
+            float4 h;
+            h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+            h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+            h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+            h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+            float4 l = {v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w};
+            lo[e] = l;
+            if (p.write_hi) raw[e] = h;
+          }
+          fence_async_smem();
+          mbar_arrive(full_lo(s));
+        }
+      }
     }
   } else {
-    // ---------------- split warps, then epilogue ----------------
-    const int t = threadIdx.x - 64;  // 0..255
-    if (p.passes == 3) {
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % C::kStages;
-        const uint32_t ph = (kb / C::kStages) & 1u;
-        if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) break;
-        float4* raw = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes);
-        float4* lo = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes + C::kRawBytes);
-        constexpr int kVecs = C::kRawBytes / 16;
-#pragma unroll 4
-        for (int i = t; i < kVecs; i += kSplitWarps * 32) {
-          float4 v = raw[i];
-          float4 h;
-          h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-          h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-          h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-          h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-          float4 l = {v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w};
-          lo[i] = l;
-          if (p.write_hi) raw[i] = h;
-        }
-        fence_async_smem();
-        mbar_arrive(full_lo(s));
-      }
-    }
-    // Epilogue: warp w may touch tensor-memory lanes [32*(w%4), 32*(w%4)+32).
-    if (num_kb > 0 && mbar_wait(accum_full, 0u, abort_flag, p.status, 105)) {
+    // ---------------- epilogue warps ----------------
+    // Warp w may touch tensor-memory lanes [32*(w%4), 32*(w%4)+32): four
+    // consecutive warps cover the 128 rows of the tile.
+    const int q = warp & 3;
+    const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint32_t tile_iter = 0;
+    for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_iter) {
+      int m0, n0;
+      tile_coords(t, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+      const uint32_t as = tile_iter & 1u;
+      if (!mbar_wait(acc_full(as), (tile_iter >> 1) & 1u, abort_flag, p.status, 105)) break;
       tc_fence_after();
-      const int q = warp & 3;
-      const int half = (warp - 2) >> 2;                   // two warps share a lane quarter
       const uint64_t row = (uint64_t)m0 + q * 32 + lane;
-      const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+      const uint32_t tmem_acc = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
+      for (int c = 0; c < BN; c += 32) {
         if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
         uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
+        tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
         tmem_ld_wait();
         if (row < p.m) {
           float* dst = p.out + row * p.n + n0 + c;
@@ -362,6 +436,8 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(acc_empty(as));   // this accumulator may be overwritten
     }
   }
 
@@ -376,7 +452,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, C::kTmemCols);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -402,7 +478,7 @@ static EncodeTiledFn get_encode() {
 
 // 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows.
 static int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer,
-                    uint32_t box_inner, uint32_t box_outer, bool mn_major) {
+                    uint32_t box_inner, uint32_t box_outer, bool mn_major, int bk) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {inner, outer};
@@ -411,7 +487,8 @@ static int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                            : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   return POLAR_B200_OK;
@@ -444,50 +521,51 @@ bool shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
   return m > 0 && n > 0 && k > 0;
 }
 
-template <int BN>
-static int launch_bn(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                     const float* right, float* out, int passes, int write_hi, cudaStream_t stream) {
-  using C = Cfg<BN>;
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  // (per process; every device runs the same binary)
+template <int BN, int BK>
+static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                      const float* right, float* out, int passes, int write_hi, cudaStream_t stream) {
+  using C = Cfg<BN, BK>;
+  static_assert(C::kStages >= 2 && C::kSmemBytes <= 227 * 1024, "stage ring must fit shared memory");
   int dev = 0;
   cudaGetDevice(&dev);
   static bool attr_done[64] = {false};
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    attr_err = cudaFuncSetAttribute(fmatmul_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)C::kSmemBytes);
-    if (attr_err != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(smem)", attr_err);
+    cudaError_t e = cudaFuncSetAttribute(fmatmul_tc_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)C::kSmemBytes);
+    if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(smem)", e);
     attr_done[dev] = true;
   }
-  (void)attr_once;
   int rc = ensure_status();
   if (rc) return rc;
   CUtensorMap map_a, map_b;
-  // left: stored [m,k] (K-major: inner k, box {32, 128}) or [k,m] (MN-major: inner m, box {32, 32})
-  rc = tl ? make_map(&map_a, left, m, k, 32, 32, true) : make_map(&map_a, left, k, m, 32, BM, false);
+  // left: stored [m,k] (K-major: inner k, box {BK, 128}) or [k,m] (MN-major: inner m, box {32, BK})
+  rc = tl ? make_map(&map_a, left, m, k, 32, BK, true, BK) : make_map(&map_a, left, k, m, BK, BM, false, BK);
   if (rc) return rc;
-  // right: stored [n,k] when transposed (K-major: inner k, box {32, BN}) or [k,n] (MN-major)
-  rc = tr ? make_map(&map_b, right, k, n, 32, BN, false) : make_map(&map_b, right, n, k, 32, 32, true);
+  // right: stored [n,k] when transposed (K-major: inner k, box {BK, BN}) or [k,n] (MN-major)
+  rc = tr ? make_map(&map_b, right, k, n, BK, BN, false, BK) : make_map(&map_b, right, n, k, 32, BK, true, BK);
   if (rc) return rc;
   Params p;
   p.m = m; p.n = n; p.k = k; p.out = out;
   p.a_mn_major = tl ? 1 : 0;
   p.b_mn_major = tr ? 0 : 1;
   p.passes = passes; p.write_hi = write_hi; p.status = g_status_dev;
-  uint64_t gx = (n + BN - 1) / BN, gy = (m + BM - 1) / BM;
-  if (gy > 65535 || gx > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
-  dim3 grid((unsigned)gx, (unsigned)gy);
-  fmatmul_tc_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+  uint64_t tm = (m + BM - 1) / BM, tn = (n + BN - 1) / BN;
+  if (tm * tn > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
+  p.tiles_m = (uint32_t)tm; p.tiles_n = (uint32_t)tn;
+  uint64_t tiles = tm * tn;
+  unsigned grid = (unsigned)(tiles < (uint64_t)sm_count() ? tiles : (uint64_t)sm_count());   // one CTA per SM
+  fmatmul_tc_kernel<BN, BK><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
   return check_launch("fmatmul_tc");
 }
 
 }  // namespace tc
 
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-              const float* right, float* out, int bn, int passes, int write_hi, cudaStream_t stream) {
-  if (bn == 128) return tc::launch_bn<128>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
-  return tc::launch_bn<256>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+              const float* right, float* out, int bn, int bk, int passes, int write_hi, cudaStream_t stream) {
+  if (bn == 128 && bk == 32) return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+  if (bn == 128) return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+  if (bk == 32) return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
 }
 
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,

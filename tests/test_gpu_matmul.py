@@ -63,6 +63,8 @@ SHAPES = [
     (200, 300, 100), (260, 516, 36), (1000, 40, 2000),      # ragged m/n/k tails (multiples of 4)
     (512, 512, 512), (256, 784, 128), (784, 128, 256),      # sizes from the logistic-regression / MLP configs
     (1024, 1024, 1024),
+    (2304, 2048, 96),                                       # 144 or 288 tiles: several tiles per persistent CTA
+    (4224, 1280, 64),
 ]
 
 
@@ -74,11 +76,12 @@ def test_tensor_core_path(gpu, par_oracle, tl, tr, shape):
     rng = np.random.default_rng(m * 7 + n * 3 + k + tl * 2 + tr)
     l, r = operands(rng, tl, tr, m, n, k)
     ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
-    got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=256)
-    assert rel_err(got, ref, mag) <= TOL
-    assert rel_err(got, ref, mag) <= 5e-6          # what the three-product split actually delivers
-    got128 = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=128)
-    assert rel_err(got128, ref, mag) <= 5e-6
+    for tile_n in (256, 128):
+        for slab_k in (16, 32):
+            got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k)
+            err = rel_err(got, ref, mag)
+            assert err <= TOL, (tile_n, slab_k, err)
+            assert err <= 5e-6, (tile_n, slab_k, err)   # what the three-product split actually delivers
     auto = gpu.fmatmul(tl, tr, l, r)
     assert rel_err(auto, ref, mag) <= TOL
     assert gpu.d.device_status() == 0
