@@ -392,13 +392,31 @@ def run_mlp(args):
             "breakdown_ms": {k: round(v["ms"], 4) for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1]["ms"])}}
     if rank == 0 and world == 1 and not args.no_extras:
         line["cpu_baseline"] = cpu_mlp_baseline(2048, steps=1)[0]
-        line["extras"] = {"gemm_8192": gemm_numbers(torch, lib, 8192, reps=3),
-                          "elementwise_2pow28": elementwise_numbers(torch, lib, 1 << 28, peaks, reps=5)}
+        # the bandwidth numbers first: the GEMM loop leaves the GPU at its power cap
+        ew = elementwise_numbers(torch, lib, 1 << 28, peaks, reps=10)
+        line["extras"] = {"elementwise_2pow28": ew, "gemm_8192": gemm_numbers(torch, lib, 8192, reps=3)}
     if rank == 0:
         print(json.dumps(line), flush=True)
+    shutdown(torch, dist, world, graph)
+
+
+def shutdown(torch, dist, world, graph):
+    """Leaves the process promptly.  Tearing down an NCCL communicator while a
+    captured CUDA graph still references its kernels was seen to block for
+    minutes after the result had been printed, so: drop the graph, drain the
+    device, meet the other ranks once, give destroy_process_group a few seconds
+    on a helper thread, then exit without running further teardown."""
+    del graph
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(timeout=10.0)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def mm_dims(program, kernel, args):

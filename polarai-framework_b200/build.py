@@ -106,11 +106,85 @@ def build_runtime(force=False):
     return lib
 
 
+REF_TESTS = ["AddOperation", "CombineOperation", "DivideOperation", "LogLossOperation", "MatMulOperation",
+             "MulConcatOperation", "MulOperation", "SigmoidOperation"]
+
+
+def build_reference_host(force=False):
+    """The unchanged PolarAI frontend (graph, autograd, operations, loaders), runtime
+    driver, support routines and LayerAllocator compiled from the reference tree
+    where it lies; this package's Executor on top; and the reference's own
+    integration tests for the builtins on this path, built against the stand-in
+    gtest header in tests/ref_integration/.  Everything lands under lib/ (not
+    tracked).  Without the reference tree, prebuilt files are kept."""
+    out_dir = os.path.join(LIB, "ref")
+    frontend = os.path.join(out_dir, "libpolar_frontend.so")
+    executor = os.path.join(LIB, "libpolar_b200_executor.so")
+    tests_bin = os.path.join(out_dir, "ref_integration_tests")
+    ref = reference_root()
+    if ref is None:
+        return [p for p in (frontend, executor, tests_bin) if os.path.exists(p)]
+    os.makedirs(out_dir, exist_ok=True)
+    obj_dir = os.path.join(OBJ, "ref")
+    gen = os.path.join(obj_dir, "gen")
+    os.makedirs(gen, exist_ok=True)
+    stubs = os.path.join(OBJ, "export_stubs")
+    os.makedirs(stubs, exist_ok=True)
+    for name in ["polar_core", "polar_utils", "polar_loaders", "polar_operation", "polar_backend_generic",
+                 "polar_rt_support", "polar_io", "polar_rt_cuda", "polar_generic_be_driver"]:
+        with open(os.path.join(stubs, name + "_export.h"), "w") as fh:
+            macro = name.upper()
+            fh.write(f"#pragma once\n#define {macro}_EXPORT\n#define {macro}_NO_EXPORT\n")
+    # The driver's generated config.h: the one build-time switch the integration
+    # needs - the CUDA runtime library is on the list the RuntimeDriver loads.
+    with open(os.path.join(gen, "config.h"), "w") as fh:
+        fh.write('#pragma once\n#include <string>\n#include <vector>\n'
+                 'inline std::vector<std::string> getListOfLibraries() { return {"libpolar_rt_cuda.so"}; }\n')
+    gxx = "/usr/bin/g++"
+    flags = ["-std=c++17", "-O2", "-fPIC", "-fno-rtti", "-fno-exceptions", "-w",
+             "-DATHENA_MAJOR_VERSION=\"0\"", "-DATHENA_MINOR_VERSION=\"1\"", "-DATHENA_PATCH_VERSION=\"0\"",
+             "-I", os.path.join(ref, "include"), "-I", os.path.join(ref, "src"),
+             "-I", os.path.join(ref, "src", "backend", "generic"), "-I", stubs, "-I", gen]
+    srcs = []
+    for sub in ("core", "operation", "loaders", "utils", "io"):
+        for d, _, files in os.walk(os.path.join(ref, "src", sub)):
+            srcs += [os.path.join(d, f) for f in files if f.endswith(".cpp")]
+    g = os.path.join(ref, "src", "backend", "generic")
+    srcs += [os.path.join(g, "runtime", "driver", "RuntimeDriver.cpp"),
+             os.path.join(g, "runtime", "driver", "DynamicLibrary_posix.cpp"),
+             os.path.join(g, "runtime", "support", "routines.cpp"),
+             os.path.join(g, "lib", "allocators", "LayerAllocator.cpp")]
+    if force or not os.path.exists(frontend):
+        jobs, objs = [], []
+        for i, src in enumerate(sorted(srcs)):
+            o = os.path.join(obj_dir, f"{i:03d}_{os.path.basename(src)[:-4]}.o")
+            objs.append(o)
+            jobs.append([gxx] + flags + ["-c", src, "-o", o])
+        with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+            list(ex.map(_run, jobs))
+        _run([gxx, "-shared", "-o", frontend] + objs + ["-ldl", "-lpthread", "-Wl,-rpath,$ORIGIN/.."])
+    ex_src = os.path.join(CSRC, "executor", "direct_executor.cpp")
+    if force or _newer(ex_src, executor, (frontend,)):
+        _run([gxx] + flags + ["-shared", "-o", executor, ex_src, "-L", out_dir, "-lpolar_frontend",
+                              "-Wl,-rpath,$ORIGIN/ref:$ORIGIN"])
+    shim = os.path.join(ROOT, "tests", "ref_integration")
+    main_src = os.path.join(shim, "main.cpp")
+    if force or _newer(main_src, tests_bin, (executor, os.path.join(shim, "gtest", "gtest.h"))):
+        tdir = os.path.join(ref, "tests", "integration", "operations")
+        tsrcs = [os.path.join(tdir, t + ".cpp") for t in REF_TESTS]
+        tflags = [f for f in flags if f != "-fno-exceptions"]
+        _run([gxx] + tflags + ["-I", shim, "-I", tdir, "-o", tests_bin, main_src] + tsrcs +
+             ["-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl", "-lpthread",
+              "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
+    return [frontend, executor, tests_bin]
+
+
 def build_all(force=False, verbose=False):
     libs = [build_kernels(force, verbose)]
     rt = build_runtime(force)
     if rt:
         libs.append(rt)
+    libs += build_reference_host(force)
     return libs
 
 

@@ -75,10 +75,18 @@ struct ScaleByFirstOp {  // fmulconcat: the scalar is read once per thread
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
 
+// Per-op tile shape: vectors in flight per input per thread, and CTAs per SM the
+// register budget must allow.  flogloss carries two logf per element: measured at
+// 2^28 elements it streams fastest with less per thread and twice the CTAs
+// (6.4 vs 5.8 TB/s); the others are flat between 2 and 8 vectors per thread.
+template <class Op> struct Shape { static constexpr int kUnroll = 4, kMinCtas = kCtasPerSm; };
+template <> struct Shape<LogLossOp> { static constexpr int kUnroll = 2, kMinCtas = 8; };
+
 // NIN = number of input streams (0, 1 or 2).
 template <int NIN, class Op>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+__global__ void __launch_bounds__(kThreads, Shape<Op>::kMinCtas)
 ew_vec_kernel(Op op, const float* in0, const float* in1, float* out, uint64_t n) {
+  constexpr int kUnroll = Shape<Op>::kUnroll;
   const uint64_t nvec = n >> 2;
   const float4* v0 = reinterpret_cast<const float4*>(in0);
   const float4* v1 = reinterpret_cast<const float4*>(in1);
@@ -201,8 +209,8 @@ unsigned grid_for(uint64_t work_items, uint64_t per_cta) {
   return (unsigned)(need < cap ? need : cap);
 }
 // One tile per CTA (vector kernels).
-unsigned tiles_for(uint64_t nvec) {
-  uint64_t per_cta = (uint64_t)kThreads * kUnroll;
+unsigned tiles_for(uint64_t nvec, int unroll = kUnroll) {
+  uint64_t per_cta = (uint64_t)kThreads * unroll;
   uint64_t need = (nvec + per_cta - 1) / per_cta;
   return (unsigned)(need < 1 ? 1 : need);
 }
@@ -217,7 +225,7 @@ int launch_ew(const char* name, Op op, const float* in0, const float* in1, float
   if (n > (1ull << 40)) return fail(POLAR_B200_ERR_INVALID, "element count too large");
   bool vec = aligned16(out) && (NIN < 1 || aligned16(in0)) && (NIN < 2 || aligned16(in1)) && n >= 4;
   if (vec) {
-    unsigned grid = tiles_for(n >> 2);
+    unsigned grid = tiles_for(n >> 2, Shape<Op>::kUnroll);
     ew_vec_kernel<NIN, Op><<<grid, kThreads, 0, as_stream(stream)>>>(op, in0, in1, out, n);
   } else {
     unsigned grid = grid_for(n, kThreads);

@@ -1,0 +1,406 @@
+// A direct (non-JIT) implementation of polarai::backend::generic::Executor.
+//
+// The reference's Executor (include/polarai/backend/generic/Executor.hpp:36-61,
+// src/backend/generic/lib/ExecutorImpl.cpp) lowers a graph through MLIR and an LLVM
+// JIT into host code that calls the ath_* support routines.  This file provides the
+// same class - same header, same member functions - without a compiler: the
+// framework's own GraphCompiler::compile (src/core/graph/internal/GraphCompiler.cpp:21-110)
+// is driven with a Generator whose functors RECORD the builtin program (per node:
+// alloc, lock, invoke-loader or builtin launch, release; per cluster: barrier), and
+// evaluate() replays the record through the reference's unchanged support routines
+// (ath_device_select, ath_allocate, ath_lock, ath_load, ath_launch, ath_release,
+// ath_barrier - src/backend/generic/runtime/support/routines.cpp:37-112), which in
+// turn drive whatever devices the RuntimeDriver found - here the B200 plugin.
+//
+// Builtins are launched by native kernel name with LaunchCommand/ArgDesc/TensorInfo
+// arguments in the order the MLIR lowering would have produced
+// (utils/dialects/include/PolarGraph/PolarGraphOps.td; CodeGen.cpp:283-462).
+#include <polarai/backend/generic/Executor.hpp>
+#include <polarai/backend/generic/runtime/Event.hpp>
+#include <polarai/backend/generic/runtime/GraphHandle.hpp>
+#include <polarai/backend/generic/runtime/LaunchCommand.h>
+#include <polarai/backend/generic/runtime/TensorInfo.h>
+#include <polarai/core/Generator.hpp>
+#include <polarai/core/context/internal/ContextInternal.hpp>
+#include <polarai/core/graph/internal/GraphCompiler.hpp>
+#include <polarai/core/loader/internal/AbstractLoaderInternal.hpp>
+#include <polarai/core/node/internal/AbstractNodeInternal.hpp>
+#include <polarai/core/node/internal/InputNodeInternal.hpp>
+
+#include <lib/allocators/LayerAllocator.hpp>
+#include <runtime/driver/RuntimeDriver.hpp>
+#include <runtime/host/HostDevice.hpp>
+#include <runtime/support/api.hpp>
+
+#include <algorithm>
+#include <cstdio>
+#include <iostream>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <variant>
+#include <vector>
+
+using namespace polarai::core;
+using namespace polarai::core::internal;
+
+namespace polarai::backend::generic {
+
+namespace {
+
+// A tensor as the runtime sees it: what goes into a TensorInfo.
+struct TensorDesc {
+  uint64_t virtAddr = 0;
+  int dataType = 0;
+  std::vector<uint64_t> shape;
+};
+
+struct Value : GenValueImplBase {
+  bool isTensor = false;
+  TensorDesc tensor;
+  float scalar = 0.f;
+};
+
+GenValue makeTensorValue(const TensorInternal& t) {
+  auto v = std::make_shared<Value>();
+  v->isTensor = true;
+  v->tensor.virtAddr = t.getVirtualAddress();
+  v->tensor.dataType = static_cast<int>(t.getDataType());
+  for (size_t d : t.getShape().getShape()) v->tensor.shape.push_back(d);
+  return GenValue{v};
+}
+
+struct Command {
+  enum Kind { ALLOC, LOCK, RELEASE, LOAD, LAUNCH } kind;
+  TensorDesc tensor;                  // ALLOC, LOCK, RELEASE, LOAD
+  LockType lockType = LockType::READ; // LOCK
+  std::string nativeName;             // LAUNCH
+  std::vector<Value> args;            // LAUNCH, in LaunchCommand order
+};
+
+struct NodeRecord : GenNodeImplBase {
+  std::string name;
+  size_t nodeId = 0;
+  size_t clusterId = 0;
+  std::vector<GenValue> operands;
+  GenValue result;
+  std::vector<Command> commands;
+  auto getOperand(size_t i) -> GenValue override { return operands.at(i); }
+  auto getResult() -> GenValue override { return result; }
+  auto getBatchIndex() -> GenValue override { return GenValue{}; }
+};
+
+struct Step {
+  enum Kind { NODE, BARRIER } kind;
+  std::shared_ptr<NodeRecord> node;
+  uint64_t clusterId = 0;
+};
+
+struct GraphRecord : GenGraphImplBase {
+  std::string name;
+  std::vector<Step> steps;
+};
+
+// Where recorded commands go: a node body, a graph body, or nowhere (top level).
+struct InsertionPoint : GenInsPointImplBase {
+  NodeRecord* node = nullptr;
+  GraphRecord* graph = nullptr;
+};
+
+// Installs recording functors for every builtin of the catalogue
+// (include/polarai/core/internal/GenBuiltins.hpp:25-52).
+class Recorder {
+public:
+  explicit Recorder(Generator& gen) { install(gen); }
+  std::shared_ptr<GraphRecord> graph;
+  std::vector<std::string> unsupported;
+
+private:
+  InsertionPoint mPoint;
+
+  void emit(Command c) {
+    if (mPoint.node) mPoint.node->commands.push_back(std::move(c));
+  }
+  static const Value& val(const GenValue& v) { return v.value<Value>(); }
+
+  void launch(const char* name, std::initializer_list<GenValue> args) {
+    Command c;
+    c.kind = Command::LAUNCH;
+    c.nativeName = name;
+    for (const auto& a : args) c.args.push_back(val(a));
+    emit(std::move(c));
+  }
+  void refuse(const char* what) { unsupported.emplace_back(what); }
+
+  void install(Generator& g) {
+    g.registerConstantFunctor([](Generator::SupportedConstantT c) {
+      auto v = std::make_shared<Value>();
+      v->scalar = std::visit([](auto x) { return static_cast<float>(x); }, c);
+      return GenValue{v};
+    });
+    g.registerNodeFunctor([this](std::string_view name, size_t nodeId, size_t clusterId,
+                                 const std::vector<TensorInternal*>& operands, TensorInternal& out) {
+      auto n = std::make_shared<NodeRecord>();
+      n->name = std::string(name);
+      n->nodeId = nodeId;
+      n->clusterId = clusterId;
+      for (auto* t : operands) n->operands.push_back(makeTensorValue(*t));
+      n->result = makeTensorValue(out);
+      return GenNode{n};
+    });
+    g.registerGraphFunctor([this](std::string_view name, size_t) {
+      graph = std::make_shared<GraphRecord>();
+      graph->name = std::string(name);
+      return GenGraph{graph};
+    });
+    g.registerSetInsertionPointFunctor(std::function<void(GenInsertionPoint)>(
+        [this](GenInsertionPoint p) { mPoint = p.point<InsertionPoint>(); }));
+    g.registerSetInsertionPointFunctor(std::function<void(GenNode)>([this](GenNode n) {
+      mPoint.node = &n.node<NodeRecord>();
+      mPoint.graph = nullptr;
+    }));
+    g.registerSetInsertionPointFunctor(std::function<void(GenGraph)>([this](GenGraph gr) {
+      mPoint.node = nullptr;
+      mPoint.graph = &gr.graph<GraphRecord>();
+    }));
+    g.registerGetInsertionPointFunctor([this]() {
+      return GenInsertionPoint{std::make_shared<InsertionPoint>(mPoint)};
+    });
+
+    builtin_functor_t<builtin::Alloc> alloc = [this](GenValue t) {
+      Command c;
+      c.kind = Command::ALLOC;
+      c.tensor = val(t).tensor;
+      emit(std::move(c));
+      return GenValue{};
+    };
+    g.registerFunctor<builtin::Alloc>(alloc);
+    builtin_functor_t<builtin::Lock> lock = [this](GenValue t, LockType type) {
+      Command c;
+      c.kind = Command::LOCK;
+      c.tensor = val(t).tensor;
+      c.lockType = type;
+      emit(std::move(c));
+      return GenValue{};
+    };
+    g.registerFunctor<builtin::Lock>(lock);
+    builtin_functor_t<builtin::Release> release = [this](GenValue t) {
+      Command c;
+      c.kind = Command::RELEASE;
+      c.tensor = val(t).tensor;
+      emit(std::move(c));
+      return GenValue{};
+    };
+    g.registerFunctor<builtin::Release>(release);
+    builtin_functor_t<builtin::InvokeLoader> load = [this](GenValue t) {
+      Command c;
+      c.kind = Command::LOAD;
+      c.tensor = val(t).tensor;
+      emit(std::move(c));
+      return GenValue{};
+    };
+    g.registerFunctor<builtin::InvokeLoader>(load);
+    builtin_functor_t<builtin::Barrier> barrier = [this](uint64_t clusterId) {
+      if (mPoint.graph) mPoint.graph->steps.push_back(Step{Step::BARRIER, nullptr, clusterId});
+    };
+    g.registerFunctor<builtin::Barrier>(barrier);
+    builtin_functor_t<builtin::NodeEval> eval = [this](GenGraph gr, GenNode n, const std::vector<GenValue>&) {
+      auto& rec = gr.graph<GraphRecord>();
+      auto node = std::shared_ptr<NodeRecord>(&n.node<NodeRecord>(), [keep = n](NodeRecord*) {});
+      rec.steps.push_back(Step{Step::NODE, node, node->clusterId});
+      return n.getResult();
+    };
+    g.registerFunctor<builtin::NodeEval>(eval);
+    builtin_functor_t<builtin::Return> ret = [](std::optional<GenValue>) {};
+    g.registerFunctor<builtin::Return>(ret);
+
+    // Operation builtins -> native kernel names and LaunchCommand argument orders.
+    builtin_functor_t<builtin::Add> add = [this](GenValue a, GenValue sa, GenValue b, GenValue sb, GenValue out) {
+      launch("fadd", {a, sa, b, sb, out});
+    };
+    g.registerFunctor<builtin::Add>(add);
+    builtin_functor_t<builtin::Copy> copy = [this](GenValue in, GenValue out) { launch("fcopy", {in, out}); };
+    g.registerFunctor<builtin::Copy>(copy);
+    builtin_functor_t<builtin::Divide> div = [this](GenValue n, GenValue d, GenValue out) {
+      launch("fdivide", {n, d, out});
+    };
+    g.registerFunctor<builtin::Divide>(div);
+    builtin_functor_t<builtin::LogLoss> ll = [this](GenValue p, GenValue y, GenValue out) {
+      launch("flogloss", {p, y, out});
+    };
+    g.registerFunctor<builtin::LogLoss>(ll);
+    builtin_functor_t<builtin::MatMul> mm = [this](GenValue l, GenValue r, GenValue out, bool tl, bool tr) {
+      const char* names[2][2] = {{"fmatmul_f_f", "fmatmul_f_t"}, {"fmatmul_t_f", "fmatmul_t_t"}};
+      launch(names[tl ? 1 : 0][tr ? 1 : 0], {l, r, out});
+    };
+    g.registerFunctor<builtin::MatMul>(mm);
+    builtin_functor_t<builtin::Mul> mul = [this](GenValue a, GenValue b, GenValue out) { launch("fmul", {a, b, out}); };
+    g.registerFunctor<builtin::Mul>(mul);
+    builtin_functor_t<builtin::MulConcat> mc = [this](GenValue grad, GenValue local, GenValue out) {
+      launch("fmulconcat", {grad, local, out});
+    };
+    g.registerFunctor<builtin::MulConcat>(mc);
+    builtin_functor_t<builtin::Fill> fill = [this](GenValue pattern, GenValue out) { launch("ffill", {pattern, out}); };
+    g.registerFunctor<builtin::Fill>(fill);
+    builtin_functor_t<builtin::Sigmoid> sig = [this](GenValue in, GenValue out) { launch("fsigmoid", {in, out}); };
+    g.registerFunctor<builtin::Sigmoid>(sig);
+
+    // Builtins outside the path this runtime implements.
+    builtin_functor_t<builtin::Conv2D> conv = [this](GenValue, GenValue, GenValue) { refuse("Conv2D"); };
+    g.registerFunctor<builtin::Conv2D>(conv);
+    builtin_functor_t<builtin::Pool2D> pool = [this](GenValue, GenValue, const std::vector<int64_t>&,
+                                                     const std::vector<int64_t>&) { refuse("Pool2D"); };
+    g.registerFunctor<builtin::Pool2D>(pool);
+    builtin_functor_t<builtin::ReLU> relu = [this](GenValue, GenValue) { refuse("ReLU"); };
+    g.registerFunctor<builtin::ReLU>(relu);
+    builtin_functor_t<builtin::Softmax> sm = [this](GenValue, GenValue) { refuse("Softmax"); };
+    g.registerFunctor<builtin::Softmax>(sm);
+    builtin_functor_t<builtin::Slice> sl = [this](GenValue, GenValue) { refuse("Slice"); };
+    g.registerFunctor<builtin::Slice>(sl);
+    builtin_functor_t<builtin::Transpose> tp = [this](GenValue, GenValue) { refuse("Transpose"); };
+    g.registerFunctor<builtin::Transpose>(tp);
+  }
+};
+
+TensorInfo infoOf(TensorDesc& d) {
+  TensorInfo t;
+  t.virtAddr = d.virtAddr;
+  t.dataType = d.dataType;
+  t.dims = d.shape.size();
+  t.shape = d.shape.data();
+  return t;
+}
+
+}  // namespace
+
+class ExecutorImpl {
+public:
+  using FilterFunctionT = Executor::FilterFunctionT;
+
+  ExecutorImpl(bool debug, FilterFunctionT filter) : mDebug(debug), mFilter(std::move(filter)) {
+    mAllocator = std::make_shared<LayerAllocator>();
+    mRuntimeDriver = std::make_shared<RuntimeDriver>(debug);
+    std::copy_if(mRuntimeDriver->getDeviceList().begin(), mRuntimeDriver->getDeviceList().end(),
+                 std::back_inserter(mDevices), mFilter);
+    for (auto& dev : mDevices) {
+      if (debug) std::clog << "Registering " << dev->getDeviceName() << '\n';
+      mAllocator->registerDevice(*dev);
+    }
+    mHost = std::make_shared<HostDevice>();
+  }
+
+  void addGraph(Graph& graph) {
+    Generator generator;
+    Recorder recorder(generator);
+    GraphCompiler::compile(graph, generator);
+    for (auto& u : recorder.unsupported)
+      std::fprintf(stderr, "[polar_b200_executor] graph '%s' uses builtin %s, which this runtime does not implement\n",
+                   graph.getName().getString(), u.c_str());
+    mGraphs[graph.getName().getString()] = recorder.graph;
+    if (mDebug && recorder.graph)
+      std::clog << "Recorded graph " << recorder.graph->name << ": " << recorder.graph->steps.size() << " steps\n";
+  }
+
+  void evaluate(Graph& graph) {
+    auto it = mGraphs.find(graph.getName().getString());
+    if (it == mGraphs.end() || !it->second) {
+      std::fprintf(stderr, "[polar_b200_executor] evaluate: graph '%s' was not added\n", graph.getName().getString());
+      return;
+    }
+    if (mDevices.empty()) {
+      std::fprintf(stderr, "[polar_b200_executor] evaluate: no device\n");
+      return;
+    }
+    GraphHandle handle;
+    handle.allocator = mAllocator;
+    handle.devices.push_back(mDevices.front());
+    handle.devices.push_back(mHost);
+    // Input nodes run on the host: their loaders fill host memory (ExecutorImpl.cpp:77-93).
+    auto& traversal = graph.traverse();
+    auto ctx = graph.getContext().internal();
+    for (const auto& cluster : traversal.getClusters()) {
+      for (const auto& node : cluster.content) {
+        auto& n = ctx->getRef<AbstractNodeInternal>(node.nodeIndex);
+        if (n.getType() != NodeType::INPUT) continue;
+        auto& inp = ctx->getRef<InputNodeInternal>(node.nodeIndex);
+        auto& loader = ctx->getRef<AbstractLoaderInternal>(inp.getLoader());
+        handle.mLoaders[node.nodeIndex] = &loader;
+        handle.isHostNode.insert(node.nodeIndex);
+      }
+    }
+    std::vector<Event*> pending;
+    for (auto& step : it->second->steps) {
+      if (step.kind == Step::BARRIER) {
+        if (!pending.empty()) ath_barrier(static_cast<uint32_t>(pending.size()), pending.data());
+        for (Event* e : pending) delete e;
+        pending.clear();
+        continue;
+      }
+      NodeRecord& node = *step.node;
+      Device* device = ath_device_select(&handle, node.nodeId);
+      for (auto& c : node.commands) {
+        TensorInfo ti = infoOf(c.tensor);
+        switch (c.kind) {
+          case Command::ALLOC: ath_allocate(&handle, *device, &ti); break;
+          case Command::LOCK: ath_lock(&handle, *device, &ti, c.lockType); break;
+          // Work on a device is stream-ordered, so the lock can go as soon as the
+          // launch is queued; no event is attached.
+          case Command::RELEASE: ath_release(&handle, *device, &ti, nullptr); break;
+          case Command::LOAD: ath_load(&handle, node.nodeId, &ti); break;
+          case Command::LAUNCH: {
+            std::vector<TensorInfo> infos(c.args.size());
+            std::vector<ArgDesc> args(c.args.size());
+            for (size_t i = 0; i < c.args.size(); ++i) {
+              Value& v = c.args[i];
+              if (v.isTensor) {
+                infos[i] = infoOf(v.tensor);
+                args[i] = ArgDesc{0, &infos[i], ArgDesc::TENSOR};
+              } else {
+                args[i] = ArgDesc{sizeof(float), &v.scalar, ArgDesc::DATA};
+              }
+            }
+            std::string kernelName = node.name + "_" + c.nativeName;
+            LaunchCommand cmd{kernelName.c_str(), args.size(), args.data(), c.nativeName.c_str()};
+            Event* evt = ath_launch(&handle, device, nullptr, cmd);
+            if (evt) pending.push_back(evt);
+            break;
+          }
+        }
+      }
+    }
+    if (!pending.empty()) ath_barrier(static_cast<uint32_t>(pending.size()), pending.data());
+    for (Event* e : pending) delete e;
+  }
+
+  BackendAllocator& getAllocator() { return *mAllocator; }
+  std::shared_ptr<BackendAllocator> getAllocatorPtr() { return mAllocator; }
+  void setAllocator(std::shared_ptr<BackendAllocator>& allocator) {
+    mAllocator = std::move(allocator);
+    for (auto& dev : mDevices) mAllocator->registerDevice(*dev);
+  }
+  std::vector<std::shared_ptr<Device>>& getDevices() { return mDevices; }
+
+private:
+  bool mDebug;
+  FilterFunctionT mFilter;
+  // The driver owns the plugin library: it must outlive the devices' users.
+  std::shared_ptr<RuntimeDriver> mRuntimeDriver;
+  std::vector<std::shared_ptr<Device>> mDevices;
+  std::shared_ptr<Device> mHost;
+  std::shared_ptr<BackendAllocator> mAllocator;
+  std::map<std::string, std::shared_ptr<GraphRecord>> mGraphs;
+};
+
+// ---- the public class declared by the reference header ----------------------
+
+Executor::Executor(bool enableDebugOutput, FilterFunctionT filter)
+    : mImpl(polarai::utils::makeShared<ExecutorImpl>(enableDebugOutput, std::move(filter))) {}
+void Executor::addGraph(Graph& graph) { mImpl->addGraph(graph); }
+void Executor::evaluate(Graph& graph) { mImpl->evaluate(graph); }
+BackendAllocator& Executor::getAllocator() { return mImpl->getAllocator(); }
+std::shared_ptr<BackendAllocator> Executor::getAllocatorPtr() { return mImpl->getAllocatorPtr(); }
+void Executor::setAllocator(std::shared_ptr<BackendAllocator>& allocator) { mImpl->setAllocator(allocator); }
+std::vector<std::shared_ptr<Device>>& Executor::getDevices() { return mImpl->getDevices(); }
+
+}  // namespace polarai::backend::generic
