@@ -292,7 +292,6 @@ def run_mlp(args):
     n0 = lib.launch_count()
     ms = time_region(torch, timed_step, args.steps, dist, world)
     launched = lib.launch_count() - n0
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = GLOBAL_BATCH / (ms_per_step / 1e3)
 
@@ -332,6 +331,16 @@ def run_mlp(args):
     e2e_step()
     e2e_ms = time_region(torch, e2e_step, args.steps, dist, world) / args.steps
     copy_stream.synchronize()
+    # Clocks are sampled over both timed regions (device-resident and end to end).
+    # At 8 GPUs one region lasts about 25 ms, shorter than nvidia-smi's period, so
+    # every rank runs the same number of further steps (the count derives from the
+    # max-reduced step time, identical on all ranks) until about 0.3 s are covered.
+    covered_ms = (ms_per_step + e2e_ms) * args.steps
+    if covered_ms < 300.0:
+        for _ in range(int((300.0 - covered_ms) / ms_per_step) + 1):
+            timed_step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
     e2e = {"value": GLOBAL_BATCH / (e2e_ms / 1e3), "unit": "samples/s",
            "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 4) * world,
            "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_ms,
@@ -530,6 +539,8 @@ def main():
     ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "elementwise"])
     ap.add_argument("--size", type=int, default=0,
                     help="gemm: m=n=k (default 8192); elementwise: log2 of the element count (default 28)")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="mlp: global batch override for profiling small cases (default 65536, the metric's)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
@@ -541,6 +552,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the runtime has no CPU path (use --impl reference "
                          "for the CPU arm)")
     if args.workload == "mlp":
+        if args.batch:
+            global GLOBAL_BATCH
+            GLOBAL_BATCH = args.batch
         run_mlp(args)
     else:
         run_single_kernel_workload(args)
