@@ -123,7 +123,7 @@ def build_reference_host(force=False):
     tests_bin = os.path.join(out_dir, "ref_integration_tests")
     ref = reference_root()
     if ref is None:
-        return [p for p in (frontend, executor, tests_bin) if os.path.exists(p)]
+        return [p for p in (frontend, executor, tests_bin, os.path.join(out_dir, "autograd_parity")) if os.path.exists(p)]
     os.makedirs(out_dir, exist_ok=True)
     obj_dir = os.path.join(OBJ, "ref")
     gen = os.path.join(obj_dir, "gen")
@@ -176,7 +176,18 @@ def build_reference_host(force=False):
         _run([gxx] + tflags + ["-I", shim, "-I", tdir, "-o", tests_bin, main_src] + tsrcs +
              ["-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl", "-lpthread",
               "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
-    return [frontend, executor, tests_bin]
+    # whole-graph parity (autograd included) between the B200 device and a CPU oracle device
+    parity_bin = os.path.join(out_dir, "autograd_parity")
+    parity_src = os.path.join(shim, "autograd_parity.cpp")
+    oracle_c = os.path.join(ROOT, "oracle", "builtins_oracle.c")
+    if force or _newer(parity_src, parity_bin, (executor, os.path.join(shim, "oracle_device.hpp"), oracle_c)):
+        oracle_o = os.path.join(obj_dir, "builtins_oracle.o")
+        _run(["/usr/bin/gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-c", oracle_c, "-o", oracle_o])
+        tflags = [f for f in flags if f != "-fno-exceptions"]
+        _run([gxx] + tflags + ["-I", shim, "-fopenmp", "-o", parity_bin, parity_src, oracle_o,
+                               "-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl",
+                               "-lpthread", "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
+    return [frontend, executor, tests_bin, parity_bin]
 
 
 def build_all(force=False, verbose=False):

@@ -45,3 +45,27 @@ def test_reference_integration_tests_pass_on_the_b200_device():
     out, (ran, failed, skipped, disabled) = run("--also_run_disabled_tests")
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
     assert (ran, failed, skipped, disabled) == (13, 0, 0, 0), out.stdout[-3000:]
+
+
+PARITY = os.path.join(ROOT, "polarai-framework_b200", "lib", "ref", "autograd_parity")
+
+
+@pytest.mark.skipif(not os.path.exists(PARITY), reason="autograd parity binary is not built")
+@pytest.mark.parametrize("batch", [1, 256])
+def test_reference_autograd_runs_through_the_executor_on_the_oracle_device(batch):
+    # CPU part: Graph::getGradient's gradient and weight-update graphs execute through the
+    # direct Executor on the oracle device; at batch 1 the result equals the analytic SGD step.
+    out = subprocess.run([PARITY, str(batch)], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "oracle device: 18 launches" in out.stdout
+    if batch == 1:
+        assert "analytic SGD step" in out.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [1, 256])
+def test_logistic_regression_with_reference_autograd_matches_the_oracle_device(batch):
+    assert os.path.exists(PARITY), "build the package where the reference tree is present"
+    out = subprocess.run([PARITY, str(batch)], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "PARITY OK" in out.stdout, out.stdout
