@@ -108,7 +108,10 @@ int polar_b200_fmulconcat(const float* gradient, const float* localDerivative,
  * Replaces PolarGraph/kernels/MatMulOp.cpp:36-85 and opencl/kernels.h:80-117.
  *
  * `workspace` is device scratch of `workspace_bytes` bytes, 256-byte aligned;
- * polar_b200_fmatmul_workspace_bytes gives the size this call needs (0 = none).
+ * polar_b200_fmatmul_workspace_bytes gives the size this call needs (0 = none;
+ * non-zero when the sum over k is cut into several work units whose partial
+ * products are added afterwards in a fixed order: narrow results with a long k,
+ * and tensor-core shapes with too few tiles to load every SM).
  * With workspace == NULL the call takes the scratch it needs from the
  * device's stream-ordered memory pool (cudaMallocAsync/cudaFreeAsync on
  * `stream`). */
@@ -163,14 +166,16 @@ int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
  * pipeline stage); passes is 3 (fp32-accurate three-product
  * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi != 0 makes the
  * split warps store the masked high parts explicitly instead of relying on the
- * tensor core ignoring the low 13 mantissa bits.  Fails with
+ * tensor core ignoring the low 13 mantissa bits; splits is the number of work
+ * units the k range of each tile is cut into (1 = none, 0 = the automatic choice;
+ * scratch for the partial products comes from the stream-ordered pool).  Fails with
  * POLAR_B200_ERR_UNSUPPORTED when the operands cannot be described to TMA
  * (bases not 16-byte aligned, or a contiguous extent that is not a multiple of
  * 4 floats). */
 int polar_b200_fmatmul_tc(int transLeft, int transRight, uint64_t m, uint64_t n,
                           uint64_t k, const float* left, const float* right,
                           float* out, int tile_n, int slab_k, int passes,
-                          int write_hi, void* stream);
+                          int write_hi, int splits, void* stream);
 
 /* Status word the kernels write when a bounded device-side wait gives up
  * (0 = none; 101..106 = which wait of the tensor-core matmul).  It lives in
@@ -186,6 +191,15 @@ int polar_b200_fmatmul_path(int transLeft, int transRight, uint64_t m,
                             uint64_t n, uint64_t k);
 
 /* ---- extended builtins (beside, never instead of, the ones above) -------- */
+
+/* fsigmoid_grad: out[i] = gradient[i] * ((1 - s[i]) * s[i]) where s is the OUTPUT of
+ * fsigmoid.  One pass over the three launches the reference's Sigmoid derivative
+ * compiles to - fadd(ones,1,s,-1), fmul(.,s), fmul(gradient,.)
+ * (src/operation/internal/SigmoidOperationInternal.cpp:107-135) - keeping their three
+ * roundings, so the result is bit-identical to the chain; 12 instead of 36 bytes per
+ * element.  Args as a builtin: T gradient, T sigmoidOut, T out. */
+int polar_b200_fsigmoid_grad(const float* gradient, const float* sigmoidOut,
+                             float* out, uint64_t n, void* stream);
 
 /* Sum of n floats into *sum (a device double, ADDED to: clear it first), with
  * warp-shuffle + one atomic per block.  Used to report the scalar mean of an

@@ -41,11 +41,12 @@ SIGNATURES = {
     "polar_b200_fsigmoid": (_i, [_p, _p, _u64, _p]),
     "polar_b200_fsigmoid_unclamped": (_i, [_p, _p, _u64, _p]),
     "polar_b200_flogloss": (_i, [_p, _p, _p, _u64, _p]),
+    "polar_b200_fsigmoid_grad": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fmulconcat": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_workspace_bytes": (_u64, [_i, _i, _u64, _u64, _u64]),
     "polar_b200_fmatmul_ffma": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p]),
-    "polar_b200_fmatmul_tc": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "polar_b200_fmatmul_tc": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "polar_b200_fmatmul_tn_small_n_static": (_i, [_i, _u64, _u64, _u64, _p, _p, _p, _p]),
     "polar_b200_static_scratch_bytes": (_u64, []),
     "polar_b200_fmatmul_path": (_i, [_i, _i, _u64, _u64, _u64]),

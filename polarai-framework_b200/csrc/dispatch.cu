@@ -7,7 +7,9 @@ namespace polar_b200 {
 int launch_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                 const float* right, float* out, cudaStream_t stream);
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-              const float* right, float* out, int bn, int bk, int passes, int write_hi, cudaStream_t stream);
+              const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
+              uint32_t splits, cudaStream_t stream);
+uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
 int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -32,6 +34,30 @@ int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
   return kPathFfma;
 }
 
+// The tensor-core path with `splits` work units per tile; scratch for the partial
+// products comes from the caller's workspace or, without one, from the
+// stream-ordered pool.
+int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
+           float* out, int bn, int bk, int passes, int write_hi, uint32_t splits, void* workspace,
+           uint64_t workspace_bytes, cudaStream_t stream) {
+  if (splits <= 1) return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, stream);
+  const uint64_t need = (uint64_t)splits * m * n * sizeof(float);
+  if (workspace) {
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
+    return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(workspace),
+                     splits, stream);
+  }
+  void* ws = nullptr;
+  cudaError_t e = cudaMallocAsync(&ws, need, stream);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+  int rc = launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(ws), splits,
+                     stream);
+  e = cudaFreeAsync(ws, stream);
+  if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+  return rc;
+}
+
 int check_mm(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
              const float* right, float* out) {
   if ((tl != 0 && tl != 1) || (tr != 0 && tr != 1))
@@ -53,7 +79,12 @@ extern "C" {
 uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
   const float* al = reinterpret_cast<const float*>(256);
   int kind = skinny_kind(tl, tr, m, n, k, al, al, al);
-  return kind ? skinny_workspace_bytes(kind, m, n, k) : 0;
+  if (kind) return skinny_workspace_bytes(kind, m, n, k);
+  if (choose_path(tl, tr, m, n, k, al, al, al) == kPathTc) {
+    uint32_t s = tc_default_splits(m, n, k);
+    return s > 1 ? (uint64_t)s * m * n * sizeof(float) : 0;
+  }
+  return 0;
 }
 
 int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
@@ -72,7 +103,8 @@ int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const
   if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);  // empty sum
   switch (choose_path(tl, tr, m, n, k, left, right, out)) {
     case kPathTc:
-      return launch_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, as_stream(stream));
+      return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k), workspace,
+                    workspace_bytes, as_stream(stream));
     case kPathSkinny: {
       const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
       const uint64_t need = skinny_workspace_bytes(kind, m, n, k);
@@ -109,7 +141,7 @@ int polar_b200_fmatmul_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
 
 int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                           const float* right, float* out, int tile_n, int slab_k, int passes,
-                          int write_hi, void* stream) {
+                          int write_hi, int splits, void* stream) {
   clear_error();
   int rc = check_mm(tl, tr, m, n, k, left, right, out);
   if (rc) return rc;
@@ -120,7 +152,10 @@ int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, co
     return fail(POLAR_B200_ERR_INVALID, "passes must be 1 or 3 (13: issue-rate diagnostic)");
   if (!tc_shape_ok(tl, tr, m, n, k, left, right))
     return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
-  return launch_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, as_stream(stream));
+  if (splits < 0 || splits > 64 || (splits > 1 && ((m * n) & 3)))
+    return fail(POLAR_B200_ERR_INVALID, "splits must be 0 (automatic) or 1..64, and m*n a multiple of 4 when > 1");
+  const uint32_t s = splits == 0 ? tc_default_splits(m, n, k) : (uint32_t)splits;
+  return run_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, s, nullptr, 0, as_stream(stream));
 }
 
 int polar_b200_device_status(void) { return tc_status_word(); }
@@ -171,6 +206,12 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
   if (!std::strcmp(name, "fsigmoid")) {
     if (!pattern("TT") || !same(0, 1)) return fail(bad_args, "fsigmoid expects (T in, T out) of equal size");
     return polar_b200_fsigmoid(a[0].tensor.data, a[1].tensor.data, numel(a[1].tensor), stream);
+  }
+  if (!std::strcmp(name, "fsigmoid_grad")) {
+    if (!pattern("TTT") || !same(0, 2) || !same(1, 2))
+      return fail(bad_args, "fsigmoid_grad expects (T gradient, T sigmoidOut, T out) of equal size");
+    return polar_b200_fsigmoid_grad(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data, numel(a[2].tensor),
+                                    stream);
   }
   if (!std::strcmp(name, "fmulconcat")) {
     if (!pattern("TTT") || !same(1, 2) || numel(a[0].tensor) < 1)

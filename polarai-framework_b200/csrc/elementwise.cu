@@ -67,6 +67,15 @@ struct LogLossOp {
     return __fadd_rn(t0, -t1);
   }
 };
+// Extended builtin: the three launches the reference's Sigmoid derivative compiles to
+// (SigmoidOperationInternal.cpp:107-135: fadd(ones,1,s,-1) -> fmul(.,s) -> fmul(grad,.))
+// in one pass, with the same three roundings, so the result is bit-identical.
+struct SigmoidGradOp {
+  __device__ __forceinline__ float operator()(float g, float s) const {
+    float one_minus = __fadd_rn(__fmul_rn(1.0f, 1.0f), __fmul_rn(s, -1.0f));
+    return __fmul_rn(g, __fmul_rn(one_minus, s));
+  }
+};
 struct ScaleByFirstOp {  // fmulconcat: the scalar is read once per thread
   float g;
   __device__ __forceinline__ float operator()(float l, float) const { return __fmul_rn(g, l); }
@@ -267,6 +276,11 @@ int polar_b200_fsigmoid_unclamped(const float* in, float* out, uint64_t n, void*
 int polar_b200_flogloss(const float* predicted, const float* groundTruth, float* out, uint64_t n,
                         void* stream) {
   return launch_ew<2>("flogloss", LogLossOp{}, predicted, groundTruth, out, n, stream);
+}
+
+int polar_b200_fsigmoid_grad(const float* gradient, const float* sigmoidOut, float* out, uint64_t n,
+                             void* stream) {
+  return launch_ew<2>("fsigmoid_grad", SigmoidGradOp{}, gradient, sigmoidOut, out, n, stream);
 }
 
 int polar_b200_fmulconcat(const float* gradient, const float* localDerivative, float* out,

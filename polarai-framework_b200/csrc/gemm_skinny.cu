@@ -6,8 +6,9 @@
 // memory or registers.
 //
 //   small_n, left K-contiguous  (left stored [m,k]):   C[m, n<=16] = L . R
-//       one warp per group of 4 rows; lanes walk k four floats at a time; the
-//       k-slab of R sits transposed in shared memory; warp-shuffle reduction.
+//       one warp per group of 4 rows; lanes walk k four floats at a time; R sits
+//       transposed in shared memory - all of it, loaded once per persistent CTA,
+//       when it fits, else one k-slab at a time; warp-shuffle reduction.
 //   small_n, left M-contiguous  (left stored [k,m]):   C[m, n<=16] = L^T . R
 //       the sum runs over the long (batch) dimension: the k range is split over
 //       CTAs, each thread owns 4 consecutive m and n accumulators each, partial
@@ -97,6 +98,95 @@ small_n_kmajor_kernel(const float* __restrict__ left, const float* __restrict__ 
 #pragma unroll
         for (int j = 0; j < NP; ++j)
           if ((uint64_t)j < n) out[row * n + j] = acc[r][j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- small n, K-major left, R resident
+
+// When the whole small operand fits in shared memory (n_padded * (k + 4) floats, e.g.
+// 164 KB for the MLP's 4096 x 10 output layer) it is loaded ONCE per CTA; one
+// persistent 512-thread CTA per SM then streams row groups of the large operand
+// with no barrier in the loop.  Each warp owns 4 rows at a time and keeps two
+// k chunks (8 x 128-bit loads per lane) in flight.
+constexpr int kResidentThreads = 512;
+
+template <int NP>
+__global__ void __launch_bounds__(kResidentThreads, 1)
+small_n_kmajor_resident_kernel(const float* __restrict__ left, const float* __restrict__ right,
+                               float* __restrict__ out, uint64_t m, uint64_t n, uint64_t k, uint64_t rsk,
+                               uint64_t rsj) {
+  extern __shared__ float bs[];   // [NP][k + 4], k contiguous
+  const uint32_t kpad = (uint32_t)k + 4;
+  for (uint64_t e = threadIdx.x; e < (uint64_t)NP * k; e += kResidentThreads) {
+    uint32_t j = (uint32_t)(e % NP), kk = (uint32_t)(e / NP);
+    bs[j * kpad + kk] = ((uint64_t)j < n) ? right[(uint64_t)kk * rsk + (uint64_t)j * rsj] : 0.f;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t warps_total = (uint64_t)gridDim.x * (kResidentThreads / 32);
+  const uint64_t groups = (m + ROWS_PER_WARP - 1) / ROWS_PER_WARP;
+  for (uint64_t g = (uint64_t)blockIdx.x * (kResidentThreads / 32) + warp; g < groups; g += warps_total) {
+    const uint64_t row0 = g * ROWS_PER_WARP;
+    float acc[ROWS_PER_WARP][NP];
+#pragma unroll
+    for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+      for (int j = 0; j < NP; ++j) acc[r][j] = 0.f;
+    const float* rows[ROWS_PER_WARP];
+#pragma unroll
+    for (int r = 0; r < ROWS_PER_WARP; ++r)
+      rows[r] = left + ((row0 + r < m) ? (row0 + r) : (m - 1)) * k;   // clamped: results of padding rows are dropped
+    for (uint32_t kk = lane * 4; kk < (uint32_t)k; kk += 256) {
+      float4 a0[ROWS_PER_WARP], a1[ROWS_PER_WARP];
+      const bool second = kk + 128 < (uint32_t)k;
+#pragma unroll
+      for (int r = 0; r < ROWS_PER_WARP; ++r) {
+        a0[r] = __ldcs(reinterpret_cast<const float4*>(rows[r] + kk));
+        a1[r] = second ? __ldcs(reinterpret_cast<const float4*>(rows[r] + kk + 128))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float4 b0 = *reinterpret_cast<const float4*>(&bs[j * kpad + kk]);
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_WARP; ++r) {
+          acc[r][j] = fmaf(a0[r].x, b0.x, acc[r][j]);
+          acc[r][j] = fmaf(a0[r].y, b0.y, acc[r][j]);
+          acc[r][j] = fmaf(a0[r].z, b0.z, acc[r][j]);
+          acc[r][j] = fmaf(a0[r].w, b0.w, acc[r][j]);
+        }
+      }
+      if (second) {
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+          const float4 b1 = *reinterpret_cast<const float4*>(&bs[j * kpad + kk + 128]);
+#pragma unroll
+          for (int r = 0; r < ROWS_PER_WARP; ++r) {
+            acc[r][j] = fmaf(a1[r].x, b1.x, acc[r][j]);
+            acc[r][j] = fmaf(a1[r].y, b1.y, acc[r][j]);
+            acc[r][j] = fmaf(a1[r].z, b1.z, acc[r][j]);
+            acc[r][j] = fmaf(a1[r].w, b1.w, acc[r][j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        float v = acc[r][j];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        acc[r][j] = v;
+      }
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < ROWS_PER_WARP; ++r)
+        if (row0 + r < m)
+#pragma unroll
+          for (int j = 0; j < NP; ++j)
+            if ((uint64_t)j < n) out[(row0 + r) * n + j] = acc[r][j];
     }
   }
 }
@@ -250,6 +340,23 @@ uint32_t splits_for(uint64_t m, uint64_t k) {
 template <int NP>
 int launch_small_n_k(const float* l, const float* r, float* out, uint64_t m, uint64_t n, uint64_t k,
                      uint64_t rsk, uint64_t rsj, cudaStream_t st) {
+  // whole small operand resident in shared memory when it fits (and there are rows
+  // enough to keep every SM busy); otherwise k slabs
+  const size_t resident = (size_t)NP * (k + 4) * sizeof(float);
+  if (resident <= 200 * 1024 && m >= 4096) {
+    static bool res_attr[64] = {false};
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d >= 0 && d < 64 && !res_attr[d]) {
+      cudaError_t e = cudaFuncSetAttribute(small_n_kmajor_resident_kernel<NP>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(small_n resident)", e);
+      res_attr[d] = true;
+    }
+    small_n_kmajor_resident_kernel<NP><<<(unsigned)sm_count(), kResidentThreads, resident, st>>>(
+        l, r, out, m, n, k, rsk, rsj);
+    return check_launch("fmatmul_small_n_resident");
+  }
   const size_t smem = (size_t)NP * KT_PAD * sizeof(float);
   static bool attr_done[64] = {false};
   int dev = 0;

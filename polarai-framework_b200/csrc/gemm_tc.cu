@@ -29,6 +29,11 @@
 // (the only MN-major layout tcgen05 takes for 32-bit operands); only the shared-memory
 // descriptors, the instruction descriptor's major bits and the TMA boxes differ.
 //
+// Shapes with too few tiles to load every SM evenly (e.g. 784 x 4096 with a k of
+// 65536: 112 tiles on 148 SMs) are cut along k into up to 8 work units per tile;
+// each unit writes its partial product to scratch and a second kernel adds them
+// in a fixed order.
+//
 // Every wait on an mbarrier is bounded: after about two seconds of polling the
 // waiter records a code in the status word, raises the CTA's abort flag, and
 // every role leaves its loop; the CTA then lets copies in flight land, frees its
@@ -203,6 +208,8 @@ struct Params {
   int write_hi;     // split warps also store the masked hi part in place
   int* status;      // device-visible status word
   uint32_t tiles_m, tiles_n;
+  uint32_t splits;  // work units per tile: the k range is cut into `splits` parts
+  float* partial;   // [splits][m][n] partial products when splits > 1
 };
 
 // Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
@@ -240,7 +247,11 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
-  const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+  // A work unit is (tile, split): tile = unit / splits, the split takes slabs
+  // [split * num_kb / splits, (split + 1) * num_kb / splits).
+  const uint32_t num_tiles = p.tiles_m * p.tiles_n * p.splits;
+  auto slab_begin = [&](uint32_t unit) { return (uint32_t)(((uint64_t)(unit % p.splits) * num_kb) / p.splits); };
+  auto slab_end = [&](uint32_t unit) { return (uint32_t)(((uint64_t)(unit % p.splits + 1) * num_kb) / p.splits); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -271,8 +282,8 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m0, n0;
-        tile_coords(t, p.tiles_m, p.tiles_n, BN, &m0, &n0);
-        for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+        tile_coords(t / p.splits, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+        for (uint32_t kb = slab_begin(t), kb_end = slab_end(t); kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101)) { ok = false; break; }
@@ -320,7 +331,8 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + as * BN;
-        for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+        const uint32_t kb_first = slab_begin(t);
+        for (uint32_t kb = kb_first, kb_end = slab_end(t); kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102);
@@ -335,7 +347,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           for (int kk = 0; kk < BK / 8; ++kk) {
             const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
             const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
-            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, (kb | (uint32_t)kk) ? 1u : 0u);
+            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, ((kb - kb_first) | (uint32_t)kk) ? 1u : 0u);
           }
           if (p.passes == 3) {
             ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103);
@@ -374,7 +386,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (uint32_t kb = 0; kb < num_kb; ++kb, ++it) {
+        for (uint32_t kb = slab_begin(t), kb_end = slab_end(t); kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) { ok = false; break; }
@@ -405,11 +417,13 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // Warp w may touch tensor-memory lanes [32*(w%4), 32*(w%4)+32): four
     // consecutive warps cover the 128 rows of the tile.
     const int q = warp & 3;
-    const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
     uint32_t tile_iter = 0;
     for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_iter) {
       int m0, n0;
-      tile_coords(t, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+      tile_coords(t / p.splits, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+      float* const out_base = p.splits > 1 ? p.partial + (uint64_t)(t % p.splits) * p.m * p.n : p.out;
       const uint32_t as = tile_iter & 1u;
       if (!mbar_wait(acc_full(as), (tile_iter >> 1) & 1u, abort_flag, p.status, 105)) break;
       tc_fence_after();
@@ -421,7 +435,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
         tmem_ld_wait();
         if (row < p.m) {
-          float* dst = p.out + row * p.n + n0 + c;
+          float* dst = out_base + row * p.n + n0 + c;
           if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -521,9 +535,41 @@ bool shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
   return m > 0 && n > 0 && k > 0;
 }
 
+// out[e] = sum of the splits' partial products, ascending split index (fixed order).
+__global__ void __launch_bounds__(256) add_splits_kernel(const float4* __restrict__ partial, float4* __restrict__ out,
+                                                         uint64_t nvec, uint32_t splits) {
+  const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= nvec) return;
+  float4 s = __ldcs(partial + i);
+  for (uint32_t sp = 1; sp < splits; ++sp) {
+    float4 v = __ldcs(partial + (uint64_t)sp * nvec + i);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  out[i] = s;
+}
+
+// How many ways to cut k so that the persistent grid is evenly loaded: the smallest
+// count up to 8 whose last wave is at least 90 % full, else the best one.  Needs
+// m*n to be a multiple of 4 for the vectorised sum of the partial products.
+uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) {
+  const uint64_t sms = (uint64_t)sm_count();
+  if (((m * n) & 3) != 0 || tiles >= 8 * sms) return 1;
+  double best_eff = 0.0;
+  uint32_t best = 1;
+  for (uint32_t s = 1; s <= 8; ++s) {
+    if (num_kb / s < 32) break;                       // keep at least 32 slabs per unit
+    const uint64_t units = tiles * s;
+    const double eff = (double)units / (double)(((units + sms - 1) / sms) * sms);
+    if (eff >= 0.9) return s;
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  return best;
+}
+
 template <int BN, int BK>
 static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                      const float* right, float* out, int passes, int write_hi, cudaStream_t stream) {
+                      const float* right, float* out, int passes, int write_hi, float* ws, uint32_t splits,
+                      cudaStream_t stream) {
   using C = Cfg<BN, BK>;
   static_assert(C::kStages >= 2 && C::kSmemBytes <= 227 * 1024, "stage ring must fit shared memory");
   int dev = 0;
@@ -552,20 +598,37 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   uint64_t tm = (m + BM - 1) / BM, tn = (n + BN - 1) / BN;
   if (tm * tn > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   p.tiles_m = (uint32_t)tm; p.tiles_n = (uint32_t)tn;
-  uint64_t tiles = tm * tn;
-  unsigned grid = (unsigned)(tiles < (uint64_t)sm_count() ? tiles : (uint64_t)sm_count());   // one CTA per SM
+  const uint64_t num_kb = (k + BK - 1) / BK;
+  if (splits < 1 || !ws || splits > num_kb) splits = 1;
+  p.splits = splits;
+  p.partial = splits > 1 ? ws : nullptr;
+  uint64_t units = tm * tn * splits;
+  if (units > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
+  unsigned grid = (unsigned)(units < (uint64_t)sm_count() ? units : (uint64_t)sm_count());   // one CTA per SM
   fmatmul_tc_kernel<BN, BK><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
-  return check_launch("fmatmul_tc");
+  rc = check_launch("fmatmul_tc");
+  if (rc || splits == 1) return rc;
+  const uint64_t nvec = m * n / 4;
+  add_splits_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(ws),
+                                                                       reinterpret_cast<float4*>(out), nvec, splits);
+  return check_launch("fmatmul_add_splits");
 }
 
 }  // namespace tc
 
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-              const float* right, float* out, int bn, int bk, int passes, int write_hi, cudaStream_t stream) {
-  if (bn == 128 && bk == 32) return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
-  if (bn == 128) return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
-  if (bk == 32) return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
-  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, stream);
+              const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
+              uint32_t splits, cudaStream_t stream) {
+  if (bn == 128 && bk == 32)
+    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
+  if (bn == 128) return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
+  if (bk == 32) return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
+  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
+}
+
+// Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.
+uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k) {
+  return tc::choose_splits(((m + 127) / 128) * ((n + 255) / 256), (k + 15) / 16, m, n);
 }
 
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,

@@ -96,11 +96,11 @@ class DeviceBuiltins:
                       _ptr(out), _stream())
         return out
 
-    def fmatmul_tc(self, tl, tr, left, right, out, tile_n=256, slab_k=16, passes=3, write_hi=0):
+    def fmatmul_tc(self, tl, tr, left, right, out, tile_n=256, slab_k=16, passes=3, write_hi=0, splits=1):
         _chk(left, right, out)
         m, n, k = matmul_dims(tl, tr, left.shape, right.shape)
         self.lib.call("polar_b200_fmatmul_tc", int(tl), int(tr), m, n, k, _ptr(left), _ptr(right),
-                      _ptr(out), tile_n, slab_k, passes, write_hi, _stream())
+                      _ptr(out), tile_n, slab_k, passes, write_hi, splits, _stream())
         return out
 
     def device_status(self):

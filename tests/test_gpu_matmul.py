@@ -65,6 +65,7 @@ SHAPES = [
     (1024, 1024, 1024),
     (2304, 2048, 96),                                       # 144 or 288 tiles: several tiles per persistent CTA
     (4224, 1280, 64),
+    (1024, 1024, 2048), (784, 512, 4096),                   # few tiles, long k: the default path cuts k into work units
 ]
 
 
