@@ -224,7 +224,7 @@ def run_mlp(args):
     import __graft_entry__ as ge
     pkg = ge.load_package()
     from polarai_framework_b200.data_parallel import init_from_env, make_allreduce, shard_rows
-    from polarai_framework_b200.program import DeviceExecutor, mlp_program
+    from polarai_framework_b200.program import DeviceExecutor, fuse_program, mlp_program
 
     rank, world, local = init_from_env()
     if world != args.gpus:
@@ -237,6 +237,8 @@ def run_mlp(args):
     W1, W2 = mlp_weights(rng)                               # identical on every rank
     Xs, Ys = mlp_inputs(np.random.default_rng(1000 + rank), per)   # this rank's rows
     program = mlp_program(per, N_IN, N_HIDDEN, N_OUT, LR)
+    if args.fused:
+        program = fuse_program(program)
     ex = DeviceExecutor(program, dev, make_allreduce(world))
     x_host = torch.from_numpy(Xs).pin_memory()
     y_host = torch.from_numpy(Ys).pin_memory()
@@ -362,7 +364,7 @@ def run_mlp(args):
     total_ops_ms = sum(times)
     by_kernel = {}
     for (kernel, a), t in zip(program.ops, times):
-        key = kernel if not kernel.startswith("fmatmul") else f"{kernel}:{a[2]}"
+        key = kernel if not kernel.startswith("fmatmul") else f"{kernel}:{a[-1]}"
         d = by_kernel.setdefault(key, {"launches": 0, "ms": 0.0})
         d["launches"] += 1
         d["ms"] += t
@@ -396,6 +398,8 @@ def run_mlp(args):
             "config": {"workload": "mlp_784_4096_10_fwd_bwd_sgd", "global_batch": GLOBAL_BATCH,
                        "per_gpu_batch": per, "lr": LR, "parallelism": f"dp{world}",
                        "cuda_graph": graph is not None,
+                       "builtins": "extended (fused, bit-identical results)" if args.fused
+                       else "the reference's builtin chain, one launch per builtin",
                        "l2": "per-step working set (X 205 MB/GPU-share, seven Bx4096 activations) "
                              "exceeds the 126 MB L2 at every N"},
             "flop_per_sample": FLOP_PER_SAMPLE, "tflops": value * FLOP_PER_SAMPLE / 1e12,
@@ -404,6 +408,21 @@ def run_mlp(args):
             "launches_per_step": launches_per_step,
             "clocks": clocks, "e2e": e2e, "roofline": roofline,
             "breakdown_ms": {k: round(v["ms"], 4) for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1]["ms"])}}
+    if not args.fused and not args.no_extras:
+        # The same step with the extended (fused) builtins: bit-identical results in 13
+        # launches instead of 20.  Every rank runs it (its all-reduces are collective).
+        fex = DeviceExecutor(fuse_program(program), dev, make_allreduce(world))
+        fex.t["X"].copy_(ex.t["X"]), fex.t["Y"].copy_(ex.t["Y"])
+        fex.t["W1"].copy_(w1), fex.t["W2"].copy_(w2)
+        for _ in range(3):
+            fex.run()
+        fms = time_region(torch, fex.run, args.steps, dist, world) / args.steps
+        line["fused_program"] = {"value": GLOBAL_BATCH / (fms / 1e3), "unit": "samples/s", "ms_per_step": fms,
+                                 "launches_per_step": fex.program.launches(), "cuda_graph": False,
+                                 "note": "fmatmul+fsigmoid, fmatmul+sigmoid derivative and the sigmoid "
+                                         "derivative chain as single launches; every program output is "
+                                         "bit-identical to the unfused program"}
+        del fex
     if rank == 0 and world == 1 and not args.no_extras:
         line["cpu_baseline"] = cpu_mlp_baseline(2048, steps=1)[0]
         # the bandwidth numbers first: the GEMM loop leaves the GPU at its power cap
@@ -546,6 +565,8 @@ def main():
                     help="gemm: m=n=k (default 8192); elementwise: log2 of the element count (default 28)")
     ap.add_argument("--batch", type=int, default=0,
                     help="mlp: global batch override for profiling small cases (default 65536, the metric's)")
+    ap.add_argument("--fused", action="store_true",
+                    help="mlp: run the program with the extended (fused) builtins; results are bit-identical")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

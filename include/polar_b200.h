@@ -201,6 +201,31 @@ int polar_b200_fmatmul_path(int transLeft, int transRight, uint64_t m,
 int polar_b200_fsigmoid_grad(const float* gradient, const float* sigmoidOut,
                              float* out, uint64_t n, void* stream);
 
+/* fmatmul with the builtin that follows it fused in, bit-identical to launching the
+ * two builtins one after the other (the product is rounded to fp32 before the
+ * second step either way):
+ *   fmatmul_sigmoid       out = fsigmoid(L'.R')              - the hidden layer forward;
+ *                         in the tensor-core kernel the epilogue warps apply it while
+ *                         the next tile's k loop runs, and the pre-activation is never
+ *                         written;
+ *   fmatmul_sigmoid_grad  out = (L'.R') * ((1 - s) * s)      - the hidden layer's
+ *                         backward, s = fsigmoid output of the forward pass; in the
+ *                         small-k kernel the gradient w.r.t. the activations is never
+ *                         written.
+ * Shapes served by a kernel without a fused form run the two builtins in sequence
+ * (the second one in place).  Native names for polar_b200_launch_by_name:
+ * "fmatmul_x_y_sigmoid" (T left, T right, T out) and "fmatmul_x_y_sigmoid_grad"
+ * (T left, T right, T sigmoidOut, T out). */
+int polar_b200_fmatmul_sigmoid(int transLeft, int transRight, uint64_t m, uint64_t n,
+                               uint64_t k, const float* left, const float* right,
+                               float* out, void* workspace, uint64_t workspace_bytes,
+                               void* stream);
+int polar_b200_fmatmul_sigmoid_grad(int transLeft, int transRight, uint64_t m,
+                                    uint64_t n, uint64_t k, const float* left,
+                                    const float* right, const float* sigmoidOut,
+                                    float* out, void* workspace,
+                                    uint64_t workspace_bytes, void* stream);
+
 /* Sum of n floats into *sum (a device double, ADDED to: clear it first), with
  * warp-shuffle + one atomic per block.  Used to report the scalar mean of an
  * elementwise flogloss output; the reference has no reduction builtin. */

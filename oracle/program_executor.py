@@ -43,8 +43,17 @@ class OracleExecutor:
                 r = o.ffill(args[0], int(np.prod(shape)))
             elif kernel == "fmulconcat":
                 r = o.fmulconcat(g(0).ravel(), g(1).ravel())
+            elif kernel == "fsigmoid_grad":
+                # the reference's derivative chain, launch by launch
+                one = o.ffill(1.0, g(1).size)
+                r = o.fmul(g(0).ravel(), o.fmul(o.fadd(one, 1.0, g(1).ravel(), -1.0), g(1).ravel()))
             elif kernel.startswith("fmatmul_"):
                 r = o.fmatmul(kernel[8] == "t", kernel[10] == "t", g(0), g(1))
+                if kernel.endswith("_sigmoid"):
+                    r = o.fsigmoid(r.ravel())
+                elif kernel.endswith("_sigmoid_grad"):
+                    one = o.ffill(1.0, g(2).size)
+                    r = o.fmul(r.ravel(), o.fmul(o.fadd(one, 1.0, g(2).ravel(), -1.0), g(2).ravel()))
             else:
                 raise KeyError(kernel)
             t[out] = np.asarray(r, np.float32).reshape(shape)

@@ -44,6 +44,8 @@ SIGNATURES = {
     "polar_b200_fsigmoid_grad": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fmulconcat": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
+    "polar_b200_fmatmul_sigmoid": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
+    "polar_b200_fmatmul_sigmoid_grad": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_workspace_bytes": (_u64, [_i, _i, _u64, _u64, _u64]),
     "polar_b200_fmatmul_ffma": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p]),
     "polar_b200_fmatmul_tc": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _i, _i, _i, _p]),

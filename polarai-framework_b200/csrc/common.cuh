@@ -30,4 +30,26 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+#ifdef __CUDACC__
+// fsigmoid's arithmetic, shared by the elementwise builtin and the fused matmul
+// epilogue so that both give the same bits: r = 1/(1+exp(-x)), then the reference's
+// clamp to [1e-5, 1-1e-5] (opencl/kernels.h:141-156 of the reference).
+__device__ __forceinline__ float sigmoid_clamped(float x) {
+  const float eps = 1e-5f;
+  // 1/d as the correctly rounded reciprocal: the same bits as IEEE division of 1 by d,
+  // without the division's slow-path branch (which keeps independent elements from
+  // being interleaved in the matmul epilogue).
+  float r = __frcp_rn(__fadd_rn(1.0f, expf(-x)));
+  const float hi = __fadd_rn(1.0f, -eps);
+  r = (fabsf(__fadd_rn(r, -1.0f)) < eps) ? hi : ((fabsf(r) < eps) ? eps : r);
+  return r;
+}
+// The reference's Sigmoid derivative chain on one element, with its three roundings:
+// fadd(ones,1,s,-1) -> fmul(.,s) -> fmul(grad,.)  (SigmoidOperationInternal.cpp:107-135).
+__device__ __forceinline__ float sigmoid_grad_chain(float g, float s) {
+  float one_minus = __fadd_rn(__fmul_rn(1.0f, 1.0f), __fmul_rn(s, -1.0f));
+  return __fmul_rn(g, __fmul_rn(one_minus, s));
+}
+#endif
+
 }  // namespace polar_b200

@@ -8,7 +8,7 @@ int launch_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
                 const float* right, float* out, cudaStream_t stream);
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, cudaStream_t stream);
+              uint32_t splits, int epilogue, cudaStream_t stream);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
@@ -16,7 +16,7 @@ int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
                 const float* right, const float* out);
 uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k);
 int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                  const float* right, float* out, float* ws, cudaStream_t st);
+                  const float* right, float* out, float* ws, cudaStream_t st, const float* sig);
 int tc_status_word();
 void tc_status_clear();
 
@@ -39,20 +39,21 @@ int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
 // stream-ordered pool.
 int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
            float* out, int bn, int bk, int passes, int write_hi, uint32_t splits, void* workspace,
-           uint64_t workspace_bytes, cudaStream_t stream) {
-  if (splits <= 1) return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, stream);
+           uint64_t workspace_bytes, cudaStream_t stream, int epilogue = 0) {
+  if (splits <= 1)
+    return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream);
   const uint64_t need = (uint64_t)splits * m * n * sizeof(float);
   if (workspace) {
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
       return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
     return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(workspace),
-                     splits, stream);
+                     splits, epilogue, stream);
   }
   void* ws = nullptr;
   cudaError_t e = cudaMallocAsync(&ws, need, stream);
   if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
   int rc = launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(ws), splits,
-                     stream);
+                     epilogue, stream);
   e = cudaFreeAsync(ws, stream);
   if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
   return rc;
@@ -93,33 +94,52 @@ int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) 
   return choose_path(tl, tr, m, n, k, al, al, al);
 }
 
-int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                       const float* right, float* out, void* workspace, uint64_t workspace_bytes,
-                       void* stream) {
+// fused == 0: out = L.R;  1: out = fsigmoid(L.R);  2: out = (L.R) * ((1 - sig) * sig).
+// Where the kernel that serves the shape has no fused form, the builtin that follows
+// is launched on the result in place (same bits either way).
+static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                        const float* right, float* out, void* workspace, uint64_t workspace_bytes,
+                        void* stream, int fused, const float* sig) {
   clear_error();
   int rc = check_mm(tl, tr, m, n, k, left, right, out);
   if (rc) return rc;
   if (m == 0 || n == 0) return POLAR_B200_OK;
-  if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);  // empty sum
-  switch (choose_path(tl, tr, m, n, k, left, right, out)) {
+  if (k == 0) {
+    rc = polar_b200_ffill(0.0f, out, m * n, stream);  // empty sum
+    if (rc || fused == 0) return rc;
+    return fused == 1 ? polar_b200_fsigmoid(out, out, m * n, stream)
+                      : polar_b200_fsigmoid_grad(out, sig, out, m * n, stream);
+  }
+  const int path = choose_path(tl, tr, m, n, k, left, right, out);
+  const int kind0 = path == kPathSkinny ? skinny_kind(tl, tr, m, n, k, left, right, out) : 0;
+  const bool fused_in_kernel = (fused == 1 && path == kPathTc) || (fused == 2 && kind0 == 3);
+  if (fused != 0 && !fused_in_kernel) {
+    rc = fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 0, nullptr);
+    if (rc) return rc;
+    return fused == 1 ? polar_b200_fsigmoid(out, out, m * n, stream)
+                      : polar_b200_fsigmoid_grad(out, sig, out, m * n, stream);
+  }
+  switch (path) {
     case kPathTc:
       return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k), workspace,
-                    workspace_bytes, as_stream(stream));
+                    workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0);
     case kPathSkinny: {
       const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
       const uint64_t need = skinny_workspace_bytes(kind, m, n, k);
-      if (need == 0) return launch_skinny(kind, tl, tr, m, n, k, left, right, out, nullptr, as_stream(stream));
+      if (need == 0)
+        return launch_skinny(kind, tl, tr, m, n, k, left, right, out, nullptr, as_stream(stream),
+                             fused == 2 ? sig : nullptr);
       if (workspace) {
         if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
           return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
         return launch_skinny(kind, tl, tr, m, n, k, left, right, out, static_cast<float*>(workspace),
-                             as_stream(stream));
+                             as_stream(stream), nullptr);
       }
       // No workspace from the caller: take it from the stream-ordered pool.
       void* ws = nullptr;
       cudaError_t e = cudaMallocAsync(&ws, need, as_stream(stream));
       if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
-      rc = launch_skinny(kind, tl, tr, m, n, k, left, right, out, static_cast<float*>(ws), as_stream(stream));
+      rc = launch_skinny(kind, tl, tr, m, n, k, left, right, out, static_cast<float*>(ws), as_stream(stream), nullptr);
       e = cudaFreeAsync(ws, as_stream(stream));
       if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
       return rc;
@@ -127,6 +147,30 @@ int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const
     default:
       return launch_ffma(tl, tr, m, n, k, left, right, out, as_stream(stream));
   }
+}
+
+extern "C" {
+int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                       const float* right, float* out, void* workspace, uint64_t workspace_bytes,
+                       void* stream) {
+  return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 0, nullptr);
+}
+
+int polar_b200_fmatmul_sigmoid(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                               const float* right, float* out, void* workspace, uint64_t workspace_bytes,
+                               void* stream) {
+  return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 1, nullptr);
+}
+
+int polar_b200_fmatmul_sigmoid_grad(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                                    const float* right, const float* sigmoidOut, float* out, void* workspace,
+                                    uint64_t workspace_bytes, void* stream) {
+  if (m * n != 0 && !sigmoidOut) {
+    clear_error();
+    return fail(POLAR_B200_ERR_INVALID, "null sigmoid-output pointer");
+  }
+  return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 2, sigmoidOut);
+}
 }
 
 int polar_b200_fmatmul_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -219,10 +263,15 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     return polar_b200_fmulconcat(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data,
                                  numel(a[2].tensor), stream);
   }
-  if (!std::strncmp(name, "fmatmul_", 8) && std::strlen(name) == 11 && name[9] == '_' &&
+  if (!std::strncmp(name, "fmatmul_", 8) && std::strlen(name) >= 11 && name[9] == '_' &&
       (name[8] == 'f' || name[8] == 't') && (name[10] == 'f' || name[10] == 't')) {
-    if (!pattern("TTT")) return fail(bad_args, "fmatmul expects (T left, T right, T out)");
-    const polar_b200_tensor &l = a[0].tensor, &r = a[1].tensor, &o = a[2].tensor;
+    // "fmatmul_x_y", or the extended forms "fmatmul_x_y_sigmoid" (T left, T right, T out)
+    // and "fmatmul_x_y_sigmoid_grad" (T left, T right, T sigmoidOut, T out)
+    const char* suffix = name + 11;
+    const int fused = !*suffix ? 0 : !std::strcmp(suffix, "_sigmoid") ? 1 : !std::strcmp(suffix, "_sigmoid_grad") ? 2 : -1;
+    if (fused < 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "unknown native kernel name");
+    if (!pattern(fused == 2 ? "TTTT" : "TTT")) return fail(bad_args, "fmatmul expects (T left, T right, [T sigmoidOut,] T out)");
+    const polar_b200_tensor &l = a[0].tensor, &r = a[1].tensor, &o = a[fused == 2 ? 3 : 2].tensor;
     if (l.dims != 2 || r.dims != 2 || o.dims != 2) return fail(bad_args, "fmatmul operands must be 2-D");
     int tl = name[8] == 't', tr = name[10] == 't';
     // m = tl ? left.shape[1] : left.shape[0]; n = tr ? right.shape[0] : right.shape[1]
@@ -230,6 +279,12 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     uint64_t m = tl ? l.shape[1] : l.shape[0], k = tl ? l.shape[0] : l.shape[1];
     uint64_t n = tr ? r.shape[0] : r.shape[1], k2 = tr ? r.shape[1] : r.shape[0];
     if (k != k2 || o.shape[0] != m || o.shape[1] != n) return fail(bad_args, "fmatmul shapes do not agree");
+    if (fused == 2 && numel(a[2].tensor) != m * n) return fail(bad_args, "sigmoidOut must have the shape of out");
+    if (fused == 1)
+      return polar_b200_fmatmul_sigmoid(tl, tr, m, n, k, l.data, r.data, o.data, workspace, workspace_bytes, stream);
+    if (fused == 2)
+      return polar_b200_fmatmul_sigmoid_grad(tl, tr, m, n, k, l.data, r.data, a[2].tensor.data, o.data, workspace,
+                                             workspace_bytes, stream);
     return polar_b200_fmatmul(tl, tr, m, n, k, l.data, r.data, o.data, workspace, workspace_bytes, stream);
   }
   return fail(POLAR_B200_ERR_UNSUPPORTED, "unknown native kernel name");

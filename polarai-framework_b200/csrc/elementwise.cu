@@ -47,16 +47,8 @@ struct DivOp {
 template <bool CLAMP>
 struct SigmoidOp {
   __device__ __forceinline__ float operator()(float x, float) const {
-    const float eps = 1e-5f;
-    float r = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
-    if (CLAMP) {
-      if (fabsf(__fadd_rn(r, -1.0f)) < eps) {
-        r = __fadd_rn(1.0f, -eps);
-      } else if (fabsf(r) < eps) {
-        r = eps;
-      }
-    }
-    return r;
+    if (CLAMP) return sigmoid_clamped(x);
+    return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
   }
 };
 struct LogLossOp {
@@ -72,8 +64,7 @@ struct LogLossOp {
 // in one pass, with the same three roundings, so the result is bit-identical.
 struct SigmoidGradOp {
   __device__ __forceinline__ float operator()(float g, float s) const {
-    float one_minus = __fadd_rn(__fmul_rn(1.0f, 1.0f), __fmul_rn(s, -1.0f));
-    return __fmul_rn(g, __fmul_rn(one_minus, s));
+    return sigmoid_grad_chain(g, s);
   }
 };
 struct ScaleByFirstOp {  // fmulconcat: the scalar is read once per thread

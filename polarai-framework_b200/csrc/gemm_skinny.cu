@@ -282,7 +282,7 @@ template <int KP>
 __global__ void __launch_bounds__(kThreads)
 small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, float* __restrict__ out,
                uint64_t m, uint64_t n, uint64_t k, uint64_t lsi, uint64_t lsk, uint64_t rsk,
-               uint64_t rsj, int vec_store) {
+               uint64_t rsj, int vec_store, const float* __restrict__ sig) {
   __shared__ float as[RK][KP];
   const uint64_t j0 = ((uint64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
   const uint64_t row0 = (uint64_t)blockIdx.y * RK;
@@ -312,6 +312,20 @@ small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, 
       c3 = fmaf(a, b[3][kk], c3);
     }
     float* dst = out + (row0 + r) * n + j0;
+    if (sig) {
+      // fused Sigmoid derivative: out = product * ((1 - s) * s), s = fsigmoid output
+      const float* sp = sig + (row0 + r) * n + j0;
+      if (vec_store && j0 + 4 <= n) {
+        float4 sv = __ldcs(reinterpret_cast<const float4*>(sp));
+        c0 = sigmoid_grad_chain(c0, sv.x); c1 = sigmoid_grad_chain(c1, sv.y);
+        c2 = sigmoid_grad_chain(c2, sv.z); c3 = sigmoid_grad_chain(c3, sv.w);
+      } else {
+        c0 = sigmoid_grad_chain(c0, sp[0]);
+        if (j0 + 1 < n) c1 = sigmoid_grad_chain(c1, sp[1]);
+        if (j0 + 2 < n) c2 = sigmoid_grad_chain(c2, sp[2]);
+        if (j0 + 3 < n) c3 = sigmoid_grad_chain(c3, sp[3]);
+      }
+    }
     if (vec_store && j0 + 4 <= n) {
       __stcs(reinterpret_cast<float4*>(dst), make_float4(c0, c1, c2, c3));
     } else {
@@ -414,7 +428,7 @@ uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k) {
 }
 
 int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                  const float* right, float* out, float* ws, cudaStream_t st) {
+                  const float* right, float* out, float* ws, cudaStream_t st, const float* sig) {
   using namespace skinny;
   const uint64_t rsk = tr ? 1 : n, rsj = tr ? k : 1;
   if (kind == 1 || kind == 2) {
@@ -442,13 +456,13 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
     return fail(POLAR_B200_ERR_UNSUPPORTED, "skinny matmul: more than 65535 row blocks");
   }
   dim3 grid((unsigned)gx, (unsigned)gy);
-  int vec = ((n & 3) == 0) && aligned16(out);
+  int vec = ((n & 3) == 0) && aligned16(out) && (!sig || aligned16(sig));
   if (k <= 4)
-    small_k_kernel<4><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec);
+    small_k_kernel<4><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec, sig);
   else if (k <= 10)
-    small_k_kernel<10><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec);
+    small_k_kernel<10><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec, sig);
   else
-    small_k_kernel<16><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec);
+    small_k_kernel<16><<<grid, kThreads, 0, st>>>(left, right, out, m, n, k, lsi, lsk, rsk, rsj, vec, sig);
   return check_launch("fmatmul_small_k");
 }
 
@@ -518,7 +532,7 @@ int polar_b200_fmatmul_tn_small_n_static(int transRight, uint64_t m, uint64_t n,
   if (!scratch) return rc;
   // Every partial sum the reduction reads is written by the first kernel of this
   // call, so nothing in the scratch has to be cleared beforehand.
-  return launch_skinny(2, 1, transRight, m, n, k, left, right, out, scratch, as_stream(stream));
+  return launch_skinny(2, 1, transRight, m, n, k, left, right, out, scratch, as_stream(stream), nullptr);
 }
 
 }  // extern "C"

@@ -18,8 +18,10 @@
 //              commits to mbarriers to free stages and to publish the tile;
 //   warps 2-9  split warps: read each landed slab, write the lo part
 //              (and, when asked, the masked hi part in place) for the async proxy;
-//   warps 10-13 epilogue: tcgen05.ld the finished accumulator and store C rows
-//              with bounds checks, then hand the accumulator back.
+//   warps 10-17 epilogue: tcgen05.ld the finished accumulator (two warps per
+//              32-lane quarter, half of the columns each), apply the fused
+//              activation if asked, store C rows with bounds checks, then hand the
+//              accumulator back.
 // The hi*hi product of a slab is issued as soon as TMA has delivered it, so the
 // split warps' pass over the slab is hidden behind tensor-core work.
 //
@@ -49,7 +51,7 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int kSplitWarps = 8;                                  // warps 2..9
-constexpr int kEpilogueWarps = 4;                               // warps 10..13
+constexpr int kEpilogueWarps = 8;                               // warps 10..17
 constexpr int kThreads = 32 * (2 + kSplitWarps + kEpilogueWarps);
 constexpr int kGroupM = 16;                                     // tile raster: 16 row tiles share their column tiles
 
@@ -208,6 +210,7 @@ struct Params {
   int write_hi;     // split warps also store the masked hi part in place
   int* status;      // device-visible status word
   uint32_t tiles_m, tiles_n;
+  int epilogue;     // 0: store the product; 1: store fsigmoid(product) (only when splits == 1)
   uint32_t splits;  // work units per tile: the k range is cut into `splits` parts
   float* partial;   // [splits][m][n] partial products when splits > 1
 };
@@ -415,8 +418,10 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else {
     // ---------------- epilogue warps ----------------
     // Warp w may touch tensor-memory lanes [32*(w%4), 32*(w%4)+32): four
-    // consecutive warps cover the 128 rows of the tile.
+    // consecutive warps cover the 128 rows of the tile; the two warps of a lane
+    // quarter take half of the columns each.
     const int q = warp & 3;
+    const int half = (warp - (2 + kSplitWarps)) >> 2;
     const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
     uint32_t tile_iter = 0;
@@ -429,11 +434,15 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       tc_fence_after();
       const uint64_t row = (uint64_t)m0 + q * 32 + lane;
       const uint32_t tmem_acc = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
         if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
         tmem_ld_wait();
+        if (p.epilogue == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sigmoid_clamped(__uint_as_float(r[j])));
+        }
         if (row < p.m) {
           float* dst = out_base + row * p.n + n0 + c;
           if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
@@ -537,13 +546,16 @@ bool shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
 
 // out[e] = sum of the splits' partial products, ascending split index (fixed order).
 __global__ void __launch_bounds__(256) add_splits_kernel(const float4* __restrict__ partial, float4* __restrict__ out,
-                                                         uint64_t nvec, uint32_t splits) {
+                                                         uint64_t nvec, uint32_t splits, int epilogue) {
   const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= nvec) return;
   float4 s = __ldcs(partial + i);
   for (uint32_t sp = 1; sp < splits; ++sp) {
     float4 v = __ldcs(partial + (uint64_t)sp * nvec + i);
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  if (epilogue == 1) {
+    s.x = sigmoid_clamped(s.x); s.y = sigmoid_clamped(s.y); s.z = sigmoid_clamped(s.z); s.w = sigmoid_clamped(s.w);
   }
   out[i] = s;
 }
@@ -569,7 +581,7 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) 
 template <int BN, int BK>
 static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                       const float* right, float* out, int passes, int write_hi, float* ws, uint32_t splits,
-                      cudaStream_t stream) {
+                      int epilogue, cudaStream_t stream) {
   using C = Cfg<BN, BK>;
   static_assert(C::kStages >= 2 && C::kSmemBytes <= 227 * 1024, "stage ring must fit shared memory");
   int dev = 0;
@@ -602,6 +614,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   if (splits < 1 || !ws || splits > num_kb) splits = 1;
   p.splits = splits;
   p.partial = splits > 1 ? ws : nullptr;
+  p.epilogue = splits > 1 ? 0 : epilogue;
   uint64_t units = tm * tn * splits;
   if (units > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   unsigned grid = (unsigned)(units < (uint64_t)sm_count() ? units : (uint64_t)sm_count());   // one CTA per SM
@@ -610,7 +623,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   if (rc || splits == 1) return rc;
   const uint64_t nvec = m * n / 4;
   add_splits_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(ws),
-                                                                       reinterpret_cast<float4*>(out), nvec, splits);
+                                                                       reinterpret_cast<float4*>(out), nvec, splits, epilogue);
   return check_launch("fmatmul_add_splits");
 }
 
@@ -618,12 +631,14 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
 
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, cudaStream_t stream) {
+              uint32_t splits, int epilogue, cudaStream_t stream) {
   if (bn == 128 && bk == 32)
-    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
-  if (bn == 128) return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
-  if (bk == 32) return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
-  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, stream);
+    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
+  if (bn == 128)
+    return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
+  if (bk == 32)
+    return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
+  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
 }
 
 // Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.

@@ -132,6 +132,71 @@ def mlp_program(batch, n_in=784, n_hidden=4096, n_out=10, lr=0.1):
     return p
 
 
+def fuse_program(program):
+    """Rewrites a program with the extended builtins, keeping every result bit-identical:
+
+      fadd(ones,1,S,-1,t1); fmul(t1,S,t2); fmul(G,t2,out)   ->  fsigmoid_grad(G, S, out)
+      fmatmul_x_y(L,R,Z); fsigmoid(Z,H)                      ->  fmatmul_x_y_sigmoid(L, R, H)
+      fmatmul_x_y(L,R,G); fsigmoid_grad(G,S,out)             ->  fmatmul_x_y_sigmoid_grad(L, R, S, out)
+
+    A rewrite applies only when the intermediates (t1, t2, Z, G) are read by nothing else
+    and are not outputs of the program; they are then never written.  `ones` must be a
+    constant 1.0 tensor."""
+    ops = [(k, list(a)) for k, a in program.ops]
+
+    def readers(name, skip):
+        n = 0
+        for i, (k, a) in enumerate(ops):
+            if i in skip or k == "ALLREDUCE":
+                continue
+            ins = a[:-1]
+            n += sum(1 for x in ins if x == name)
+        return n
+
+    def dead_after(name, skip):
+        return name not in program.outputs and name not in program.inputs and readers(name, skip) == 0
+
+    changed = True
+    while changed:
+        changed = False
+        for i in range(len(ops)):
+            k, a = ops[i]
+            # sigmoid derivative chain
+            if (k == "fadd" and i + 2 < len(ops) and program.constants.get(a[0]) == 1.0 and a[1] == 1.0
+                    and a[3] == -1.0):
+                s_, t1 = a[2], a[4]
+                k2, a2 = ops[i + 1]
+                k3, a3 = ops[i + 2]
+                if (k2 == "fmul" and a2[0] == t1 and a2[1] == s_ and k3 == "fmul" and a3[1] == a2[2]
+                        and dead_after(t1, {i, i + 1, i + 2}) and dead_after(a2[2], {i, i + 1, i + 2})):
+                    ops[i:i + 3] = [("fsigmoid_grad", [a3[0], s_, a3[2]])]
+                    changed = True
+                    break
+            # matmul followed by the builtin that consumes its result
+            if k.startswith("fmatmul_") and len(k) == 11:
+                z = a[2]
+                for j in range(i + 1, len(ops)):
+                    kj, aj = ops[j]
+                    if kj == "ALLREDUCE":
+                        continue
+                    if z in aj[:-1] or aj[-1] == z:
+                        if kj == "fsigmoid" and aj[0] == z and dead_after(z, {i, j}):
+                            ops[j] = (k + "_sigmoid", [a[0], a[1], aj[1]])
+                            del ops[i]
+                            changed = True
+                        elif (kj == "fsigmoid_grad" and aj[0] == z and aj[1] != z and dead_after(z, {i, j})
+                              and not any(o[1][-1] in (a[0], a[1]) for o in ops[i + 1:j] if o[0] != "ALLREDUCE")):
+                            ops[j] = (k + "_sigmoid_grad", [a[0], a[1], aj[1], aj[2]])
+                            del ops[i]
+                            changed = True
+                        break
+                if changed:
+                    break
+    fused = Program(program.name + "_fused", dict(program.tensors), ops, list(program.inputs),
+                    dict(program.constants), list(program.outputs))
+    return fused
+
+
 class DeviceExecutor:
     """Runs a Program on one GPU: one device tensor per program tensor, every op
     through polar_b200_launch_by_name on torch's current stream.  Argument
