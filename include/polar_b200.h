@@ -98,6 +98,34 @@ int polar_b200_flogloss(const float* predicted, const float* groundTruth,
 int polar_b200_fmulconcat(const float* gradient, const float* localDerivative,
                           float* out, uint64_t n, void* stream);
 
+/* ---- the other operation builtins (not on the benchmarked path) ---------- */
+
+/* frelu: out[i] = in[i] > 0 ? in[i] : 0.  Args: T in, T out.
+ * Replaces PolarGraph/kernels/ReLUOp.cpp:36-44. */
+int polar_b200_frelu(const float* in, float* out, uint64_t n, void* stream);
+
+/* fsoftmax over the WHOLE tensor: out[i] = exp(in[i]) / sum_j exp(in[j]), no maximum
+ * subtracted (PolarGraph/kernels/SoftmaxOp.cpp:38-66).  Args: T in, T out.  Needs 8
+ * bytes of scratch for the sum: `workspace` (8-byte aligned) or, when NULL, the
+ * stream-ordered pool. */
+int polar_b200_fsoftmax(const float* in, float* out, uint64_t n, void* workspace,
+                        uint64_t workspace_bytes, void* stream);
+
+/* fpool: 2-D max pooling of an [h,w] tensor; out is [(h-windowH)/strideH+1,
+ * (w-windowW)/strideW+1]; every maximum starts from -10e5 as in the reference
+ * (PolarGraph/kernels/Pool2DOp.cpp:44-84).  As a builtin: T in, four 8-byte integer
+ * DATA arguments (windowH, windowW, strideH, strideW), T out. */
+int polar_b200_fpool(const float* in, uint64_t h, uint64_t w, uint64_t windowH,
+                     uint64_t windowW, uint64_t strideH, uint64_t strideW, float* out,
+                     void* stream);
+
+/* fconv2d: single-channel "valid" cross-correlation, out[i,j] = sum_{a,b}
+ * in[i+a,j+b]*kernel[a,b] (products rounded, added in row-major kernel order); out is
+ * [h-kh+1, w-kw+1]; kernel extents must be odd (PolarGraph/kernels/Conv2DOp.cpp:35-90).
+ * Args: T in, T kernel, T out. */
+int polar_b200_fconv2d(const float* in, uint64_t h, uint64_t w, const float* kernel,
+                       uint64_t kh, uint64_t kw, float* out, void* stream);
+
 /* ---- matmul -------------------------------------------------------------- */
 
 /* fmatmul_{f,t}_{f,t}: out[i,j] = sum_k L'[i,k]*R'[k,j] in fp32 accuracy.
@@ -177,8 +205,17 @@ int polar_b200_fmatmul_tc(int transLeft, int transRight, uint64_t m, uint64_t n,
                           float* out, int tile_n, int slab_k, int passes,
                           int write_hi, int splits, void* stream);
 
+/* The tensor-core path with PAIRS of CTAs (tcgen05 cta_group::2): two CTAs of a
+ * cluster compute one 256 x 256 tile, each staging only its half of the operands.
+ * Same product and accuracy as polar_b200_fmatmul_tc with passes = 3; exposed for
+ * tests and benchmarks.  splits as above (1..64); fuse_sigmoid != 0 stores
+ * fsigmoid(product). */
+int polar_b200_fmatmul_tc_pair(int transLeft, int transRight, uint64_t m, uint64_t n,
+                               uint64_t k, const float* left, const float* right,
+                               float* out, int splits, int fuse_sigmoid, void* stream);
+
 /* Status word the kernels write when a bounded device-side wait gives up
- * (0 = none; 101..106 = which wait of the tensor-core matmul).  It lives in
+ * (0 = none; 101..106 and 201..206 = which wait of the tensor-core matmuls).  It lives in
  * pinned host memory, so reading it needs no CUDA call; read it after the
  * stream has been synchronised. */
 int polar_b200_device_status(void);
@@ -240,12 +277,18 @@ typedef struct polar_b200_tensor {
 } polar_b200_tensor;
 
 typedef struct polar_b200_arg {
-  int is_tensor;            /* 1: ArgDesc::TENSOR, 0: ArgDesc::DATA (one f32) */
+  int is_tensor;            /* 1: ArgDesc::TENSOR, 0: ArgDesc::DATA */
   polar_b200_tensor tensor; /* when is_tensor */
-  float scalar;             /* when !is_tensor */
+  float scalar;             /* DATA of 4 bytes: one f32 */
+  int64_t integer;          /* DATA of 8 bytes: one i64 (fpool's window and stride) */
 } polar_b200_arg;
 
-/* Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
+/* Native names: the twelve of the benchmarked path, "frelu", "fsoftmax", "fpool",
+ * "fconv2d" (the reference's own table names ReLU, Softmax and Transpose all
+ * "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own here), and
+ * the extended "fsigmoid_grad", "fmatmul_x_y_sigmoid", "fmatmul_x_y_sigmoid_grad".
+ *
+ * Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
  * on arguments in LaunchCommand order; this is what Device::launch forwards to
  * once it has turned each TensorInfo into a device pointer.  Shapes are
  * checked against the builtin's rules (equal element counts; matmul inner

@@ -126,6 +126,64 @@ void oracle_fmulconcat(const float* gradient, const float* local, float* out,
   for (int64_t i = 0; i < (int64_t)n; ++i) out[i] = g * local[i];
 }
 
+/* frelu: out = in > 0 ? in : 0 (ordered compare: NaN gives 0).
+ * utils/dialects/lib/PolarGraph/kernels/ReLUOp.cpp:36-44. */
+void oracle_frelu(const float* in, float* out, uint64_t n) {
+  PAR_FOR
+  for (int64_t i = 0; i < (int64_t)n; ++i) out[i] = in[i] > 0.0f ? in[i] : 0.0f;
+}
+
+/* fsoftmax: over the WHOLE tensor, out[i] = exp(in[i]) / sum_j exp(in[j]); the sum is
+ * accumulated in fp32 in index order starting from 0, no maximum is subtracted.
+ * utils/dialects/lib/PolarGraph/kernels/SoftmaxOp.cpp:38-66 (which recomputes the
+ * same sum for every output element). */
+void oracle_fsoftmax(const float* in, float* out, uint64_t n) {
+  float total = 0.0f;
+  for (uint64_t j = 0; j < n; ++j) total = expf(in[j]) + total;
+  PAR_FOR
+  for (int64_t i = 0; i < (int64_t)n; ++i) out[i] = expf(in[i]) / total;
+}
+
+/* fpool: 2-D max pooling; out[i,j] starts at -10e5f and takes every larger input of
+ * the window rows i*sh .. i*sh+wh-1, columns j*sw .. j*sw+ww-1; the result is
+ * [(h-wh)/sh+1, (w-ww)/sw+1].  Pool2DOp.cpp:44-84;
+ * src/operation/internal/Pool2DOperationInternal.cpp:36-41 (shape). */
+void oracle_fpool(const float* in, uint64_t h, uint64_t w, uint64_t wh, uint64_t ww, uint64_t sh,
+                  uint64_t sw, float* out) {
+  const uint64_t oh = (h - wh) / sh + 1, ow = (w - ww) / sw + 1;
+  PAR_FOR
+  for (int64_t i = 0; i < (int64_t)oh; ++i)
+    for (uint64_t j = 0; j < ow; ++j) {
+      float best = -10e5f;
+      for (uint64_t a = 0; a < wh; ++a)
+        for (uint64_t b = 0; b < ww; ++b) {
+          float v = in[((uint64_t)i * sh + a) * w + j * sw + b];
+          best = v > best ? v : best;
+        }
+      out[(uint64_t)i * ow + j] = best;
+    }
+}
+
+/* fconv2d: single-channel "valid" cross-correlation with an odd-sized kernel;
+ * out[i,j] = sum over kernel rows a, columns b (in that order) of in[i+a, j+b]*ker[a,b],
+ * each product rounded, then added; the result is [h-kh+1, w-kw+1].
+ * Conv2DOp.cpp:35-90; src/operation/internal/Conv2DOperationInternal.cpp:34-39. */
+void oracle_fconv2d(const float* in, uint64_t h, uint64_t w, const float* ker, uint64_t kh, uint64_t kw,
+                    float* out) {
+  const uint64_t oh = h - kh + 1, ow = w - kw + 1;
+  PAR_FOR
+  for (int64_t i = 0; i < (int64_t)oh; ++i)
+    for (uint64_t j = 0; j < ow; ++j) {
+      float acc = 0.0f;
+      for (uint64_t a = 0; a < kh; ++a)
+        for (uint64_t b = 0; b < kw; ++b) {
+          float prod = in[((uint64_t)i + a) * w + j + b] * ker[a * kw + b];
+          acc = prod + acc;
+        }
+      out[(uint64_t)i * ow + j] = acc;
+    }
+}
+
 /* Index walk shared by the matmul forms: the left operand is stored [m,k] or,
  * transposed, [k,m]; the right one [k,n] or, transposed, [n,k].
  * kernels.h:80-117; MatMulOperation.cpp:17-51 (same strides). */

@@ -59,6 +59,10 @@ class Oracle:
         L.oracle_flogloss.argtypes = [_F, _F, _F, ctypes.c_uint64]
         L.oracle_fmulconcat.argtypes = [_F, _F, _F, ctypes.c_uint64]
         u = ctypes.c_uint64
+        L.oracle_frelu.argtypes = [_F, _F, u]
+        L.oracle_fsoftmax.argtypes = [_F, _F, u]
+        L.oracle_fpool.argtypes = [_F, u, u, u, u, u, u, _F]
+        L.oracle_fconv2d.argtypes = [_F, u, u, _F, u, u, _F]
         L.oracle_fmatmul.argtypes = [ctypes.c_int, ctypes.c_int, u, u, u, _F, _F, _F]
         L.oracle_fmatmul_f64.argtypes = [ctypes.c_int, ctypes.c_int, u, u, u, _F, _F, _D, _D]
         L.oracle_fmatmul_entries_f64.argtypes = [ctypes.c_int, ctypes.c_int, u, u, u, _F, _F,
@@ -117,6 +121,33 @@ class Oracle:
         g, l = _f32(gradient), _f32(local)
         out = np.empty_like(l)
         self.lib.oracle_fmulconcat(_p(g), _p(l), _p(out), l.size)
+        return out
+
+    def frelu(self, a):
+        a = _f32(a)
+        out = np.empty_like(a)
+        self.lib.oracle_frelu(_p(a), _p(out), a.size)
+        return out
+
+    def fsoftmax(self, a):
+        a = _f32(a)
+        out = np.empty_like(a)
+        self.lib.oracle_fsoftmax(_p(a), _p(out), a.size)
+        return out
+
+    def fpool(self, a, window, stride):
+        a = _f32(a)
+        h, w = a.shape
+        out = np.empty(((h - window[0]) // stride[0] + 1, (w - window[1]) // stride[1] + 1), np.float32)
+        self.lib.oracle_fpool(_p(a), h, w, window[0], window[1], stride[0], stride[1], _p(out))
+        return out
+
+    def fconv2d(self, a, kernel):
+        a, kernel = _f32(a), _f32(kernel)
+        h, w = a.shape
+        kh, kw = kernel.shape
+        out = np.empty((h - kh + 1, w - kw + 1), np.float32)
+        self.lib.oracle_fconv2d(_p(a), h, w, _p(kernel), kh, kw, _p(out))
         return out
 
     def fmatmul(self, tl, tr, left, right):

@@ -23,7 +23,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++"] + ARCH
 
-KERNEL_SOURCES = ["common.cu", "elementwise.cu", "gemm_ffma.cu", "gemm_skinny.cu", "gemm_tc.cu", "dispatch.cu"]
+KERNEL_SOURCES = ["common.cu", "elementwise.cu", "extra_builtins.cu", "gemm_ffma.cu", "gemm_skinny.cu", "gemm_tc.cu", "gemm_tc2.cu", "dispatch.cu"]
 
 
 def _newer(src, dst, extra=()):
@@ -106,8 +106,9 @@ def build_runtime(force=False):
     return lib
 
 
-REF_TESTS = ["AddOperation", "CombineOperation", "DivideOperation", "LogLossOperation", "MatMulOperation",
-             "MulConcatOperation", "MulOperation", "SigmoidOperation"]
+REF_TESTS = ["AddOperation", "CombineOperation", "Conv2DOperation", "DivideOperation", "LogLossOperation",
+             "MatMulOperation", "MulConcatOperation", "MulOperation", "Pool2DOperation", "ReLUOperation",
+             "SigmoidOperation", "SoftmaxOperation"]
 
 
 def build_reference_host(force=False):

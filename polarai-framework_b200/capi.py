@@ -26,7 +26,7 @@ class Tensor(ctypes.Structure):
 
 
 class Arg(ctypes.Structure):
-    _fields_ = [("is_tensor", _i), ("tensor", Tensor), ("scalar", _f)]
+    _fields_ = [("is_tensor", _i), ("tensor", Tensor), ("scalar", _f), ("integer", ctypes.c_int64)]
 
 
 SIGNATURES = {
@@ -43,6 +43,10 @@ SIGNATURES = {
     "polar_b200_flogloss": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fsigmoid_grad": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fmulconcat": (_i, [_p, _p, _p, _u64, _p]),
+    "polar_b200_frelu": (_i, [_p, _p, _u64, _p]),
+    "polar_b200_fsoftmax": (_i, [_p, _p, _u64, _p, _u64, _p]),
+    "polar_b200_fpool": (_i, [_p, _u64, _u64, _u64, _u64, _u64, _u64, _p, _p]),
+    "polar_b200_fconv2d": (_i, [_p, _u64, _u64, _p, _u64, _u64, _p, _p]),
     "polar_b200_fmatmul": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid_grad": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
@@ -51,6 +55,7 @@ SIGNATURES = {
     "polar_b200_fmatmul_tc": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "polar_b200_fmatmul_tn_small_n_static": (_i, [_i, _u64, _u64, _u64, _p, _p, _p, _p]),
     "polar_b200_static_scratch_bytes": (_u64, []),
+    "polar_b200_fmatmul_tc_pair": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _p]),
     "polar_b200_fmatmul_path": (_i, [_i, _i, _u64, _u64, _u64]),
     "polar_b200_device_status": (_i, []),
     "polar_b200_device_status_clear": (None, []),

@@ -10,6 +10,8 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
               uint32_t splits, int epilogue, cudaStream_t stream);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k);
+int launch_tc_pair(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
+                   float* out, float* ws, uint32_t splits, int epilogue, cudaStream_t stream);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
 int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -202,6 +204,28 @@ int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, co
   return run_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, s, nullptr, 0, as_stream(stream));
 }
 
+int polar_b200_fmatmul_tc_pair(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
+                               const float* right, float* out, int splits, int fuse_sigmoid, void* stream) {
+  clear_error();
+  int rc = check_mm(tl, tr, m, n, k, left, right, out);
+  if (rc) return rc;
+  if (m == 0 || n == 0 || k == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "empty matrix");
+  if (!tc_shape_ok(tl, tr, m, n, k, left, right))
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
+  if (splits < 1 || splits > 64 || (splits > 1 && ((m * n) & 3)))
+    return fail(POLAR_B200_ERR_INVALID, "splits must be 1..64, and m*n a multiple of 4 when > 1");
+  cudaStream_t st = as_stream(stream);
+  if (splits == 1) return launch_tc_pair(tl, tr, m, n, k, left, right, out, nullptr, 1, fuse_sigmoid & 3, st);
+  void* ws = nullptr;
+  cudaError_t e = cudaMallocAsync(&ws, (uint64_t)splits * m * n * sizeof(float), st);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+  rc = launch_tc_pair(tl, tr, m, n, k, left, right, out, static_cast<float*>(ws), (uint32_t)splits,
+                      fuse_sigmoid ? 1 : 0, st);
+  e = cudaFreeAsync(ws, st);
+  if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+  return rc;
+}
+
 int polar_b200_device_status(void) { return tc_status_word(); }
 void polar_b200_device_status_clear(void) { tc_status_clear(); }
 
@@ -250,6 +274,33 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
   if (!std::strcmp(name, "fsigmoid")) {
     if (!pattern("TT") || !same(0, 1)) return fail(bad_args, "fsigmoid expects (T in, T out) of equal size");
     return polar_b200_fsigmoid(a[0].tensor.data, a[1].tensor.data, numel(a[1].tensor), stream);
+  }
+  if (!std::strcmp(name, "frelu")) {
+    if (!pattern("TT") || !same(0, 1)) return fail(bad_args, "frelu expects (T in, T out) of equal size");
+    return polar_b200_frelu(a[0].tensor.data, a[1].tensor.data, numel(a[1].tensor), stream);
+  }
+  if (!std::strcmp(name, "fsoftmax")) {
+    if (!pattern("TT") || !same(0, 1)) return fail(bad_args, "fsoftmax expects (T in, T out) of equal size");
+    return polar_b200_fsoftmax(a[0].tensor.data, a[1].tensor.data, numel(a[1].tensor), nullptr, 0, stream);
+  }
+  if (!std::strcmp(name, "fpool")) {
+    if (!pattern("TffffT") || a[0].tensor.dims != 2 || a[5].tensor.dims != 2)
+      return fail(bad_args, "fpool expects (T in[h,w], i64 windowH, i64 windowW, i64 strideH, i64 strideW, T out)");
+    const uint64_t h = a[0].tensor.shape[0], w = a[0].tensor.shape[1];
+    const int64_t wh = a[1].integer, ww = a[2].integer, sh = a[3].integer, sw = a[4].integer;
+    if (wh <= 0 || ww <= 0 || sh <= 0 || sw <= 0 || (uint64_t)wh > h || (uint64_t)ww > w ||
+        a[5].tensor.shape[0] != (h - wh) / sh + 1 || a[5].tensor.shape[1] != (w - ww) / sw + 1)
+      return fail(bad_args, "fpool: window, stride and output shape do not agree");
+    return polar_b200_fpool(a[0].tensor.data, h, w, wh, ww, sh, sw, a[5].tensor.data, stream);
+  }
+  if (!std::strcmp(name, "fconv2d")) {
+    if (!pattern("TTT") || a[0].tensor.dims != 2 || a[1].tensor.dims != 2 || a[2].tensor.dims != 2)
+      return fail(bad_args, "fconv2d expects (T in[h,w], T kernel[kh,kw], T out)");
+    const uint64_t h = a[0].tensor.shape[0], w = a[0].tensor.shape[1];
+    const uint64_t kh = a[1].tensor.shape[0], kw = a[1].tensor.shape[1];
+    if (kh > h || kw > w || a[2].tensor.shape[0] != h - kh + 1 || a[2].tensor.shape[1] != w - kw + 1)
+      return fail(bad_args, "fconv2d: shapes do not agree");
+    return polar_b200_fconv2d(a[0].tensor.data, h, w, a[1].tensor.data, kh, kw, a[2].tensor.data, stream);
   }
   if (!std::strcmp(name, "fsigmoid_grad")) {
     if (!pattern("TTT") || !same(0, 2) || !same(1, 2))

@@ -60,6 +60,8 @@ struct Value : GenValueImplBase {
   bool isTensor = false;
   TensorDesc tensor;
   float scalar = 0.f;
+  bool isInteger = false;   // an 8-byte integer attribute (pooling window, stride)
+  int64_t integer = 0;
 };
 
 GenValue makeTensorValue(const TensorInternal& t) {
@@ -246,16 +248,29 @@ private:
     builtin_functor_t<builtin::Sigmoid> sig = [this](GenValue in, GenValue out) { launch("fsigmoid", {in, out}); };
     g.registerFunctor<builtin::Sigmoid>(sig);
 
-    // Builtins outside the path this runtime implements.
-    builtin_functor_t<builtin::Conv2D> conv = [this](GenValue, GenValue, GenValue) { refuse("Conv2D"); };
+    builtin_functor_t<builtin::Conv2D> conv = [this](GenValue in, GenValue ker, GenValue out) {
+      launch("fconv2d", {in, ker, out});
+    };
     g.registerFunctor<builtin::Conv2D>(conv);
-    builtin_functor_t<builtin::Pool2D> pool = [this](GenValue, GenValue, const std::vector<int64_t>&,
-                                                     const std::vector<int64_t>&) { refuse("Pool2D"); };
+    // The window and the stride are attributes of the operation; they travel as four
+    // 8-byte integer DATA arguments between the input and the output tensor.
+    builtin_functor_t<builtin::Pool2D> pool = [this](GenValue in, GenValue out, const std::vector<int64_t>& window,
+                                                     const std::vector<int64_t>& stride) {
+      if (window.size() != 2 || stride.size() != 2) return refuse("Pool2D with a window that is not 2-D");
+      auto attr = [](int64_t v) {
+        auto a = std::make_shared<Value>();
+        a->isInteger = true;
+        a->integer = v;
+        return GenValue{a};
+      };
+      launch("fpool", {in, attr(window[0]), attr(window[1]), attr(stride[0]), attr(stride[1]), out});
+    };
     g.registerFunctor<builtin::Pool2D>(pool);
-    builtin_functor_t<builtin::ReLU> relu = [this](GenValue, GenValue) { refuse("ReLU"); };
+    builtin_functor_t<builtin::ReLU> relu = [this](GenValue in, GenValue out) { launch("frelu", {in, out}); };
     g.registerFunctor<builtin::ReLU>(relu);
-    builtin_functor_t<builtin::Softmax> sm = [this](GenValue, GenValue) { refuse("Softmax"); };
+    builtin_functor_t<builtin::Softmax> sm = [this](GenValue in, GenValue out) { launch("fsoftmax", {in, out}); };
     g.registerFunctor<builtin::Softmax>(sm);
+    // Builtins no operation of the reference emits.
     builtin_functor_t<builtin::Slice> sl = [this](GenValue, GenValue) { refuse("Slice"); };
     g.registerFunctor<builtin::Slice>(sl);
     builtin_functor_t<builtin::Transpose> tp = [this](GenValue, GenValue) { refuse("Transpose"); };
@@ -356,6 +371,8 @@ public:
               if (v.isTensor) {
                 infos[i] = infoOf(v.tensor);
                 args[i] = ArgDesc{0, &infos[i], ArgDesc::TENSOR};
+              } else if (v.isInteger) {
+                args[i] = ArgDesc{sizeof(int64_t), &v.integer, ArgDesc::DATA};
               } else {
                 args[i] = ArgDesc{sizeof(float), &v.scalar, ArgDesc::DATA};
               }

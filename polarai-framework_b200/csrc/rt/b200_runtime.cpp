@@ -304,6 +304,7 @@ auto B200Device::launch(BackendAllocator& allocator, LaunchCommand& cmd, Event* 
       args[i].tensor.dims = t->dims;
       args[i].tensor.shape = t->shape;
       args[i].scalar = 0.f;
+      args[i].integer = 0;
       if (!args[i].tensor.data && rec.allocationSize) {
         status = POLAR_B200_ERR_INVALID;
         mLastError = "launch: tensor is not allocated on this device";
@@ -311,7 +312,13 @@ auto B200Device::launch(BackendAllocator& allocator, LaunchCommand& cmd, Event* 
     } else {
       args[i].is_tensor = 0;
       args[i].tensor = polar_b200_tensor{nullptr, 0, nullptr};
-      args[i].scalar = a.arg ? *static_cast<float*>(a.arg) : 0.f;
+      args[i].scalar = 0.f;
+      args[i].integer = 0;
+      if (a.arg && a.size == 8) {
+        args[i].integer = *static_cast<int64_t*>(a.arg);     // attributes such as a pooling window
+      } else if (a.arg) {
+        args[i].scalar = *static_cast<float*>(a.arg);
+      }
     }
   }
   if (status == POLAR_B200_OK) {

@@ -74,6 +74,30 @@ class DeviceBuiltins:
         self.lib.call("polar_b200_fmulconcat", _ptr(gradient), _ptr(local), _ptr(out), out.numel(), _stream())
         return out
 
+    def frelu(self, a, out):
+        _chk(a, out)
+        self.lib.call("polar_b200_frelu", _ptr(a), _ptr(out), out.numel(), _stream())
+        return out
+
+    def fsoftmax(self, a, out):
+        _chk(a, out)
+        self.lib.call("polar_b200_fsoftmax", _ptr(a), _ptr(out), out.numel(), None, 0, _stream())
+        return out
+
+    def fpool(self, a, window, stride, out):
+        _chk(a, out)
+        h, w = a.shape
+        self.lib.call("polar_b200_fpool", _ptr(a), h, w, window[0], window[1], stride[0], stride[1], _ptr(out),
+                      _stream())
+        return out
+
+    def fconv2d(self, a, kernel, out):
+        _chk(a, kernel, out)
+        h, w = a.shape
+        kh, kw = kernel.shape
+        self.lib.call("polar_b200_fconv2d", _ptr(a), h, w, _ptr(kernel), kh, kw, _ptr(out), _stream())
+        return out
+
     def fsum(self, a, acc):
         """Adds sum(a) to the float64 one-element tensor `acc`."""
         _chk(a)
@@ -101,6 +125,13 @@ class DeviceBuiltins:
         m, n, k = matmul_dims(tl, tr, left.shape, right.shape)
         self.lib.call("polar_b200_fmatmul_tc", int(tl), int(tr), m, n, k, _ptr(left), _ptr(right),
                       _ptr(out), tile_n, slab_k, passes, write_hi, splits, _stream())
+        return out
+
+    def fmatmul_tc_pair(self, tl, tr, left, right, out, splits=1, fuse_sigmoid=0):
+        _chk(left, right, out)
+        m, n, k = matmul_dims(tl, tr, left.shape, right.shape)
+        self.lib.call("polar_b200_fmatmul_tc_pair", int(tl), int(tr), m, n, k, _ptr(left), _ptr(right),
+                      _ptr(out), splits, fuse_sigmoid, _stream())
         return out
 
     def device_status(self):
@@ -161,6 +192,25 @@ class HostBuiltins:
     def fmulconcat(self, g, l):
         g, l = self._up(g), self._up(l)
         return self._down(self.d.fmulconcat(g, l, torch.empty_like(l)))
+
+    def frelu(self, a):
+        a = self._up(a)
+        return self._down(self.d.frelu(a, torch.empty_like(a)))
+
+    def fsoftmax(self, a):
+        a = self._up(a)
+        return self._down(self.d.fsoftmax(a, torch.empty_like(a)))
+
+    def fpool(self, a, window, stride):
+        a = self._up(a)
+        h, w = a.shape
+        out = torch.empty(((h - window[0]) // stride[0] + 1, (w - window[1]) // stride[1] + 1), device=self.dev)
+        return self._down(self.d.fpool(a, window, stride, out))
+
+    def fconv2d(self, a, kernel):
+        a, kernel = self._up(a), self._up(kernel)
+        out = torch.empty((a.shape[0] - kernel.shape[0] + 1, a.shape[1] - kernel.shape[1] + 1), device=self.dev)
+        return self._down(self.d.fconv2d(a, kernel, out))
 
     def fmatmul(self, tl, tr, left, right, which="auto", **kw):
         l, r = self._up(left), self._up(right)

@@ -30,6 +30,10 @@ void oracle_fdivide(const float* a, const float* b, float* out, uint64_t n);
 void oracle_fsigmoid(const float* in, float* out, uint64_t n, int clamp);
 void oracle_flogloss(const float* p, const float* y, float* out, uint64_t n);
 void oracle_fmulconcat(const float* g, const float* l, float* out, uint64_t n);
+void oracle_frelu(const float* in, float* out, uint64_t n);
+void oracle_fsoftmax(const float* in, float* out, uint64_t n);
+void oracle_fpool(const float* in, uint64_t h, uint64_t w, uint64_t wh, uint64_t ww, uint64_t sh, uint64_t sw, float* out);
+void oracle_fconv2d(const float* in, uint64_t h, uint64_t w, const float* ker, uint64_t kh, uint64_t kw, float* out);
 void oracle_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l, const float* r, float* out);
 }
 
@@ -117,6 +121,7 @@ public:
     uint64_t n[8] = {0};
     TensorInfo* ti[8] = {nullptr};
     float f[8] = {0};
+    int64_t iv[8] = {0};
     for (uint64_t i = 0; i < cmd.argsCount && i < 8; ++i) {
       if (cmd.args[i].type == ArgDesc::TENSOR) {
         ti[i] = static_cast<TensorInfo*>(cmd.args[i].arg);
@@ -125,6 +130,8 @@ public:
         for (uint64_t d = 0; d < ti[i]->dims; ++d) n[i] *= ti[i]->shape[d];
         r.allocationSize *= n[i];
         t[i] = alloc.get<float>(r, *this);
+      } else if (cmd.args[i].size == 8) {
+        iv[i] = *static_cast<int64_t*>(cmd.args[i].arg);
       } else {
         f[i] = *static_cast<float*>(cmd.args[i].arg);
       }
@@ -137,6 +144,12 @@ public:
     else if (name == "fsigmoid") oracle_fsigmoid(t[0], t[1], n[1], 1);
     else if (name == "flogloss") oracle_flogloss(t[0], t[1], t[2], n[2]);
     else if (name == "fmulconcat") oracle_fmulconcat(t[0], t[1], t[2], n[2]);
+    else if (name == "frelu") oracle_frelu(t[0], t[1], n[1]);
+    else if (name == "fsoftmax") oracle_fsoftmax(t[0], t[1], n[1]);
+    else if (name == "fpool")
+      oracle_fpool(t[0], ti[0]->shape[0], ti[0]->shape[1], iv[1], iv[2], iv[3], iv[4], t[5]);
+    else if (name == "fconv2d")
+      oracle_fconv2d(t[0], ti[0]->shape[0], ti[0]->shape[1], t[1], ti[1]->shape[0], ti[1]->shape[1], t[2]);
     else if (name.rfind("fmatmul_", 0) == 0 && name.size() == 11) {
       int tl = name[8] == 't', tr = name[10] == 't';
       uint64_t m = tl ? ti[0]->shape[1] : ti[0]->shape[0], k = tl ? ti[0]->shape[0] : ti[0]->shape[1];

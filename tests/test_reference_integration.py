@@ -1,6 +1,6 @@
-"""The reference project's own integration tests for the builtins on this path
-(tests/integration/operations/{Add,Combine,Divide,LogLoss,MatMul,MulConcat,Mul,
-Sigmoid}Operation.cpp of the reference), compiled unmodified against this
+"""The reference project's own integration tests - all twelve files of
+tests/integration/operations/ in the reference (Add, Combine, Conv2D, Divide, LogLoss,
+MatMul, MulConcat, Mul, Pool2D, ReLU, Sigmoid, Softmax) - compiled unmodified against this
 package's Executor and run against the B200 device plugin.
 
 The binary is built by polarai-framework_b200/build.py from the reference tree
@@ -32,7 +32,7 @@ def test_binary_loads_the_plugin_and_skips_without_a_device():
     if torch.cuda.is_available():
         pytest.skip("covered by the GPU test")
     out, (ran, failed, skipped, disabled) = run("--also_run_disabled_tests")
-    assert out.returncode == 0 and ran == 13 and failed == 0 and skipped == 13
+    assert out.returncode == 0 and ran == 17 and failed == 0 and skipped == 17
 
 
 @pytest.mark.gpu
@@ -40,11 +40,11 @@ def test_reference_integration_tests_pass_on_the_b200_device():
     assert os.path.exists(BIN), "build the package where the reference tree is present"
     out, (ran, failed, skipped, disabled) = run()
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
-    assert (ran, failed, skipped, disabled) == (11, 0, 0, 2), out.stdout[-3000:]
+    assert (ran, failed, skipped, disabled) == (15, 0, 0, 2), out.stdout[-3000:]
     # the two tests the reference ships DISABLED_ (Sigmoid, LogLoss) pass as well
     out, (ran, failed, skipped, disabled) = run("--also_run_disabled_tests")
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
-    assert (ran, failed, skipped, disabled) == (13, 0, 0, 0), out.stdout[-3000:]
+    assert (ran, failed, skipped, disabled) == (17, 0, 0, 0), out.stdout[-3000:]
 
 
 PARITY = os.path.join(ROOT, "polarai-framework_b200", "lib", "ref", "autograd_parity")
