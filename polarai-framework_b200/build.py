@@ -6,8 +6,8 @@
 libpolar_b200.so    - the builtin kernels and their C ABI (include/polar_b200.h)
 libpolar_rt_cuda.so - the PolarAI device-runtime plugin (initContext/closeContext)
                       built against the reference's runtime headers when the
-                      reference tree is present (POLAR_REFERENCE_ROOT, default
-                      /root/reference); otherwise a prebuilt file is kept.
+                      reference tree is present (environment variable
+                      POLAR_REFERENCE_ROOT); otherwise a prebuilt file is kept.
 """
 import concurrent.futures
 import os
@@ -124,7 +124,8 @@ def build_reference_host(force=False):
     tests_bin = os.path.join(out_dir, "ref_integration_tests")
     ref = reference_root()
     if ref is None:
-        return [p for p in (frontend, executor, tests_bin, os.path.join(out_dir, "autograd_parity")) if os.path.exists(p)]
+        return [p for p in (frontend, executor, tests_bin, os.path.join(out_dir, "autograd_parity"),
+                            os.path.join(out_dir, "lspolar")) if os.path.exists(p)]
     os.makedirs(out_dir, exist_ok=True)
     obj_dir = os.path.join(OBJ, "ref")
     gen = os.path.join(obj_dir, "gen")
@@ -188,7 +189,13 @@ def build_reference_host(force=False):
         _run([gxx] + tflags + ["-I", shim, "-fopenmp", "-o", parity_bin, parity_src, oracle_o,
                                "-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl",
                                "-lpthread", "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
-    return [frontend, executor, tests_bin, parity_bin]
+    # the reference's device-listing tool, unmodified, against the same driver
+    lspolar_bin = os.path.join(out_dir, "lspolar")
+    lspolar_src = os.path.join(ref, "utils", "lspolar", "main.cpp")
+    if os.path.exists(lspolar_src) and (force or _newer(lspolar_src, lspolar_bin, (frontend,))):
+        _run([gxx] + flags + ["-I", os.path.join(g, "runtime", "driver"), "-o", lspolar_bin, lspolar_src, "-L", out_dir, "-lpolar_frontend", "-ldl", "-lpthread",
+                              "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
+    return [frontend, executor, tests_bin, parity_bin, lspolar_bin]
 
 
 def build_all(force=False, verbose=False):

@@ -171,3 +171,19 @@ def test_linearity_at_8192(gpu):
     torch.cuda.synchronize()
     assert float((strip - C1[:256]).abs().max()) / (n * 0.25) <= TOL
     assert d.device_status() == 0
+
+
+@pytest.mark.parametrize("tl,tr", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_cta_pair_kernel(gpu, par_oracle, tl, tr):
+    # the experimental cta_group::2 kernel: two CTAs per 256 x 256 tile
+    import torch
+    for (m, n, k, splits) in ((256, 256, 64, 1), (200, 300, 100, 1), (1300, 1028, 520, 1), (1024, 512, 2048, 4)):
+        rng = np.random.default_rng(m + n + k + 2 * tl + tr)
+        l, r = operands(rng, tl, tr, m, n, k)
+        ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
+        L, R = torch.from_numpy(l).cuda(), torch.from_numpy(r).cuda()
+        out = torch.full((m, n), float("nan"), device="cuda")
+        gpu.d.fmatmul_tc_pair(tl, tr, L, R, out, splits=splits)
+        torch.cuda.synchronize()
+        assert gpu.d.device_status() == 0
+        assert rel_err(out.cpu().numpy(), ref, mag) <= 5e-6

@@ -69,3 +69,23 @@ def test_logistic_regression_with_reference_autograd_matches_the_oracle_device(b
     out = subprocess.run([PARITY, str(batch)], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "PARITY OK" in out.stdout, out.stdout
+
+
+LSPOLAR = os.path.join(ROOT, "polarai-framework_b200", "lib", "ref", "lspolar")
+
+
+@pytest.mark.skipif(not os.path.exists(LSPOLAR), reason="lspolar is not built")
+def test_reference_lspolar_loads_the_plugin():
+    # utils/lspolar/main.cpp of the reference, unmodified: RuntimeDriver dlopens libpolar_rt_cuda.so
+    import torch
+    out = subprocess.run([LSPOLAR], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "Total device count:" in out.stdout
+    if torch.cuda.is_available():
+        n = torch.cuda.device_count()
+        assert f"Total device count: {n}" in out.stdout
+        for i in range(n):
+            assert f"#{i}" in out.stdout
+        assert "Provider   : CUDA" in out.stdout and "Kind       : GPU" in out.stdout
+    else:
+        assert "Total device count: 0" in out.stdout
