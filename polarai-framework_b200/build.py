@@ -189,13 +189,27 @@ def build_reference_host(force=False):
         _run([gxx] + tflags + ["-I", shim, "-fopenmp", "-o", parity_bin, parity_src, oracle_o,
                                "-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl",
                                "-lpthread", "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
+    # host-side unit tests of the pool-based BackendAllocator with fake devices
+    alloc_bin = os.path.join(out_dir, "pool_allocator_test")
+    alloc_src = os.path.join(shim, "pool_allocator_test.cpp")
+    rt_dir = os.path.join(CSRC, "rt")
+    rt_lib = os.path.join(LIB, "libpolar_rt_cuda.so")
+    if force or _newer(alloc_src, alloc_bin, (rt_lib, main_src, os.path.join(shim, "oracle_device.hpp"))):
+        oracle_o = os.path.join(obj_dir, "builtins_oracle.o")
+        if not os.path.exists(oracle_o):
+            _run(["/usr/bin/gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-c", oracle_c, "-o", oracle_o])
+        tflags = [f for f in flags if f != "-fno-exceptions"]
+        _run([gxx] + tflags + ["-I", shim, "-I", CSRC, "-I", os.path.join(ROOT, "include"),
+                               "-I", "/usr/local/cuda/include", "-fopenmp", "-o", alloc_bin, main_src, alloc_src,
+                               oracle_o, "-L", LIB, "-lpolar_rt_cuda", "-lpolar_b200", "-ldl", "-lpthread",
+                               "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
     # the reference's device-listing tool, unmodified, against the same driver
     lspolar_bin = os.path.join(out_dir, "lspolar")
     lspolar_src = os.path.join(ref, "utils", "lspolar", "main.cpp")
     if os.path.exists(lspolar_src) and (force or _newer(lspolar_src, lspolar_bin, (frontend,))):
         _run([gxx] + flags + ["-I", os.path.join(g, "runtime", "driver"), "-o", lspolar_bin, lspolar_src, "-L", out_dir, "-lpolar_frontend", "-ldl", "-lpthread",
                               "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
-    return [frontend, executor, tests_bin, parity_bin, lspolar_bin]
+    return [frontend, executor, tests_bin, parity_bin, alloc_bin, lspolar_bin]
 
 
 def build_all(force=False, verbose=False):

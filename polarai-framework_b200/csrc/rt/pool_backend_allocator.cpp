@@ -4,13 +4,22 @@
 #include <polar_b200.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 namespace polarai::backend::generic {
 
 using core::internal::LockType;
 
+void PoolBackendAllocator::freeHost(HostBlock& b) {
+  if (b.pinned) {
+    cudaFreeHost(b.ptr);
+  } else {
+    std::free(b.ptr);
+  }
+}
+
 PoolBackendAllocator::~PoolBackendAllocator() {
-  for (auto& kv : mHost) cudaFreeHost(kv.second.ptr);
+  for (auto& kv : mHost) freeHost(kv.second);
 }
 
 void PoolBackendAllocator::registerDevice(Device& device) {
@@ -61,12 +70,19 @@ void PoolBackendAllocator::ensureHost(const MemoryRecord& record) {
   size_t bytes = record.allocationSize ? record.allocationSize : 4;
   // Pinned, so that host<->device copies run at full PCIe/C2C rate and can be
   // asynchronous.
+  bool pinned = true;
   if (cudaMallocHost(&p, bytes) != cudaSuccess) {
+    // No CUDA driver (a host-only process) or no pinnable memory left: pageable
+    // memory holds the same data, copies are just slower.
     cudaGetLastError();
-    fail(POLAR_B200_ERR_CUDA, "pinned host allocation failed");
-    return;
+    pinned = false;
+    p = std::malloc(bytes);
+    if (!p) {
+      fail(POLAR_B200_ERR_CUDA, "host allocation failed");
+      return;
+    }
   }
-  mHost[record.virtualAddress] = HostBlock{p, bytes, 0};
+  mHost[record.virtualAddress] = HostBlock{p, bytes, 0, pinned};
 }
 
 void PoolBackendAllocator::updateHost(const MemoryRecord& record) {
@@ -128,7 +144,7 @@ void PoolBackendAllocator::deallocate(const MemoryRecord& record) {
     if (l.layer->isAllocated(record)) l.layer->deallocate(record);
   auto hit = mHost.find(record.virtualAddress);
   if (hit != mHost.end()) {
-    cudaFreeHost(hit->second.ptr);
+    freeHost(hit->second);
     mHost.erase(hit);
   }
   if (it != mEntries.end()) mEntries.erase(it);
@@ -165,10 +181,16 @@ void PoolBackendAllocator::lock(const MemoryRecord& record, Device& device, Lock
         if (&o != l && o.layer->isAllocated(record) && o.layer->getTag(record) == e.tag) src = &o;
     if (host_has) {
       device.copyToDevice(record, hit->second.ptr);
-    } else if (src) {
-      // device to device, no RAM staging
+    } else if (src && src->device->getProvider() == DeviceProvider::CUDA &&
+               device.getProvider() == DeviceProvider::CUDA) {
+      // CUDA device to CUDA device: a peer copy, no RAM staging
       cudaMemcpy(l->layer->getPtr(record), src->layer->getPtr(record), record.allocationSize,
                  cudaMemcpyDefault);
+    } else if (src) {
+      // devices of another provider only promise copyToHost/copyToDevice
+      updateHost(record);
+      auto h2 = mHost.find(record.virtualAddress);
+      if (h2 != mHost.end()) device.copyToDevice(record, h2->second.ptr);
     }
     // else: nobody has written the record yet; its contents are undefined by contract
   }

@@ -62,7 +62,8 @@ protected:
   void* getImpl(const MemoryRecord& record, Device& device) override;
 
 private:
-  struct HostBlock { void* ptr; size_t size; size_t tag; };
+  struct HostBlock { void* ptr; size_t size; size_t tag; bool pinned; };
+  static void freeHost(HostBlock& b);
   struct Lock { LockType type; Device* device; };  // device == nullptr: host
   struct Entry {
     size_t tag = 1;                       // newest version of the record

@@ -90,10 +90,12 @@ private:
 
 class OracleDevice final : public Device {
 public:
-  OracleDevice() : mLayer(std::make_shared<OracleLayer>()) { oracle_set_threads(8); }
+  explicit OracleDevice(std::string name = "oracle-cpu") : mName(std::move(name)), mLayer(std::make_shared<OracleLayer>()) {
+    oracle_set_threads(8);
+  }
   auto getProvider() const -> DeviceProvider override { return DeviceProvider::HOST; }
   auto getKind() const -> DeviceKind override { return DeviceKind::CPU; }
-  std::string getDeviceName() const override { return "oracle-cpu"; }
+  std::string getDeviceName() const override { return mName; }
   bool hasAllocator() override { return true; }
   std::vector<std::shared_ptr<Device>> partition(PartitionDomain) override { return {}; }
   std::shared_ptr<AllocatorLayerBase> getAllocator() override { return mLayer; }
@@ -163,6 +165,7 @@ public:
   }
 
 private:
+  std::string mName;
   std::shared_ptr<OracleLayer> mLayer;
 };
 

@@ -89,3 +89,14 @@ def test_reference_lspolar_loads_the_plugin():
         assert "Provider   : CUDA" in out.stdout and "Kind       : GPU" in out.stdout
     else:
         assert "Total device count: 0" in out.stdout
+
+
+ALLOC_TEST = os.path.join(ROOT, "polarai-framework_b200", "lib", "ref", "pool_allocator_test")
+
+
+@pytest.mark.skipif(not os.path.exists(ALLOC_TEST), reason="allocator unit tests are not built")
+def test_pool_backend_allocator_host_logic():
+    # coherence, lock conflicts and error statuses of the BackendAllocator, with fake devices (no CUDA needed)
+    out = subprocess.run([ALLOC_TEST], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "4 ran, 0 failed, 0 skipped" in out.stdout
