@@ -207,6 +207,8 @@ def per_op_times(torch, ex, reps):
             if kernel is None:
                 if ex.allreduce is not None:
                     ex.allreduce(ex.t[arr])
+            elif kernel == "peers":
+                ex.peers.launch(arr[0], arr[1], arr[2], s)
             else:
                 ex.lib.check(ex._fn(kernel, arr, n, ex._ws_ptr, ex._ws_bytes, s))
             b.record()
@@ -224,7 +226,9 @@ def run_mlp(args):
     import __graft_entry__ as ge
     pkg = ge.load_package()
     from polarai_framework_b200.data_parallel import init_from_env, make_allreduce, shard_rows
-    from polarai_framework_b200.program import DeviceExecutor, fuse_program, mlp_program
+    from polarai_framework_b200.peer_gradients import PeerGradients
+    from polarai_framework_b200.program import (DeviceExecutor, fuse_gradient_exchange, fuse_program,
+                                                mlp_program)
 
     rank, world, local = init_from_env()
     if world != args.gpus:
@@ -236,10 +240,31 @@ def run_mlp(args):
     rng = np.random.default_rng(0)
     W1, W2 = mlp_weights(rng)                               # identical on every rank
     Xs, Ys = mlp_inputs(np.random.default_rng(1000 + rank), per)   # this rank's rows
-    program = mlp_program(per, N_IN, N_HIDDEN, N_OUT, LR)
-    if args.fused:
-        program = fuse_program(program)
-    ex = DeviceExecutor(program, dev, make_allreduce(world))
+    chain = mlp_program(per, N_IN, N_HIDDEN, N_OUT, LR)
+    fused = args.builtins == "extended"
+    program = fuse_program(chain) if fused else chain
+    # Gradient exchange: one kernel per rank over NVLink peer memory (sum over ranks + weight
+    # update), or NCCL all-reduces followed by the fadd updates.  Mapping the peers' buffers can
+    # fail (no peer access, IPC closed in the container): every rank then takes the NCCL form.
+    peers, collective = None, "none (one rank)"
+    if world > 1:
+        collective = "nccl all-reduce, then fadd updates"
+        if fused and args.collective == "peer":
+            xprog = fuse_gradient_exchange(program)
+            why = ""
+            try:
+                peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, rank, world, dev)
+            except Exception as exc:                        # noqa: BLE001 - any failure means "not available"
+                why = f"{type(exc).__name__}: {exc}"
+            ok = torch.tensor([0 if peers is None else 1], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 1:
+                program = xprog
+                collective = "peer memory over NVLink: sum over ranks and weight update in one kernel per rank"
+            else:
+                peers = None
+                collective += f" (peer memory unavailable on some rank{': ' + why if why else ''})"
+    ex = DeviceExecutor(program, dev, make_allreduce(world), peers=peers)
     x_host = torch.from_numpy(Xs).pin_memory()
     y_host = torch.from_numpy(Ys).pin_memory()
     w1, w2 = torch.from_numpy(W1).to(dev), torch.from_numpy(W2).to(dev)
@@ -336,10 +361,10 @@ def run_mlp(args):
     # Clocks are sampled over both timed regions (device-resident and end to end).
     # At 8 GPUs one region lasts about 25 ms, shorter than nvidia-smi's period, so
     # every rank runs the same number of further steps (the count derives from the
-    # max-reduced step time, identical on all ranks) until about 0.3 s are covered.
+    # max-reduced step time, identical on all ranks) until about 1 s is covered.
     covered_ms = (ms_per_step + e2e_ms) * args.steps
-    if covered_ms < 300.0:
-        for _ in range(int((300.0 - covered_ms) / ms_per_step) + 1):
+    if covered_ms < 1000.0:
+        for _ in range(int((1000.0 - covered_ms) / ms_per_step) + 1):
             timed_step()
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
@@ -398,8 +423,9 @@ def run_mlp(args):
             "config": {"workload": "mlp_784_4096_10_fwd_bwd_sgd", "global_batch": GLOBAL_BATCH,
                        "per_gpu_batch": per, "lr": LR, "parallelism": f"dp{world}",
                        "cuda_graph": graph is not None,
-                       "builtins": "extended (fused, bit-identical results)" if args.fused
-                       else "the reference's builtin chain, one launch per builtin",
+                       "builtins": "extended (fused launches, every output bit-identical to the builtin chain)"
+                       if fused else "the reference's builtin chain, one launch per builtin",
+                       "collective": collective,
                        "l2": "per-step working set (X 205 MB/GPU-share, seven Bx4096 activations) "
                              "exceeds the 126 MB L2 at every N"},
             "flop_per_sample": FLOP_PER_SAMPLE, "tflops": value * FLOP_PER_SAMPLE / 1e12,
@@ -408,21 +434,23 @@ def run_mlp(args):
             "launches_per_step": launches_per_step,
             "clocks": clocks, "e2e": e2e, "roofline": roofline,
             "breakdown_ms": {k: round(v["ms"], 4) for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1]["ms"])}}
-    if not args.fused and not args.no_extras:
-        # The same step with the extended (fused) builtins: bit-identical results in 13
-        # launches instead of 20.  Every rank runs it (its all-reduces are collective).
-        fex = DeviceExecutor(fuse_program(program), dev, make_allreduce(world))
-        fex.t["X"].copy_(ex.t["X"]), fex.t["Y"].copy_(ex.t["Y"])
-        fex.t["W1"].copy_(w1), fex.t["W2"].copy_(w2)
+    status = int(lib.cdll.polar_b200_device_status())
+    line["device_status"] = status                          # 0: no bounded device-side wait gave up
+    if fused and not args.no_extras:
+        # The same step as the reference's own builtin chain, one launch per builtin (20 launches
+        # instead of 12-13) with NCCL all-reduces: same outputs bit for bit at one rank.  Every
+        # rank runs it (its all-reduces are collective).
+        cex = DeviceExecutor(chain, dev, make_allreduce(world))
+        cex.t["X"].copy_(ex.t["X"]), cex.t["Y"].copy_(ex.t["Y"])
+        cex.t["W1"].copy_(w1), cex.t["W2"].copy_(w2)
         for _ in range(3):
-            fex.run()
-        fms = time_region(torch, fex.run, args.steps, dist, world) / args.steps
-        line["fused_program"] = {"value": GLOBAL_BATCH / (fms / 1e3), "unit": "samples/s", "ms_per_step": fms,
-                                 "launches_per_step": fex.program.launches(), "cuda_graph": False,
-                                 "note": "fmatmul+fsigmoid, fmatmul+sigmoid derivative and the sigmoid "
-                                         "derivative chain as single launches; every program output is "
-                                         "bit-identical to the unfused program"}
-        del fex
+            cex.run()
+        cms = time_region(torch, cex.run, args.steps, dist, world) / args.steps
+        line["builtin_chain"] = {"value": GLOBAL_BATCH / (cms / 1e3), "unit": "samples/s", "ms_per_step": cms,
+                                 "launches_per_step": chain.launches(), "cuda_graph": False,
+                                 "note": "the unfused program: one launch per reference builtin, NCCL "
+                                         "all-reduce of dW2 and dW1, fadd updates"}
+        del cex
     if rank == 0 and world == 1 and not args.no_extras:
         line["cpu_baseline"] = cpu_mlp_baseline(2048, steps=1)[0]
         # the bandwidth numbers first: the GEMM loop leaves the GPU at its power cap
@@ -565,8 +593,12 @@ def main():
                     help="gemm: m=n=k (default 8192); elementwise: log2 of the element count (default 28)")
     ap.add_argument("--batch", type=int, default=0,
                     help="mlp: global batch override for profiling small cases (default 65536, the metric's)")
-    ap.add_argument("--fused", action="store_true",
-                    help="mlp: run the program with the extended (fused) builtins; results are bit-identical")
+    ap.add_argument("--builtins", default="extended", choices=["extended", "reference"],
+                    help="mlp: 'extended' runs the fused launches (every output bit-identical to the chain), "
+                         "'reference' one launch per reference builtin")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="mlp at N>1 with extended builtins: gradient sum + update as one peer-memory kernel, "
+                         "or NCCL all-reduces followed by fadd")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

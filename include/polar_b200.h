@@ -298,6 +298,49 @@ int polar_b200_launch_by_name(const char* nativeKernelName,
                               void* workspace, uint64_t workspace_bytes,
                               void* stream);
 
+/* ---- Gradient exchange over NVLink peer memory (data-parallel step) -------------
+ * No counterpart in the reference: it runs every node on one device
+ * (ExecutorImpl.cpp:71-75) and has no collective.  What the fused launch replaces on
+ * each rank is the pair "sum dW over ranks" + the reference's own weight update
+ * fadd(W, 1, dW, -lr) (AddOperationInternal.cpp:61-66); the update's arithmetic is
+ * fadd's, so a replica ends with the bits the two-step form gives for the same sum.
+ *
+ * A peer buffer = POLAR_B200_PEER_CONTROL_BYTES of control words (zeroed by
+ * polar_b200_peer_alloc, then owned by the kernels) followed by the payload (the
+ * gradient vector, padded with zeros to 16 bytes).  Each rank allocates one, exports
+ * it as a CUDA IPC handle, and opens every other rank's handle; ranks must be
+ * distinct processes on GPUs with peer access (NVLink). */
+#define POLAR_B200_MAX_PEERS 16
+#define POLAR_B200_MAX_UPDATE_SEGMENTS 8
+#define POLAR_B200_PEER_CONTROL_BYTES 256
+#define POLAR_B200_PEER_HANDLE_BYTES 64
+
+int polar_b200_peer_alloc(uint64_t payload_bytes, void** buffer);
+int polar_b200_peer_free(void* buffer);
+int polar_b200_peer_export(void* buffer, unsigned char handle[POLAR_B200_PEER_HANDLE_BYTES]);
+int polar_b200_peer_open(const unsigned char handle[POLAR_B200_PEER_HANDLE_BYTES], void** buffer);
+int polar_b200_peer_close(void* buffer);
+
+typedef struct polar_b200_update_segment {
+  float* weights;   /* this rank's replica of one weight tensor (16-byte aligned) */
+  uint64_t offset;  /* where its gradient starts in the payload, in floats (multiple of 4) */
+  uint64_t count;   /* elements */
+} polar_b200_update_segment;
+
+/* One launch per rank, all ranks of the group in the same step:
+ *   payload <- sum over ranks of payload   (ranks added in ascending order: every rank
+ *                                            ends with the same bits, in every buffer)
+ *   weights[i] <- fl(fl(weights[i]*scale_w) + fl(payload[offset+i]*scale_g))  per segment
+ * `buffers[r]` is rank r's peer buffer as mapped in THIS process (own buffer at
+ * buffers[rank]); `n` is the payload length in floats.  The ranks' kernels wait for one
+ * another with a bound of 4 s; a wait that gives up sets polar_b200_device_status() to
+ * 301 (a peer's gradient never became ready) or 302 (a peer never finished its slice)
+ * and the launch still terminates.  The launches that produced the payload must precede
+ * this one on `stream`.  world == 1 is valid (no exchange, update only). */
+int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
+                              const polar_b200_update_segment* segments, uint32_t n_segments,
+                              float scale_w, float scale_g, void* stream);
+
 /* Number of kernels this library has launched since it was loaded (all
  * threads), for launch accounting in benchmarks. */
 uint64_t polar_b200_launch_count(void);

@@ -25,6 +25,15 @@ class OracleExecutor:
                 if self.allreduce is not None:
                     t[args[0]] = self.allreduce(t[args[0]])
                 continue
+            if kernel == "ALLREDUCE_FADD":
+                # sum over ranks, then the reference's update fadd(W, sw, g, sg) per pair
+                for i in range(2, len(args), 2):
+                    w, gname = args[i], args[i + 1]
+                    if self.allreduce is not None:
+                        t[gname] = self.allreduce(t[gname])
+                    t[w] = np.asarray(o.fadd(t[w].ravel(), args[0], t[gname].ravel(), args[1]),
+                                      np.float32).reshape(self.program.tensors[w])
+                continue
             out = args[-1]
             shape = self.program.tensors[out]
             if kernel == "fadd":

@@ -60,6 +60,13 @@ SIGNATURES = {
     "polar_b200_device_status": (_i, []),
     "polar_b200_device_status_clear": (None, []),
     "polar_b200_fsum": (_i, [_p, _p, _u64, _p]),
+    "polar_b200_peer_alloc": (_i, [_u64, ctypes.POINTER(_p)]),
+    "polar_b200_peer_free": (_i, [_p]),
+    "polar_b200_peer_export": (_i, [_p, ctypes.POINTER(ctypes.c_ubyte)]),
+    "polar_b200_peer_open": (_i, [ctypes.POINTER(ctypes.c_ubyte), ctypes.POINTER(_p)]),
+    "polar_b200_peer_close": (_i, [_p]),
+    "polar_b200_allreduce_fadd": (_i, [ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32, _u64, _p,
+                                       ctypes.c_uint32, _f, _f, _p]),
     "polar_b200_launch_by_name": (_i, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64, _p, _u64, _p]),
     "polar_b200_launch_count": (_u64, []),
 }

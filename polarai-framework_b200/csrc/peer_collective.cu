@@ -1,0 +1,296 @@
+// Gradient exchange of the data-parallel step as ONE kernel over NVLink peer memory:
+// sum of a gradient vector over ranks fused with the weight update that consumes it.
+//
+// The reference has no collective (every node runs on devices.front(),
+// ExecutorImpl.cpp:71-75 of the reference) and updates weights with a separate
+// fadd(W, 1, dW, -lr) launch (AddOperationInternal.cpp:61-66).  Here every rank holds
+// its gradient vector G in a buffer its peers have mapped (CUDA IPC); one launch per
+// rank then
+//   1. tells every peer "my G of step s is complete" and waits for the same from all,
+//   2. sums slice `rank` of G over all ranks (loads over NVLink, ranks in ascending
+//      order, so every rank computes the same bits) and stores the sum into slice
+//      `rank` of EVERY rank's G (stores over NVLink),
+//   3. tells every peer "slice `rank` is in place" and waits for the same from all,
+//   4. applies W = fl(fl(W*sw) + fl(G*sg)) - fadd's arithmetic - on its own replica.
+// Nothing else touches slice r of any rank's G between 1 and 3, so the exchange is in
+// place.  No multicast object, no TMA: plain peer loads and stores.
+//
+// Flags are step numbers that only grow, so nothing is ever reset and a rank that is
+// one step ahead cannot confuse a slower one.  Every wait is bounded (kWaitNs); a wait
+// that gives up writes 301 (ready) or 302 (done) to the status word, the data phases
+// still run to completion on whatever is there, and the host reads the word after it
+// has synchronised the stream.
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace polar_b200 {
+namespace tc {
+extern int* g_status_dev;
+int ensure_status();
+}  // namespace tc
+
+namespace peer {
+
+constexpr int kMaxWorld = POLAR_B200_MAX_PEERS;
+constexpr int kMaxSegments = POLAR_B200_MAX_UPDATE_SEGMENTS;
+constexpr int kThreads = 512;
+constexpr unsigned long long kWaitNs = 4000000000ull;   // 4 s
+
+// Control words at the head of every rank's buffer (uint32 each).
+constexpr int kReady = 0;                 // [kMaxWorld] written by peer p at index p
+constexpr int kDone = kMaxWorld;          // [kMaxWorld]
+constexpr int kStep = 2 * kMaxWorld;      // local: last completed step
+constexpr int kTicketA = kStep + 1;       // local: CTAs that finished phase 2
+constexpr int kTicketB = kStep + 2;       // local: CTAs that finished phase 4
+static_assert((2 * kMaxWorld + 3) * 4 <= POLAR_B200_PEER_CONTROL_BYTES, "control block too small");
+
+struct Segment {
+  float* w;
+  uint64_t offset;   // in floats, into G
+  uint64_t count;
+};
+
+struct Params {
+  unsigned char* base[kMaxWorld];   // every rank's buffer (own one included), control block first
+  Segment seg[kMaxSegments];
+  uint64_t n4;                      // length of G in float4
+  uint32_t rank, world, n_seg;
+  float scale_w, scale_g;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_peer(const float4* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer(float4* p, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Threads 0..world-1 of the CTA each watch one peer's word until it reaches `step`.
+__device__ __forceinline__ void wait_all(const uint32_t* words, uint32_t world, uint32_t step, int* status,
+                                         int code) {
+  if (threadIdx.x < world) {
+    const uint32_t* w = words + threadIdx.x;
+    const unsigned long long t0 = now_ns();
+    // step numbers wrap after 2^32 steps: compare as a signed distance
+    while ((int32_t)(ld_acquire_sys(w) - step) < 0) {
+      if (now_ns() - t0 > kWaitNs) {
+        *(volatile int*)status = code;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+}
+
+template <int WORLD>   // 0 = any world size up to kMaxWorld
+__global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p) {
+  const uint32_t world = WORLD ? (uint32_t)WORLD : p.world;
+  uint32_t* ctl = reinterpret_cast<uint32_t*>(p.base[p.rank]);
+  const uint32_t step = *(volatile uint32_t*)(ctl + kStep) + 1u;
+
+  // 1. my G is complete (the launches that wrote it precede this one in the stream)
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kReady + p.rank, step);
+  }
+  wait_all(ctl + kReady, world, step, p.status, 301);
+
+  // 2. slice `rank`, summed in rank order, to everyone
+  {
+    const uint64_t per = (p.n4 + world - 1) / world;
+    const uint64_t lo = (uint64_t)p.rank * per;
+    const uint64_t hi = lo + per < p.n4 ? lo + per : p.n4;
+    for (uint64_t i = lo + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < hi;
+         i += (uint64_t)gridDim.x * kThreads) {
+      float4 v[WORLD ? WORLD : kMaxWorld];
+#pragma unroll
+      for (int r = 0; r < (WORLD ? WORLD : kMaxWorld); ++r)
+        if (r < (int)world)
+          v[r] = ld_peer(reinterpret_cast<const float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i);
+      float4 s = v[0];
+#pragma unroll
+      for (int r = 1; r < (WORLD ? WORLD : kMaxWorld); ++r)
+        if (r < (int)world) {
+          s.x = __fadd_rn(s.x, v[r].x);
+          s.y = __fadd_rn(s.y, v[r].y);
+          s.z = __fadd_rn(s.z, v[r].z);
+          s.w = __fadd_rn(s.w, v[r].w);
+        }
+#pragma unroll
+      for (int r = 0; r < (WORLD ? WORLD : kMaxWorld); ++r)
+        if (r < (int)world)
+          st_peer(reinterpret_cast<float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i, s);
+    }
+  }
+
+  // 3. the last CTA to get here tells every peer that slice `rank` is in place
+  __threadfence_system();
+  __syncthreads();
+  __shared__ uint32_t last;
+  if (threadIdx.x == 0) last = (atomicAdd(ctl + kTicketA, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (last && threadIdx.x < world) {
+    if (threadIdx.x == 0) ctl[kTicketA] = 0;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kDone + p.rank, step);
+  }
+  wait_all(ctl + kDone, world, step, p.status, 302);
+
+  // 4. fadd(W, sw, G, sg) -> W on this rank's replica
+  const float* g = reinterpret_cast<const float*>(p.base[p.rank] + POLAR_B200_PEER_CONTROL_BYTES);
+  for (uint32_t sidx = 0; sidx < p.n_seg; ++sidx) {
+    const Segment sg = p.seg[sidx];
+    const float4* g4 = reinterpret_cast<const float4*>(g + sg.offset);
+    float4* w4 = reinterpret_cast<float4*>(sg.w);
+    const uint64_t c4 = sg.count >> 2;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < c4; i += (uint64_t)gridDim.x * kThreads) {
+      const float4 gv = __ldcg(g4 + i);
+      float4 wv = w4[i];
+      wv.x = __fadd_rn(__fmul_rn(wv.x, p.scale_w), __fmul_rn(gv.x, p.scale_g));
+      wv.y = __fadd_rn(__fmul_rn(wv.y, p.scale_w), __fmul_rn(gv.y, p.scale_g));
+      wv.z = __fadd_rn(__fmul_rn(wv.z, p.scale_w), __fmul_rn(gv.z, p.scale_g));
+      wv.w = __fadd_rn(__fmul_rn(wv.w, p.scale_w), __fmul_rn(gv.w, p.scale_g));
+      w4[i] = wv;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (sg.count & 3)) {   // ragged tail of the segment
+      const uint64_t i = (c4 << 2) + threadIdx.x;
+      sg.w[i] = __fadd_rn(__fmul_rn(sg.w[i], p.scale_w), __fmul_rn(__ldcg(g + sg.offset + i), p.scale_g));
+    }
+  }
+
+  // the last CTA to finish closes the step
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(ctl + kTicketB, 1u) == gridDim.x - 1) {
+      ctl[kTicketB] = 0;
+      __threadfence();
+      *(volatile uint32_t*)(ctl + kStep) = step;
+    }
+  }
+}
+
+}  // namespace peer
+}  // namespace polar_b200
+
+using namespace polar_b200;
+
+extern "C" {
+
+int polar_b200_peer_alloc(uint64_t payload_bytes, void** buffer) {
+  clear_error();
+  if (!buffer) return fail(POLAR_B200_ERR_INVALID, "null result pointer");
+  void* p = nullptr;
+  const uint64_t total = POLAR_B200_PEER_CONTROL_BYTES + ((payload_bytes + 15) & ~15ull);
+  // A plain cudaMalloc: allocations of a stream-ordered pool cannot be exported as IPC handles.
+  cudaError_t e = cudaMalloc(&p, total);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMalloc(peer buffer)", e);
+  e = cudaMemset(p, 0, total);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(POLAR_B200_ERR_CUDA, "clearing the peer buffer", e);
+  }
+  *buffer = p;
+  return POLAR_B200_OK;
+}
+
+int polar_b200_peer_free(void* buffer) {
+  clear_error();
+  if (!buffer) return POLAR_B200_OK;
+  cudaError_t e = cudaFree(buffer);
+  return e == cudaSuccess ? POLAR_B200_OK : fail(POLAR_B200_ERR_CUDA, "cudaFree(peer buffer)", e);
+}
+
+int polar_b200_peer_export(void* buffer, unsigned char handle[POLAR_B200_PEER_HANDLE_BYTES]) {
+  clear_error();
+  static_assert(sizeof(cudaIpcMemHandle_t) == POLAR_B200_PEER_HANDLE_BYTES, "IPC handle size");
+  if (!buffer || !handle) return fail(POLAR_B200_ERR_INVALID, "null buffer or handle");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, buffer);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaIpcGetMemHandle", e);
+  memcpy(handle, &h, sizeof h);
+  return POLAR_B200_OK;
+}
+
+int polar_b200_peer_open(const unsigned char handle[POLAR_B200_PEER_HANDLE_BYTES], void** buffer) {
+  clear_error();
+  if (!buffer || !handle) return fail(POLAR_B200_ERR_INVALID, "null buffer or handle");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaIpcOpenMemHandle", e);
+  *buffer = p;
+  return POLAR_B200_OK;
+}
+
+int polar_b200_peer_close(void* buffer) {
+  clear_error();
+  if (!buffer) return POLAR_B200_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(buffer);
+  return e == cudaSuccess ? POLAR_B200_OK : fail(POLAR_B200_ERR_CUDA, "cudaIpcCloseMemHandle", e);
+}
+
+int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
+                              const polar_b200_update_segment* segments, uint32_t n_segments, float scale_w,
+                              float scale_g, void* stream) {
+  clear_error();
+  if (!buffers || world == 0 || world > (uint32_t)peer::kMaxWorld || rank >= world)
+    return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: bad rank/world or null buffer list");
+  if (n_segments > (uint32_t)peer::kMaxSegments || (n_segments && !segments))
+    return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: too many update segments");
+  if (n == 0) return POLAR_B200_OK;
+  peer::Params p{};
+  for (uint32_t r = 0; r < world; ++r) {
+    if (!buffers[r] || !aligned16(buffers[r])) return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: null or unaligned buffer");
+    p.base[r] = static_cast<unsigned char*>(buffers[r]);
+  }
+  for (uint32_t s = 0; s < n_segments; ++s) {
+    const polar_b200_update_segment& g = segments[s];
+    if (!g.weights || !aligned16(g.weights) || (g.offset & 3) || g.offset + g.count > n)
+      return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: segment outside the vector, or not 16-byte aligned");
+    p.seg[s] = peer::Segment{g.weights, g.offset, g.count};
+  }
+  int rc = tc::ensure_status();
+  if (rc) return rc;
+  p.n4 = (n + 3) / 4;   // the buffer is padded to 16 bytes by polar_b200_peer_alloc
+  p.rank = rank; p.world = world; p.n_seg = n_segments;
+  p.scale_w = scale_w; p.scale_g = scale_g;
+  p.status = tc::g_status_dev;
+  // Every CTA waits on the other ranks, so all of them must be resident at once: one per SM.
+  uint64_t most = p.n4;
+  uint64_t want = (most + peer::kThreads - 1) / peer::kThreads;
+  unsigned grid = (unsigned)(want < (uint64_t)sm_count() ? (want ? want : 1) : (uint64_t)sm_count());
+  cudaStream_t st = as_stream(stream);
+  switch (world) {
+    case 2: peer::allreduce_fadd_kernel<2><<<grid, peer::kThreads, 0, st>>>(p); break;
+    case 4: peer::allreduce_fadd_kernel<4><<<grid, peer::kThreads, 0, st>>>(p); break;
+    case 8: peer::allreduce_fadd_kernel<8><<<grid, peer::kThreads, 0, st>>>(p); break;
+    default: peer::allreduce_fadd_kernel<0><<<grid, peer::kThreads, 0, st>>>(p); break;
+  }
+  return check_launch("allreduce_fadd launch");
+}
+
+}  // extern "C"

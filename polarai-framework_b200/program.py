@@ -42,6 +42,13 @@ class Program:
     def launches(self):
         return sum(1 for k, _ in self.ops if k != "ALLREDUCE")
 
+    def exchanged(self):
+        """Names of the gradients an ALLREDUCE_FADD op sums, in payload order."""
+        for k, a in self.ops:
+            if k == "ALLREDUCE_FADD":
+                return [a[i] for i in range(3, len(a), 2)]
+        return []
+
 
 def elementwise_chain_program(n):
     """out = sigmoid((a + b) * c / d): Add -> Mul -> Divide -> Sigmoid."""
@@ -197,21 +204,76 @@ def fuse_program(program):
     return fused
 
 
+def fuse_gradient_exchange(program):
+    """Rewrites the data-parallel tail of a program
+
+        ALLREDUCE(g1) ... ALLREDUCE(gk) ... fadd(W1,sw,g1,sg,W1) ... fadd(Wk,sw,gk,sg,Wk)
+
+    into one op  ALLREDUCE_FADD(sw, sg, W1, g1, ..., Wk, gk)  at the place of the first of
+    those updates: the sum over ranks and the updates in a single launch
+    (polar_b200_allreduce_fadd).  It applies only when every ALLREDUCE'd gradient has exactly
+    such an update after the last ALLREDUCE, all with the same two scales, and nothing after the
+    first update reads a weight or gradient involved; otherwise the program is returned as is."""
+    ops = [(k, list(a)) for k, a in program.ops]
+    red = [(i, a[0]) for i, (k, a) in enumerate(ops) if k == "ALLREDUCE"]
+    if not red:
+        return program
+    last_red = max(i for i, _ in red)
+    grads = [g for _, g in red]
+    upd = {}
+    for i, (k, a) in enumerate(ops):
+        if k == "fadd" and i > last_red and a[2] in grads and a[0] == a[4] and a[2] not in upd:
+            upd[a[2]] = i
+    if sorted(upd) != sorted(grads):
+        return program
+    first = min(upd.values())
+    scales = {(ops[i][1][1], ops[i][1][3]) for i in upd.values()}
+    if len(scales) != 1:
+        return program
+    touched = set(grads) | {ops[i][1][0] for i in upd.values()}
+    for i in range(first, len(ops)):
+        if i in upd.values():
+            continue
+        if any(isinstance(x, str) and x in touched for x in ops[i][1]):
+            return program
+    sw, sg = next(iter(scales))
+    # payload order: the order the backward pass produces the gradients in
+    pairs = []
+    for _, g in red:
+        pairs += [ops[upd[g]][1][0], g]
+    new_ops = []
+    for i, op in enumerate(ops):
+        if op[0] == "ALLREDUCE" or i in upd.values():
+            if i == first:
+                new_ops.append(("ALLREDUCE_FADD", [float(sw), float(sg)] + pairs))
+            continue
+        new_ops.append(op)
+    return Program(program.name + "_xchg", dict(program.tensors), new_ops, list(program.inputs),
+                   dict(program.constants), list(program.outputs))
+
+
 class DeviceExecutor:
     """Runs a Program on one GPU: one device tensor per program tensor, every op
     through polar_b200_launch_by_name on torch's current stream.  Argument
     structs are built once, so replaying the program costs one ctypes call per
     launch.  `allreduce` is a callable taking a tensor (torch.distributed over
-    NCCL in the data-parallel runs; None = single rank, no-op)."""
+    NCCL in the data-parallel runs; None = single rank, no-op).  A program with an
+    ALLREDUCE_FADD op needs `peers`, a PeerGradients built for program.exchanged():
+    those gradients then live in its peer buffer."""
 
-    def __init__(self, program, device="cuda:0", allreduce=None):
+    def __init__(self, program, device="cuda:0", allreduce=None, peers=None):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: programs have no CPU path in this package")
         self.program = program
         self.device = torch.device(device)
         self.lib = lib()
         self.allreduce = allreduce
-        self.t = {n: torch.empty(s, dtype=torch.float32, device=self.device)
+        exchanged = program.exchanged()
+        if exchanged and (peers is None or sorted(peers.tensors) != sorted(exchanged)):
+            raise ValueError("the program exchanges gradients over peer memory: pass `peers` built for "
+                             f"{exchanged}")
+        self.peers = peers if exchanged else None
+        self.t = {n: (peers.tensors[n] if n in exchanged else torch.empty(s, dtype=torch.float32, device=self.device))
                   for n, s in program.tensors.items()}
         self._keep = []
         self._compiled = []
@@ -219,6 +281,10 @@ class DeviceExecutor:
         for kernel, args in program.ops:
             if kernel == "ALLREDUCE":
                 self._compiled.append((None, args[0], 0))
+                continue
+            if kernel == "ALLREDUCE_FADD":
+                pairs = [(self.t[args[i]], args[i + 1]) for i in range(2, len(args), 2)]
+                self._compiled.append(("peers", (peers.segments(pairs), float(args[0]), float(args[1])), 0))
                 continue
             arr = (Arg * len(args))()
             for i, a in enumerate(args):
@@ -265,6 +331,9 @@ class DeviceExecutor:
             if kernel is None:
                 if self.allreduce is not None:
                     self.allreduce(self.t[arr])
+                continue
+            if kernel == "peers":
+                self.peers.launch(arr[0], arr[1], arr[2], s)
                 continue
             rc = self._fn(kernel, arr, n, self._ws_ptr, self._ws_bytes, s)
             if rc != 0:

@@ -1,0 +1,132 @@
+"""polar_b200_allreduce_fadd: the gradient sum over ranks fused with the weight update, over
+NVLink peer memory.  One rank (always): same bits as the all-reduce-free program.  Two ranks
+(when the box has two GPUs; one process per GPU, never two waiting kernels on one GPU):
+replicas identical, and identical to NCCL all-reduce + fadd (a sum of two terms has one order)."""
+import ctypes
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _inputs(batch, hidden, seed=0):
+    rng = np.random.default_rng(seed)
+    X = rng.standard_normal((batch, 784)).astype(np.float32)
+    Y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, batch)]
+    W1 = rng.uniform(-0.05, 0.05, (784, hidden)).astype(np.float32)
+    W2 = rng.uniform(-0.2, 0.2, (hidden, 10)).astype(np.float32)
+    return X, Y, W1, W2
+
+
+def test_one_rank_equals_the_plain_program_over_several_steps():
+    import torch
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    from polarai_framework_b200.peer_gradients import PeerGradients
+    from polarai_framework_b200.program import DeviceExecutor, fuse_gradient_exchange, fuse_program, mlp_program
+    lib = pkg.lib()
+    lib.cdll.polar_b200_device_status_clear()
+    batch, hidden = 512, 1024
+    X, Y, W1, W2 = _inputs(batch, hidden)
+    fused = fuse_program(mlp_program(batch, 784, hidden, 10, 0.1))
+    xprog = fuse_gradient_exchange(fused)
+    peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, 0, 1, "cuda:0")
+    a = DeviceExecutor(fused, "cuda:0")
+    b = DeviceExecutor(xprog, "cuda:0", peers=peers)
+    for ex in (a, b):
+        ex.set_inputs(X=X, Y=Y, W1=W1, W2=W2)
+    for step in range(4):
+        a.run(), b.run()
+        for k in ("L", "W1", "W2", "dW1", "dW2"):
+            assert np.array_equal(a.output(k).view(np.uint32), b.output(k).view(np.uint32)), (step, k)
+    assert lib.cdll.polar_b200_device_status() == 0
+    del b
+    peers.close()
+
+
+def test_bad_arguments_are_statuses():
+    import torch
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    from polarai_framework_b200.peer_gradients import PeerGradients, UpdateSegment
+    lib = pkg.lib()
+    peers = PeerGradients({"g": (64,)}, 0, 1, "cuda:0")
+    w = torch.zeros(64, device="cuda")
+    fn = lib.cdll.polar_b200_allreduce_fadd
+    s = torch.cuda.current_stream().cuda_stream
+    seg = peers.segments([(w, "g")])
+    assert fn(peers.buffers, 1, 1, peers.n, seg, 1, 1.0, -0.1, s) != 0          # rank outside the group
+    assert fn(peers.buffers, 0, 17, peers.n, seg, 1, 1.0, -0.1, s) != 0         # more ranks than the control block holds
+    bad = (UpdateSegment * 1)()
+    bad[0].weights, bad[0].offset, bad[0].count = w.data_ptr(), 32, 64            # runs past the payload
+    assert fn(peers.buffers, 0, 1, peers.n, bad, 1, 1.0, -0.1, s) != 0
+    bad[0].offset, bad[0].count = 2, 8                                            # gradient not 16-byte aligned
+    assert fn(peers.buffers, 0, 1, peers.n, bad, 1, 1.0, -0.1, s) != 0
+    assert "allreduce_fadd" in lib.last_error()
+    null = (ctypes.c_void_p * 1)()
+    assert fn(null, 0, 1, peers.n, seg, 1, 1.0, -0.1, s) != 0
+    # and a good call still works afterwards: g = 3, w = 1  ->  w = 1*1 + 3*(-0.5) = -0.5
+    peers.tensors["g"].fill_(3.0)
+    w.fill_(1.0)
+    assert fn(peers.buffers, 0, 1, peers.n, seg, 1, 1.0, -0.5, s) == 0
+    torch.cuda.synchronize()
+    assert torch.all(w == -0.5) and lib.cdll.polar_b200_device_status() == 0
+    peers.close()
+
+
+def _rank_main(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    from polarai_framework_b200.data_parallel import init_from_env, make_allreduce, shard_rows
+    from polarai_framework_b200.peer_gradients import PeerGradients
+    from polarai_framework_b200.program import DeviceExecutor, fuse_gradient_exchange, fuse_program, mlp_program
+    r, w, local = init_from_env("nccl")
+    dev = f"cuda:{local}"
+    batch, hidden = 1024, 1024
+    lo, hi = shard_rows(batch, r, w)
+    X, Y, W1, W2 = _inputs(batch, hidden)
+    fused = fuse_program(mlp_program(hi - lo, 784, hidden, 10, 0.1))
+    xprog = fuse_gradient_exchange(fused)
+    peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, r, w, dev)
+    a = DeviceExecutor(fused, dev, make_allreduce(w))
+    b = DeviceExecutor(xprog, dev, peers=peers)
+    for ex in (a, b):
+        ex.set_inputs(X=X[lo:hi], Y=Y[lo:hi], W1=W1, W2=W2)
+    res = {}
+    for step in range(3):
+        a.run(), b.run()
+    torch.cuda.synchronize()
+    for k in ("W1", "W2", "dW1", "dW2"):
+        res[f"nccl_{k}"], res[f"peer_{k}"] = a.output(k), b.output(k)
+    res["status"] = np.array([pkg.lib().cdll.polar_b200_device_status()])
+    np.savez(os.path.join(out_dir, f"rank{r}.npz"), **res)
+    dist.barrier()
+    torch.cuda.synchronize()
+    del b
+    peers.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_on_two_gpus(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs: one process per GPU")
+    port = 29700 + os.getpid() % 200
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    assert int(r0["status"][0]) == 0 and int(r1["status"][0]) == 0
+    for k in ("W1", "W2", "dW1", "dW2"):
+        assert np.array_equal(r0[f"peer_{k}"], r1[f"peer_{k}"]), k            # replicas identical
+        assert np.array_equal(r0[f"peer_{k}"], r0[f"nccl_{k}"]), k            # a + b has one rounding
