@@ -26,6 +26,7 @@
 #include <polarai/core/loader/internal/AbstractLoaderInternal.hpp>
 #include <polarai/core/node/internal/AbstractNodeInternal.hpp>
 #include <polarai/core/node/internal/InputNodeInternal.hpp>
+#include <polarai/loaders/internal/ConstantLoaderInternal.hpp>
 
 #include <lib/allocators/LayerAllocator.hpp>
 #include <runtime/driver/RuntimeDriver.hpp>
@@ -34,6 +35,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <iostream>
 #include <map>
 #include <memory>
@@ -289,6 +291,25 @@ TensorInfo infoOf(TensorDesc& d) {
 
 }  // namespace
 
+// ---- constants filled on the device -------------------------------------------------------
+// The reference fills a constant tensor element by element on the host and copies it over
+// (ConstantLoaderInternal.cpp:24-31); gradient graphs create such ones/zeros tensors for every
+// differentiated node (GraphInternal.cpp:242-251,282-292).  Here an input node fed by a
+// ConstantLoader is placed on the compute device and its LOAD becomes one `ffill` launch -
+// the builtin the reference registers (CodeGen.cpp:454-462) but never emits.
+//
+// This build has no RTTI (like the reference's), so a loader's dynamic type is read off its
+// vtable pointer and compared with that of a ConstantLoaderInternal made here; the class has
+// one vtable, emitted with its key function in the frontend library.
+namespace {
+struct ConstantPeek : polarai::loaders::internal::ConstantLoaderInternal {
+  static float value(const polarai::loaders::internal::ConstantLoaderInternal& c) {
+    return c.*(&ConstantPeek::mFloatValue);
+  }
+};
+inline const void* vtableOf(const void* object) { return *static_cast<const void* const*>(object); }
+}  // namespace
+
 class ExecutorImpl {
 public:
   using FilterFunctionT = Executor::FilterFunctionT;
@@ -331,9 +352,12 @@ public:
     handle.allocator = mAllocator;
     handle.devices.push_back(mDevices.front());
     handle.devices.push_back(mHost);
-    // Input nodes run on the host: their loaders fill host memory (ExecutorImpl.cpp:77-93).
+    // Input nodes run on the host: their loaders fill host memory (ExecutorImpl.cpp:77-93) -
+    // except constants, which are filled where they are used.
     auto& traversal = graph.traverse();
     auto ctx = graph.getContext().internal();
+    polarai::loaders::internal::ConstantLoaderInternal constantProbe(ctx, 0, 0.0f);
+    std::unordered_map<uint64_t, float> constants;   // input node -> fill value
     for (const auto& cluster : traversal.getClusters()) {
       for (const auto& node : cluster.content) {
         auto& n = ctx->getRef<AbstractNodeInternal>(node.nodeIndex);
@@ -341,6 +365,11 @@ public:
         auto& inp = ctx->getRef<InputNodeInternal>(node.nodeIndex);
         auto& loader = ctx->getRef<AbstractLoaderInternal>(inp.getLoader());
         handle.mLoaders[node.nodeIndex] = &loader;
+        if (mDeviceConstants && vtableOf(&loader) == vtableOf(&constantProbe)) {
+          constants[node.nodeIndex] =
+              ConstantPeek::value(static_cast<const polarai::loaders::internal::ConstantLoaderInternal&>(loader));
+          continue;   // stays on the compute device: ath_device_select sends only host nodes to the host
+        }
         handle.isHostNode.insert(node.nodeIndex);
       }
     }
@@ -362,7 +391,19 @@ public:
           // Work on a device is stream-ordered, so the lock can go as soon as the
           // launch is queued; no event is attached.
           case Command::RELEASE: ath_release(&handle, *device, &ti, nullptr); break;
-          case Command::LOAD: ath_load(&handle, node.nodeId, &ti); break;
+          case Command::LOAD: {
+            auto cst = constants.find(node.nodeId);
+            if (cst == constants.end()) {
+              ath_load(&handle, node.nodeId, &ti);
+              break;
+            }
+            ArgDesc fillArgs[2] = {{sizeof(float), &cst->second, ArgDesc::DATA}, {0, &ti, ArgDesc::TENSOR}};
+            std::string kernelName = node.name + "_ffill";
+            LaunchCommand cmd{kernelName.c_str(), 2, fillArgs, "ffill"};
+            Event* evt = ath_launch(&handle, device, nullptr, cmd);
+            if (evt) pending.push_back(evt);
+            break;
+          }
           case Command::LAUNCH: {
             std::vector<TensorInfo> infos(c.args.size());
             std::vector<ArgDesc> args(c.args.size());
@@ -400,6 +441,8 @@ public:
 
 private:
   bool mDebug;
+  // POLAR_B200_HOST_CONSTANTS=1 keeps the reference's host-side constant fill
+  bool mDeviceConstants = std::getenv("POLAR_B200_HOST_CONSTANTS") == nullptr;
   FilterFunctionT mFilter;
   // The driver owns the plugin library: it must outlive the devices' users.
   std::shared_ptr<RuntimeDriver> mRuntimeDriver;

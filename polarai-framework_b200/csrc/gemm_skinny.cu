@@ -222,13 +222,15 @@ small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__
     __syncthreads();
     if (live) {
       int kk = 0;
-      for (; kk + 4 <= ks; kk += 4) {
-        float4 a[4];
+      // eight 128-bit loads in flight per thread: two CTAs of 256 threads per SM then keep
+      // 64 KB outstanding, what HBM latency x bandwidth asks of one SM
+      for (; kk + 8 <= ks; kk += 8) {
+        float4 a[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
           a[u] = __ldcs(reinterpret_cast<const float4*>(left + (k0 + kk + u) * m + m0));
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
 #pragma unroll
           for (int j = 0; j < NP; ++j) {
             float b = bs[kk + u][j];
@@ -301,38 +303,53 @@ small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, 
       b[c][kk] = (j0 + c < n && (uint64_t)kk < k) ? right[(uint64_t)kk * rsk + (j0 + c) * rsj] : 0.f;
   __syncthreads();
   if (j0 >= n) return;
-  for (int r = 0; r < rows; ++r) {
-    float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
-#pragma unroll
-    for (int kk = 0; kk < KP; ++kk) {
-      float a = as[r][kk];
-      c0 = fmaf(a, b[0][kk], c0);
-      c1 = fmaf(a, b[1][kk], c1);
-      c2 = fmaf(a, b[2][kk], c2);
-      c3 = fmaf(a, b[3][kk], c3);
-    }
-    float* dst = out + (row0 + r) * n + j0;
+  const bool vec = vec_store && j0 + 4 <= n;
+  // Rows in groups of four: the four loads of the sigmoid values are issued before any of
+  // the arithmetic, so each thread keeps four 128-bit loads in flight.
+  for (int rb = 0; rb < rows; rb += 4) {
+    float4 sv[4];
     if (sig) {
-      // fused Sigmoid derivative: out = product * ((1 - s) * s), s = fsigmoid output
-      const float* sp = sig + (row0 + r) * n + j0;
-      if (vec_store && j0 + 4 <= n) {
-        float4 sv = __ldcs(reinterpret_cast<const float4*>(sp));
-        c0 = sigmoid_grad_chain(c0, sv.x); c1 = sigmoid_grad_chain(c1, sv.y);
-        c2 = sigmoid_grad_chain(c2, sv.z); c3 = sigmoid_grad_chain(c3, sv.w);
-      } else {
-        c0 = sigmoid_grad_chain(c0, sp[0]);
-        if (j0 + 1 < n) c1 = sigmoid_grad_chain(c1, sp[1]);
-        if (j0 + 2 < n) c2 = sigmoid_grad_chain(c2, sp[2]);
-        if (j0 + 3 < n) c3 = sigmoid_grad_chain(c3, sp[3]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (rb + u >= rows) continue;
+        const float* sp = sig + (row0 + rb + u) * n + j0;
+        if (vec) {
+          sv[u] = __ldcs(reinterpret_cast<const float4*>(sp));
+        } else {
+          sv[u].x = sp[0];
+          sv[u].y = (j0 + 1 < n) ? sp[1] : 0.f;
+          sv[u].z = (j0 + 2 < n) ? sp[2] : 0.f;
+          sv[u].w = (j0 + 3 < n) ? sp[3] : 0.f;
+        }
       }
     }
-    if (vec_store && j0 + 4 <= n) {
-      __stcs(reinterpret_cast<float4*>(dst), make_float4(c0, c1, c2, c3));
-    } else {
-      dst[0] = c0;
-      if (j0 + 1 < n) dst[1] = c1;
-      if (j0 + 2 < n) dst[2] = c2;
-      if (j0 + 3 < n) dst[3] = c3;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = rb + u;
+      if (r >= rows) continue;
+      float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KP; ++kk) {
+        float a = as[r][kk];
+        c0 = fmaf(a, b[0][kk], c0);
+        c1 = fmaf(a, b[1][kk], c1);
+        c2 = fmaf(a, b[2][kk], c2);
+        c3 = fmaf(a, b[3][kk], c3);
+      }
+      if (sig) {
+        // fused Sigmoid derivative: out = product * ((1 - s) * s), s = fsigmoid output
+        c0 = sigmoid_grad_chain(c0, sv[u].x); c1 = sigmoid_grad_chain(c1, sv[u].y);
+        c2 = sigmoid_grad_chain(c2, sv[u].z); c3 = sigmoid_grad_chain(c3, sv[u].w);
+      }
+      float* dst = out + (row0 + r) * n + j0;
+      if (vec) {
+        __stcs(reinterpret_cast<float4*>(dst), make_float4(c0, c1, c2, c3));
+      } else {
+        dst[0] = c0;
+        if (j0 + 1 < n) dst[1] = c1;
+        if (j0 + 2 < n) dst[2] = c2;
+        if (j0 + 3 < n) dst[3] = c3;
+      }
     }
   }
 }

@@ -57,9 +57,17 @@ def test_reference_autograd_runs_through_the_executor_on_the_oracle_device(batch
     # direct Executor on the oracle device; at batch 1 the result equals the analytic SGD step.
     out = subprocess.run([PARITY, str(batch)], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
-    assert "oracle device: 18 launches" in out.stdout
+    # 18 builtins of the two graphs + 7 constant tensors (ones/zeros of the gradient graph, the
+    # learning rate) filled on the device by ffill instead of the reference's host loop
+    assert "oracle device: 25 launches" in out.stdout
     if batch == 1:
         assert "analytic SGD step" in out.stdout
+    # with the reference's host-side constant fill the same numbers come out of 18 launches
+    env = dict(os.environ, POLAR_B200_HOST_CONSTANTS="1")
+    host = subprocess.run([PARITY, str(batch)], capture_output=True, text=True, timeout=300, env=env)
+    assert host.returncode == 0, host.stdout + host.stderr
+    assert "oracle device: 18 launches" in host.stdout
+    assert host.stdout.split("launches", 1)[1] == out.stdout.split("launches", 1)[1]
 
 
 @pytest.mark.gpu
