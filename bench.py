@@ -270,7 +270,6 @@ def run_mlp(args):
     w1, w2 = torch.from_numpy(W1).to(dev), torch.from_numpy(W2).to(dev)
     ex.t["X"].copy_(x_host), ex.t["Y"].copy_(y_host)
     loss_acc = torch.zeros(1, dtype=torch.float64, device=dev)
-    loss_host = torch.zeros(1, dtype=torch.float64).pin_memory()
     lib = pkg.lib()
 
     def reset_weights():
@@ -338,8 +337,19 @@ def run_mlp(args):
             stage_y.copy_(y_host, non_blocking=True)
             ev_staged.record(copy_stream)
 
+    # The loss of step i is read on the host while step i+1 is already queued: the read-back
+    # goes to one of two pinned slots and the host waits for the PREVIOUS step's slot, so the
+    # GPU is never idle while the host issues the next step.  Every step's loss is read; the
+    # last one after the region's closing synchronize.
+    loss_slots = torch.zeros(2, dtype=torch.float64).pin_memory()
+    ev_loss = [torch.cuda.Event(), torch.cuda.Event()]
+    losses_read = []
+    e2e_count = [0]
+
     def e2e_step():
         cur = torch.cuda.current_stream()
+        i = e2e_count[0]
+        e2e_count[0] += 1
         cur.wait_event(ev_staged)
         ex.t["X"].copy_(stage_x, non_blocking=True)
         ex.t["Y"].copy_(stage_y, non_blocking=True)
@@ -350,13 +360,20 @@ def run_mlp(args):
         loss_acc.zero_()
         ex.lib.call("polar_b200_fsum", ex.t["L"].data_ptr(), loss_acc.data_ptr(), ex.t["L"].numel(),
                     cur.cuda_stream)
-        loss_host.copy_(loss_acc, non_blocking=True)
-        cur.synchronize()                                   # the caller reads the loss each step
+        loss_slots[i % 2:i % 2 + 1].copy_(loss_acc, non_blocking=True)
+        ev_loss[i % 2].record(cur)
+        if i > 0:
+            ev_loss[(i - 1) % 2].synchronize()
+            losses_read.append(float(loss_slots[(i - 1) % 2]))
 
     reset_weights()
     prefetch()
     e2e_step()
     e2e_ms = time_region(torch, e2e_step, args.steps, dist, world) / args.steps
+    losses_read.append(float(loss_slots[(e2e_count[0] - 1) % 2]))
+    # the same host-to-device copy with the GPU otherwise idle: the floor PCIe sets for a step
+    h2d_ms = event_time(torch, lambda: (stage_x.copy_(x_host, non_blocking=True),
+                                        stage_y.copy_(y_host, non_blocking=True)), 3, warmup=1)
     copy_stream.synchronize()
     # Clocks are sampled over both timed regions (device-resident and end to end).
     # At 8 GPUs one region lasts about 25 ms, shorter than nvidia-smi's period, so
@@ -372,7 +389,10 @@ def run_mlp(args):
            "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 4) * world,
            "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_ms,
            "path": "pinned host X,Y shard -> cudaMemcpyAsync on a copy stream (overlaps the previous step) -> "
-                   "device-to-device into the program's inputs -> builtin program -> fsum -> 8-byte loss readback"}
+                   "device-to-device into the program's inputs -> builtin program -> fsum -> 8-byte loss readback "
+                   "(the host reads step i's loss after queuing step i+1)",
+           "losses_read": len(losses_read), "h2d_copy_alone_ms": h2d_ms,
+           "h2d_copy_alone_gbs": (x_host.numel() + y_host.numel()) * 4 / (h2d_ms / 1e3) / 1e9}
 
     # ---- first-step loss, for the record ----
     reset_weights()
