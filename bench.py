@@ -454,6 +454,8 @@ def run_mlp(args):
             "launches_per_step": launches_per_step,
             "clocks": clocks, "e2e": e2e, "roofline": roofline,
             "breakdown_ms": {k: round(v["ms"], 4) for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1]["ms"])}}
+    if peers is not None:
+        line["exchange_phases_us"] = {k: round(v, 1) for k, v in peers.phase_times_us().items()}
     status = int(lib.cdll.polar_b200_device_status())
     line["device_status"] = status                          # 0: no bounded device-side wait gave up
     if fused and not args.no_extras:

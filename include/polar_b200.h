@@ -306,7 +306,8 @@ int polar_b200_launch_by_name(const char* nativeKernelName,
  * fadd's, so a replica ends with the bits the two-step form gives for the same sum.
  *
  * A peer buffer = POLAR_B200_PEER_CONTROL_BYTES of control words (zeroed by
- * polar_b200_peer_alloc, then owned by the kernels) followed by the payload (the
+ * polar_b200_peer_alloc, then owned by the kernels; 64-bit words 20..24 hold the last
+ * launch's phase timestamps in ns for profiling) followed by the payload (the
  * gradient vector, padded with zeros to 16 bytes).  Each rank allocates one, exports
  * it as a CUDA IPC handle, and opens every other rank's handle; ranks must be
  * distinct processes on GPUs with peer access (NVLink). */

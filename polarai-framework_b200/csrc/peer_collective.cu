@@ -45,7 +45,10 @@ constexpr int kDone = kMaxWorld;          // [kMaxWorld]
 constexpr int kStep = 2 * kMaxWorld;      // local: last completed step
 constexpr int kTicketA = kStep + 1;       // local: CTAs that finished phase 2
 constexpr int kTicketB = kStep + 2;       // local: CTAs that finished phase 4
-static_assert((2 * kMaxWorld + 3) * 4 <= POLAR_B200_PEER_CONTROL_BYTES, "control block too small");
+// %globaltimer (ns) of CTA 0 in the last launch: start, gradients of all ranks ready, slice
+// summed and stored, all slices in place, update done.  Five 64-bit words, for profiling.
+constexpr int kStamps = 40;
+static_assert((kStamps + 10) * 4 <= POLAR_B200_PEER_CONTROL_BYTES, "control block too small");
 
 struct Segment {
   float* w;
@@ -70,6 +73,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Payload accesses are strong operations at system scope.  Weak (ld.cg/st.cg) and volatile
+// forms were measured at two ranks and move the slice in the same 25 us, so the form the
+// memory model is clearest about stays.
 __device__ __forceinline__ float4 ld_peer(const float4* p) {
   float4 v;
   asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -109,6 +115,9 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
   const uint32_t world = WORLD ? (uint32_t)WORLD : p.world;
   uint32_t* ctl = reinterpret_cast<uint32_t*>(p.base[p.rank]);
   const uint32_t step = *(volatile uint32_t*)(ctl + kStep) + 1u;
+  unsigned long long* stamps = reinterpret_cast<unsigned long long*>(ctl + kStamps);
+  const bool stamper = blockIdx.x == 0 && threadIdx.x == 0;
+  if (stamper) stamps[0] = now_ns();
 
   // 1. my G is complete (the launches that wrote it precede this one in the stream)
   if (blockIdx.x == 0 && threadIdx.x < world) {
@@ -116,38 +125,54 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kReady + p.rank, step);
   }
   wait_all(ctl + kReady, world, step, p.status, 301);
+  if (stamper) stamps[1] = now_ns();
 
   // 2. slice `rank`, summed in rank order, to everyone
   {
     const uint64_t per = (p.n4 + world - 1) / world;
     const uint64_t lo = (uint64_t)p.rank * per;
     const uint64_t hi = lo + per < p.n4 ? lo + per : p.n4;
-    for (uint64_t i = lo + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < hi;
-         i += (uint64_t)gridDim.x * kThreads) {
-      float4 v[WORLD ? WORLD : kMaxWorld];
+    // With few ranks a thread has many elements and one NVLink round trip per element would
+    // be a chain of latencies: UNR elements' loads are issued together.
+    constexpr int W = WORLD ? WORLD : kMaxWorld;
+    constexpr int UNR = WORLD == 2 ? 4 : (WORLD == 4 ? 2 : 1);
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i0 = lo + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i0 < hi; i0 += stride * UNR) {
+      float4 v[UNR][W];
 #pragma unroll
-      for (int r = 0; r < (WORLD ? WORLD : kMaxWorld); ++r)
-        if (r < (int)world)
-          v[r] = ld_peer(reinterpret_cast<const float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i);
-      float4 s = v[0];
+      for (int u = 0; u < UNR; ++u) {
+        const uint64_t i = i0 + (uint64_t)u * stride;
+        if (i >= hi) continue;
 #pragma unroll
-      for (int r = 1; r < (WORLD ? WORLD : kMaxWorld); ++r)
-        if (r < (int)world) {
-          s.x = __fadd_rn(s.x, v[r].x);
-          s.y = __fadd_rn(s.y, v[r].y);
-          s.z = __fadd_rn(s.z, v[r].z);
-          s.w = __fadd_rn(s.w, v[r].w);
-        }
+        for (int r = 0; r < W; ++r)
+          if (r < (int)world)
+            v[u][r] = ld_peer(reinterpret_cast<const float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i);
+      }
 #pragma unroll
-      for (int r = 0; r < (WORLD ? WORLD : kMaxWorld); ++r)
-        if (r < (int)world)
-          st_peer(reinterpret_cast<float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i, s);
+      for (int u = 0; u < UNR; ++u) {
+        const uint64_t i = i0 + (uint64_t)u * stride;
+        if (i >= hi) continue;
+        float4 s = v[u][0];
+#pragma unroll
+        for (int r = 1; r < W; ++r)
+          if (r < (int)world) {
+            s.x = __fadd_rn(s.x, v[u][r].x);
+            s.y = __fadd_rn(s.y, v[u][r].y);
+            s.z = __fadd_rn(s.z, v[u][r].z);
+            s.w = __fadd_rn(s.w, v[u][r].w);
+          }
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < (int)world)
+            st_peer(reinterpret_cast<float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i, s);
+      }
     }
   }
 
   // 3. the last CTA to get here tells every peer that slice `rank` is in place
   __threadfence_system();
   __syncthreads();
+  if (stamper) stamps[2] = now_ns();
   __shared__ uint32_t last;
   if (threadIdx.x == 0) last = (atomicAdd(ctl + kTicketA, 1u) == gridDim.x - 1) ? 1u : 0u;
   __syncthreads();
@@ -157,6 +182,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kDone + p.rank, step);
   }
   wait_all(ctl + kDone, world, step, p.status, 302);
+  if (stamper) stamps[3] = now_ns();
 
   // 4. fadd(W, sw, G, sg) -> W on this rank's replica
   const float* g = reinterpret_cast<const float*>(p.base[p.rank] + POLAR_B200_PEER_CONTROL_BYTES);
@@ -182,6 +208,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
 
   // the last CTA to finish closes the step
   __syncthreads();
+  if (stamper) stamps[4] = now_ns();
   if (threadIdx.x == 0) {
     if (atomicAdd(ctl + kTicketB, 1u) == gridDim.x - 1) {
       ctl[kTicketB] = 0;

@@ -111,6 +111,16 @@ class PeerGradients:
         if rc != 0:
             self.lib.check(rc)
 
+    def phase_times_us(self):
+        """Durations of the last launch's phases on this rank, from the control block's
+        timestamps (CTA 0): wait for all ranks' gradients, sum + distribute the slice, wait
+        for all slices, update."""
+        torch.cuda.synchronize(self.device)
+        ctl = torch.as_tensor(_DeviceSpan(self.own, CONTROL_BYTES // 4), device=self.device)
+        t = ctl[40:50].view(torch.int64).cpu().tolist()
+        return {"ready_wait": (t[1] - t[0]) / 1e3, "sum_slice": (t[2] - t[1]) / 1e3,
+                "done_wait": (t[3] - t[2]) / 1e3, "update": (t[4] - t[3]) / 1e3}
+
     def close(self):
         """Unmaps the peers' buffers and frees this rank's.  Every rank must have finished
         its last step (a barrier on the host) before any rank calls this."""
