@@ -8,7 +8,7 @@ int launch_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
                 const float* right, float* out, cudaStream_t stream);
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, int epilogue, cudaStream_t stream);
+              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch = 0);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k);
 int launch_tc_pair(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
                    float* out, float* ws, uint32_t splits, int epilogue, cudaStream_t stream);
@@ -19,6 +19,9 @@ int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
 uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k);
 int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                   const float* right, float* out, float* ws, cudaStream_t st, const float* sig);
+uint64_t ragged_rows_workspace_bytes(uint64_t rem, uint64_t n, uint64_t k);
+int launch_ragged_rows(const float* left_tail, uint64_t left_pitch, const float* right, float* out_tail,
+                       float* ws, uint64_t rem, uint64_t n, uint64_t k, cudaStream_t st);
 int tc_status_word();
 void tc_status_clear();
 
@@ -41,24 +44,37 @@ int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
 // stream-ordered pool.
 int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
            float* out, int bn, int bk, int passes, int write_hi, uint32_t splits, void* workspace,
-           uint64_t workspace_bytes, cudaStream_t stream, int epilogue = 0) {
+           uint64_t workspace_bytes, cudaStream_t stream, int epilogue = 0, uint64_t left_pitch = 0) {
   if (splits <= 1)
-    return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream);
+    return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream,
+                     left_pitch);
   const uint64_t need = (uint64_t)splits * m * n * sizeof(float);
   if (workspace) {
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
       return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
     return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(workspace),
-                     splits, epilogue, stream);
+                     splits, epilogue, stream, left_pitch);
   }
   void* ws = nullptr;
   cudaError_t e = cudaMallocAsync(&ws, need, stream);
   if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
   int rc = launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(ws), splits,
-                     epilogue, stream);
+                     epilogue, stream, left_pitch);
   e = cudaFreeAsync(ws, stream);
   if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
   return rc;
+}
+
+// A t_f product whose row count is a few rows past a multiple of the 128-row tile would
+// spend a whole tile row of tensor-core work on them (784 rows: 7 tile rows for 6.1 of
+// work).  Those rows go to the bandwidth-bound kernel instead, which reads `right` once
+// more - cheaper than a tile row whenever there is more than one tile row.  Returns the
+// number of such rows (0: not applicable).
+uint64_t ragged_rows(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* right, int fused) {
+  const uint64_t rem = m & 127;
+  if (!tl || tr || fused != 0 || m <= 128 || rem == 0 || rem > 16) return 0;
+  if ((n & 3) != 0 || !aligned16(right) || n * k < (1ull << 22)) return 0;
+  return rem;
 }
 
 int check_mm(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -84,8 +100,15 @@ uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t
   int kind = skinny_kind(tl, tr, m, n, k, al, al, al);
   if (kind) return skinny_workspace_bytes(kind, m, n, k);
   if (choose_path(tl, tr, m, n, k, al, al, al) == kPathTc) {
-    uint32_t s = tc_default_splits(m, n, k);
-    return s > 1 ? (uint64_t)s * m * n * sizeof(float) : 0;
+    const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, 0);
+    const uint64_t mm = m - rem;
+    uint32_t s = tc_default_splits(mm, n, k);
+    uint64_t need = s > 1 ? (uint64_t)s * mm * n * sizeof(float) : 0;
+    if (rem) {
+      const uint64_t r = ragged_rows_workspace_bytes(rem, n, k);
+      if (r > need) need = r;
+    }
+    return need;
   }
   return 0;
 }
@@ -122,9 +145,32 @@ static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, cons
                       : polar_b200_fsigmoid_grad(out, sig, out, m * n, stream);
   }
   switch (path) {
-    case kPathTc:
-      return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k), workspace,
-                    workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0);
+    case kPathTc: {
+      const uint64_t rem = ragged_rows(tl, tr, m, n, k, right, fused);
+      if (rem == 0)
+        return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k), workspace,
+                      workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0);
+      // whole tile rows on the tensor cores (left is stored [k, m]: the first m - rem columns
+      // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel
+      const uint64_t mm = m - rem;
+      rc = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k), workspace,
+                  workspace_bytes, as_stream(stream), 0, m);
+      if (rc) return rc;
+      const uint64_t need = ragged_rows_workspace_bytes(rem, n, k);
+      if (workspace) {
+        if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+          return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
+        return launch_ragged_rows(left + mm, m, right, out + mm * n, static_cast<float*>(workspace), rem, n, k,
+                                  as_stream(stream));
+      }
+      void* ws = nullptr;
+      cudaError_t e = cudaMallocAsync(&ws, need, as_stream(stream));
+      if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+      rc = launch_ragged_rows(left + mm, m, right, out + mm * n, static_cast<float*>(ws), rem, n, k, as_stream(stream));
+      e = cudaFreeAsync(ws, as_stream(stream));
+      if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+      return rc;
+    }
     case kPathSkinny: {
       const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
       const uint64_t need = skinny_workspace_bytes(kind, m, n, k);

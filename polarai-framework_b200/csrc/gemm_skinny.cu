@@ -275,6 +275,20 @@ reduce_splits_kernel(const float* __restrict__ partial, float* __restrict__ out,
   }
 }
 
+// The same sum, stored transposed: partial is [split][m][n], out is [n][m].  Used for the
+// last few rows of a product whose left operand is stored [k, rows]: they are computed as
+// the small-n product of the transposed problem and land as rows of the result.
+__global__ void __launch_bounds__(kThreads)
+reduce_splits_transposed_kernel(const float* __restrict__ partial, float* __restrict__ out, uint64_t m,
+                                uint64_t n, uint32_t splits) {
+  const uint64_t elems = m * n, stride = (uint64_t)gridDim.x * kThreads;
+  for (uint64_t e = (uint64_t)blockIdx.x * kThreads + threadIdx.x; e < elems; e += stride) {
+    float s = 0.f;
+    for (uint32_t sp = 0; sp < splits; ++sp) s += partial[(uint64_t)sp * elems + e];
+    out[(e % n) * m + e / n] = s;
+  }
+}
+
 // ---------------------------------------------------------------- small k
 
 constexpr int RK = 64;   // rows of the left operand staged per CTA
@@ -423,6 +437,37 @@ int launch_small_n_mn(const float* l, const float* r, float* out, float* ws, uin
 }
 
 }  // namespace skinny
+
+// out_tail[j, i] = sum_kk left_tail[kk*left_pitch + j] * right[kk*n + i]   (j < rem <= 16, i < n):
+// `rem` rows of a t_f product, as the small-n product right^T . left_tail stored transposed.
+// Scratch: ragged_rows_workspace_bytes.  n a multiple of 4, right 16-byte aligned.
+uint64_t ragged_rows_workspace_bytes(uint64_t rem, uint64_t n, uint64_t k) {
+  return (uint64_t)skinny::splits_for(n, k) * n * rem * sizeof(float);
+}
+
+int launch_ragged_rows(const float* left_tail, uint64_t left_pitch, const float* right, float* out_tail,
+                       float* ws, uint64_t rem, uint64_t n, uint64_t k, cudaStream_t st) {
+  using namespace skinny;
+  const uint32_t splits = splits_for(n, k);
+  uint64_t m_blocks = (n / 4 + kThreads - 1) / kThreads;
+  uint64_t k_per_split = (k + splits - 1) / splits;
+  k_per_split = (k_per_split + 3) & ~3ull;
+  dim3 grid((unsigned)m_blocks, splits);
+  const int np = round_np(rem);
+  switch (np) {
+#define POLAR_RAGGED(NP) \
+  case NP: small_n_mnmajor_kernel<NP><<<grid, kThreads, 0, st>>>(right, left_tail, ws, n, rem, k, left_pitch, 1, k_per_split); break;
+    POLAR_RAGGED(1) POLAR_RAGGED(2) POLAR_RAGGED(4) POLAR_RAGGED(8) POLAR_RAGGED(10) POLAR_RAGGED(16)
+#undef POLAR_RAGGED
+    default: return fail(POLAR_B200_ERR_UNSUPPORTED, "ragged rows: more than 16");
+  }
+  int rc = check_launch("fmatmul_ragged_rows");
+  if (rc) return rc;
+  uint64_t g = (n * rem + kThreads - 1) / kThreads;
+  uint64_t cap = (uint64_t)sm_count() * 4;
+  reduce_splits_transposed_kernel<<<(unsigned)(g < cap ? g : cap), kThreads, 0, st>>>(ws, out_tail, n, rem, splits);
+  return check_launch("fmatmul_ragged_rows_reduce");
+}
 
 // Which skinny kernel, if any, serves this shape: 1 = small n with K-major left,
 // 2 = small n with MN-major left (needs scratch), 3 = small k, 0 = none.

@@ -370,12 +370,14 @@ static EncodeTiledFn get_encode() {
 }
 
 // 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows.
+// `pitch` (floats between consecutive outer rows; 0 = inner) lets a map cover the first
+// `inner` columns of a wider stored matrix.
 int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer,
-                    uint32_t box_inner, uint32_t box_outer, bool mn_major, int bk) {
+                    uint32_t box_inner, uint32_t box_outer, bool mn_major, int bk, uint64_t pitch = 0) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return fail(POLAR_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {inner * 4};
+  cuuint64_t strides[1] = {(pitch ? pitch : inner) * 4};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
@@ -460,7 +462,7 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) 
 template <int BN, int BK>
 static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                       const float* right, float* out, int passes, int write_hi, float* ws, uint32_t splits,
-                      int epilogue, cudaStream_t stream) {
+                      int epilogue, cudaStream_t stream, uint64_t left_pitch) {
   using C = Cfg<BN, BK>;
   static_assert(C::kStages >= 2 && C::kSmemBytes <= 227 * 1024, "stage ring must fit shared memory");
   int dev = 0;
@@ -476,7 +478,8 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   if (rc) return rc;
   CUtensorMap map_a, map_b;
   // left: stored [m,k] (K-major: inner k, box {BK, 128}) or [k,m] (MN-major: inner m, box {32, BK})
-  rc = tl ? make_map(&map_a, left, m, k, 32, BK, true, BK) : make_map(&map_a, left, k, m, BK, BM, false, BK);
+  rc = tl ? make_map(&map_a, left, m, k, 32, BK, true, BK, left_pitch)
+          : make_map(&map_a, left, k, m, BK, BM, false, BK, left_pitch);
   if (rc) return rc;
   // right: stored [n,k] when transposed (K-major: inner k, box {BK, BN}) or [k,n] (MN-major)
   rc = tr ? make_map(&map_b, right, k, n, BK, BN, false, BK) : make_map(&map_b, right, n, k, 32, BK, true, BK);
@@ -510,14 +513,14 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
 
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, int epilogue, cudaStream_t stream) {
+              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch) {
   if (bn == 128 && bk == 32)
-    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
+    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
   if (bn == 128)
-    return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
+    return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
   if (bk == 32)
-    return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
-  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream);
+    return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
+  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
 }
 
 // Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.

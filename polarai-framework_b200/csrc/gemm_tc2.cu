@@ -36,7 +36,7 @@ namespace polar_b200 {
 namespace tc {
 
 int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
-             uint32_t box_outer, bool mn_major, int bk);
+             uint32_t box_outer, bool mn_major, int bk, uint64_t pitch = 0);
 int ensure_status();
 extern int* g_status_dev;
 int launch_add_splits(const float* ws, float* out, uint64_t m, uint64_t n, uint32_t splits, int epilogue,

@@ -107,6 +107,32 @@ def test_shapes_tma_cannot_describe(gpu, par_oracle, tl, tr, m, n, k):
     assert rel_err(gpu.fmatmul(tl, tr, l, r), ref, mag) <= TOL
 
 
+@pytest.mark.parametrize("m,n,k", [(784, 4096, 2048), (260, 1024, 4096), (1296, 2048, 2052), (144, 8192, 512)])
+def test_rows_past_a_tile_boundary_of_t_f_products(gpu, par_oracle, m, n, k):
+    # left stored [k, m] with m a few rows past a multiple of 128: whole tile rows on the tensor
+    # cores, the rest on the bandwidth-bound kernel; with the library's own scratch and with a
+    # caller workspace of exactly the size the library asks for
+    import torch
+    rng = np.random.default_rng(m + n + k)
+    l, r = operands(rng, 1, 0, m, n, k)
+    ref, mag = par_oracle.fmatmul_f64(1, 0, l, r)
+    got = gpu.fmatmul(1, 0, l, r)
+    assert rel_err(got, ref, mag) <= 5e-6
+    lib = gpu.d.lib
+    need = int(lib.cdll.polar_b200_fmatmul_workspace_bytes(1, 0, m, n, k))
+    assert need > 0
+    L, R = torch.from_numpy(l).cuda(), torch.from_numpy(r).cuda()
+    out = torch.full((m, n), float("nan"), device="cuda")
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    lib.call("polar_b200_fmatmul", 1, 0, m, n, k, L.data_ptr(), R.data_ptr(), out.data_ptr(), ws.data_ptr(), need, st)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), got.view(np.uint32))   # deterministic
+    assert lib.cdll.polar_b200_fmatmul(1, 0, m, n, k, L.data_ptr(), R.data_ptr(), out.data_ptr(), ws.data_ptr(),
+                                       need - 16, st) != 0                            # too small: a status
+    assert gpu.d.device_status() == 0
+
+
 def test_empty_dimensions(gpu):
     assert gpu.fmatmul(0, 0, np.empty((0, 8), np.float32), np.empty((8, 4), np.float32)).shape == (0, 4)
     out = gpu.fmatmul(0, 0, np.empty((3, 0), np.float32), np.empty((0, 4), np.float32))
