@@ -238,6 +238,16 @@ int polar_b200_fmatmul_path(int transLeft, int transRight, uint64_t m,
 int polar_b200_fsigmoid_grad(const float* gradient, const float* sigmoidOut,
                              float* out, uint64_t n, void* stream);
 
+/* fsigmoid_logloss_grad: dZ[i] for LogLoss applied to a Sigmoid output p with labels y:
+ *   ((p - y) / (p - p*p)) * ((1 - p) * p)
+ * One pass over the seven launches the reference's derivatives compile to - LogLoss':
+ * fadd(p,1,y,-1), fmul(p,p), fadd(p,1,pp,-1), fdivide
+ * (src/operation/internal/LogLossOperationInternal.cpp:127-170), then Sigmoid' as in
+ * fsigmoid_grad - keeping all seven roundings, so the result is bit-identical to the
+ * chain.  Args as a builtin: T predicted, T groundTruth, T out. */
+int polar_b200_fsigmoid_logloss_grad(const float* predicted, const float* groundTruth,
+                                     float* out, uint64_t n, void* stream);
+
 /* fmatmul with the builtin that follows it fused in, bit-identical to launching the
  * two builtins one after the other (the product is rounded to fp32 before the
  * second step either way):
@@ -286,7 +296,8 @@ typedef struct polar_b200_arg {
 /* Native names: the twelve of the benchmarked path, "frelu", "fsoftmax", "fpool",
  * "fconv2d" (the reference's own table names ReLU, Softmax and Transpose all
  * "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own here), and
- * the extended "fsigmoid_grad", "fmatmul_x_y_sigmoid", "fmatmul_x_y_sigmoid_grad".
+ * the extended "fsigmoid_grad", "fsigmoid_logloss_grad", "fmatmul_x_y_sigmoid",
+ * "fmatmul_x_y_sigmoid_grad".
  *
  * Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
  * on arguments in LaunchCommand order; this is what Device::launch forwards to

@@ -56,6 +56,12 @@ class OracleExecutor:
                 # the reference's derivative chain, launch by launch
                 one = o.ffill(1.0, g(1).size)
                 r = o.fmul(g(0).ravel(), o.fmul(o.fadd(one, 1.0, g(1).ravel(), -1.0), g(1).ravel()))
+            elif kernel == "fsigmoid_logloss_grad":
+                # LogLoss' then Sigmoid', launch by launch as the reference composes them
+                pr, y = g(0).ravel(), g(1).ravel()
+                one = o.ffill(1.0, pr.size)
+                dldp = o.fdivide(o.fadd(pr, 1.0, y, -1.0), o.fadd(pr, 1.0, o.fmul(pr, pr), -1.0))
+                r = o.fmul(dldp, o.fmul(o.fadd(one, 1.0, pr, -1.0), pr))
             elif kernel.startswith("fmatmul_"):
                 r = o.fmatmul(kernel[8] == "t", kernel[10] == "t", g(0), g(1))
                 if kernel.endswith("_sigmoid"):

@@ -42,6 +42,7 @@ SIGNATURES = {
     "polar_b200_fsigmoid_unclamped": (_i, [_p, _p, _u64, _p]),
     "polar_b200_flogloss": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fsigmoid_grad": (_i, [_p, _p, _p, _u64, _p]),
+    "polar_b200_fsigmoid_logloss_grad": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_fmulconcat": (_i, [_p, _p, _p, _u64, _p]),
     "polar_b200_frelu": (_i, [_p, _p, _u64, _p]),
     "polar_b200_fsoftmax": (_i, [_p, _p, _u64, _p, _u64, _p]),

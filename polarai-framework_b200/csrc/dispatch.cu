@@ -354,6 +354,12 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     return polar_b200_fsigmoid_grad(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data, numel(a[2].tensor),
                                     stream);
   }
+  if (!std::strcmp(name, "fsigmoid_logloss_grad")) {
+    if (!pattern("TTT") || !same(0, 2) || !same(1, 2))
+      return fail(bad_args, "fsigmoid_logloss_grad expects (T predicted, T groundTruth, T out) of equal size");
+    return polar_b200_fsigmoid_logloss_grad(a[0].tensor.data, a[1].tensor.data, a[2].tensor.data,
+                                            numel(a[2].tensor), stream);
+  }
   if (!std::strcmp(name, "fmulconcat")) {
     if (!pattern("TTT") || !same(1, 2) || numel(a[0].tensor) < 1)
       return fail(bad_args, "fmulconcat expects (T gradient, T localDerivative, T out)");

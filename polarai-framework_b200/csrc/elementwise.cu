@@ -67,6 +67,19 @@ struct SigmoidGradOp {
     return sigmoid_grad_chain(g, s);
   }
 };
+// Extended builtin: dZ = dL/dP * dP/dZ for LogLoss on a Sigmoid output, the seven launches
+// the reference's derivatives compile to (LogLossOperationInternal.cpp:127-170:
+// fadd(p,1,y,-1), fmul(p,p), fadd(p,1,pp,-1), fdivide; SigmoidOperationInternal.cpp:107-135:
+// fadd(ones,1,p,-1), fmul(.,p), fmul(dLdP,.)) in one pass with the same seven roundings.
+struct SigmoidLogLossGradOp {
+  __device__ __forceinline__ float operator()(float p, float y) const {
+    const float pmy = __fadd_rn(__fmul_rn(p, 1.0f), __fmul_rn(y, -1.0f));
+    const float pp = __fmul_rn(p, p);
+    const float den = __fadd_rn(__fmul_rn(p, 1.0f), __fmul_rn(pp, -1.0f));
+    const float dldp = __fdiv_rn(pmy, den);
+    return sigmoid_grad_chain(dldp, p);
+  }
+};
 struct ScaleByFirstOp {  // fmulconcat: the scalar is read once per thread
   float g;
   __device__ __forceinline__ float operator()(float l, float) const { return __fmul_rn(g, l); }
@@ -272,6 +285,11 @@ int polar_b200_flogloss(const float* predicted, const float* groundTruth, float*
 int polar_b200_fsigmoid_grad(const float* gradient, const float* sigmoidOut, float* out, uint64_t n,
                              void* stream) {
   return launch_ew<2>("fsigmoid_grad", SigmoidGradOp{}, gradient, sigmoidOut, out, n, stream);
+}
+
+int polar_b200_fsigmoid_logloss_grad(const float* predicted, const float* groundTruth, float* out, uint64_t n,
+                                     void* stream) {
+  return launch_ew<2>("fsigmoid_logloss_grad", SigmoidLogLossGradOp{}, predicted, groundTruth, out, n, stream);
 }
 
 int polar_b200_fmulconcat(const float* gradient, const float* localDerivative, float* out,

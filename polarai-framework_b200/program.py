@@ -143,6 +143,8 @@ def fuse_program(program):
     """Rewrites a program with the extended builtins, keeping every result bit-identical:
 
       fadd(ones,1,S,-1,t1); fmul(t1,S,t2); fmul(G,t2,out)   ->  fsigmoid_grad(G, S, out)
+      fadd(P,1,Y,-1,a); fmul(P,P,b); fadd(P,1,b,-1,c); fdivide(a,c,d); fsigmoid_grad(d,P,out)
+                                                             ->  fsigmoid_logloss_grad(P, Y, out)
       fmatmul_x_y(L,R,Z); fsigmoid(Z,H)                      ->  fmatmul_x_y_sigmoid(L, R, H)
       fmatmul_x_y(L,R,G); fsigmoid_grad(G,S,out)             ->  fmatmul_x_y_sigmoid_grad(L, R, S, out)
 
@@ -177,6 +179,19 @@ def fuse_program(program):
                 if (k2 == "fmul" and a2[0] == t1 and a2[1] == s_ and k3 == "fmul" and a3[1] == a2[2]
                         and dead_after(t1, {i, i + 1, i + 2}) and dead_after(a2[2], {i, i + 1, i + 2})):
                     ops[i:i + 3] = [("fsigmoid_grad", [a3[0], s_, a3[2]])]
+                    changed = True
+                    break
+            # LogLoss derivative followed by the Sigmoid derivative of the same tensor
+            if (k == "fadd" and i + 4 < len(ops) and a[1] == 1.0 and a[3] == -1.0):
+                pr, y, pmy = a[0], a[2], a[4]
+                (k1, a1), (k2, a2), (k3, a3), (k4, a4) = ops[i + 1:i + 5]
+                span = set(range(i, i + 5))
+                if (k1 == "fmul" and a1[0] == pr and a1[1] == pr
+                        and k2 == "fadd" and a2[:4] == [pr, 1.0, a1[2], -1.0]
+                        and k3 == "fdivide" and a3[0] == pmy and a3[1] == a2[4]
+                        and k4 == "fsigmoid_grad" and a4[0] == a3[2] and a4[1] == pr
+                        and all(dead_after(t, span) for t in (pmy, a1[2], a2[4], a3[2]))):
+                    ops[i:i + 5] = [("fsigmoid_logloss_grad", [pr, y, a4[2]])]
                     changed = True
                     break
             # matmul followed by the builtin that consumes its result
