@@ -301,71 +301,77 @@ small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, 
                uint64_t rsj, int vec_store, const float* __restrict__ sig) {
   __shared__ float as[RK][KP];
   const uint64_t j0 = ((uint64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
-  const uint64_t row0 = (uint64_t)blockIdx.y * RK;
-  const int rows = (int)((m - row0 < RK) ? (m - row0) : RK);
-  for (int e = threadIdx.x; e < RK * KP; e += kThreads) {
-    int kk = e % KP, r = e / KP;
-    float v = 0.f;
-    if (r < rows && (uint64_t)kk < k) v = left[(row0 + r) * lsi + (uint64_t)kk * lsk];
-    as[r][kk] = v;
-  }
+  // Each thread's four columns of the small operand stay in registers while the CTA walks
+  // over row blocks (gridDim.y CTAs share the rows of one column block).
   float b[4][KP];
 #pragma unroll
   for (int c = 0; c < 4; ++c)
 #pragma unroll
     for (int kk = 0; kk < KP; ++kk)
       b[c][kk] = (j0 + c < n && (uint64_t)kk < k) ? right[(uint64_t)kk * rsk + (j0 + c) * rsj] : 0.f;
-  __syncthreads();
-  if (j0 >= n) return;
   const bool vec = vec_store && j0 + 4 <= n;
-  // Rows in groups of four: the four loads of the sigmoid values are issued before any of
-  // the arithmetic, so each thread keeps four 128-bit loads in flight.
-  for (int rb = 0; rb < rows; rb += 4) {
-    float4 sv[4];
-    if (sig) {
+  const uint64_t row_blocks = (m + RK - 1) / RK;
+  for (uint64_t rblk = blockIdx.y; rblk < row_blocks; rblk += gridDim.y) {
+    const uint64_t row0 = rblk * RK;
+    const int rows = (int)((m - row0 < RK) ? (m - row0) : RK);
+    __syncthreads();   // the previous block's rows are no longer read
+    for (int e = threadIdx.x; e < RK * KP; e += kThreads) {
+      int kk = e % KP, r = e / KP;
+      float v = 0.f;
+      if (r < rows && (uint64_t)kk < k) v = left[(row0 + r) * lsi + (uint64_t)kk * lsk];
+      as[r][kk] = v;
+    }
+    __syncthreads();
+    if (j0 >= n) continue;
+    // Rows in groups of four: the four loads of the sigmoid values are issued before any of
+    // the arithmetic, so each thread keeps four 128-bit loads in flight.
+    for (int rb = 0; rb < rows; rb += 4) {
+      float4 sv[4];
+      if (sig) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (rb + u >= rows) continue;
+          const float* sp = sig + (row0 + rb + u) * n + j0;
+          if (vec) {
+            sv[u] = __ldcs(reinterpret_cast<const float4*>(sp));
+          } else {
+            sv[u].x = sp[0];
+            sv[u].y = (j0 + 1 < n) ? sp[1] : 0.f;
+            sv[u].z = (j0 + 2 < n) ? sp[2] : 0.f;
+            sv[u].w = (j0 + 3 < n) ? sp[3] : 0.f;
+          }
+        }
+      }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        if (rb + u >= rows) continue;
-        const float* sp = sig + (row0 + rb + u) * n + j0;
+        const int r = rb + u;
+        if (r >= rows) continue;
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KP; ++kk) {
+          float a = as[r][kk];
+          c0 = fmaf(a, b[0][kk], c0);
+          c1 = fmaf(a, b[1][kk], c1);
+          c2 = fmaf(a, b[2][kk], c2);
+          c3 = fmaf(a, b[3][kk], c3);
+        }
+        if (sig) {
+          // fused Sigmoid derivative: out = product * ((1 - s) * s), s = fsigmoid output
+          c0 = sigmoid_grad_chain(c0, sv[u].x); c1 = sigmoid_grad_chain(c1, sv[u].y);
+          c2 = sigmoid_grad_chain(c2, sv[u].z); c3 = sigmoid_grad_chain(c3, sv[u].w);
+        }
+        float* dst = out + (row0 + r) * n + j0;
         if (vec) {
-          sv[u] = __ldcs(reinterpret_cast<const float4*>(sp));
+          __stcs(reinterpret_cast<float4*>(dst), make_float4(c0, c1, c2, c3));
         } else {
-          sv[u].x = sp[0];
-          sv[u].y = (j0 + 1 < n) ? sp[1] : 0.f;
-          sv[u].z = (j0 + 2 < n) ? sp[2] : 0.f;
-          sv[u].w = (j0 + 3 < n) ? sp[3] : 0.f;
+          dst[0] = c0;
+          if (j0 + 1 < n) dst[1] = c1;
+          if (j0 + 2 < n) dst[2] = c2;
+          if (j0 + 3 < n) dst[3] = c3;
         }
       }
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int r = rb + u;
-      if (r >= rows) continue;
-      float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
-#pragma unroll
-      for (int kk = 0; kk < KP; ++kk) {
-        float a = as[r][kk];
-        c0 = fmaf(a, b[0][kk], c0);
-        c1 = fmaf(a, b[1][kk], c1);
-        c2 = fmaf(a, b[2][kk], c2);
-        c3 = fmaf(a, b[3][kk], c3);
-      }
-      if (sig) {
-        // fused Sigmoid derivative: out = product * ((1 - s) * s), s = fsigmoid output
-        c0 = sigmoid_grad_chain(c0, sv[u].x); c1 = sigmoid_grad_chain(c1, sv[u].y);
-        c2 = sigmoid_grad_chain(c2, sv[u].z); c3 = sigmoid_grad_chain(c3, sv[u].w);
-      }
-      float* dst = out + (row0 + r) * n + j0;
-      if (vec) {
-        __stcs(reinterpret_cast<float4*>(dst), make_float4(c0, c1, c2, c3));
-      } else {
-        dst[0] = c0;
-        if (j0 + 1 < n) dst[1] = c1;
-        if (j0 + 2 < n) dst[2] = c2;
-        if (j0 + 3 < n) dst[3] = c3;
-      }
-    }
-  }
+  }   // row blocks
 }
 
 // ---------------------------------------------------------------- host side
@@ -514,6 +520,9 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
   // small k
   const uint64_t lsi = tl ? 1 : k, lsk = tl ? m : 1;
   uint64_t gx = ((n + 3) / 4 + kThreads - 1) / kThreads, gy = (m + RK - 1) / RK;
+  // about three CTAs per SM in all; each walks over the row blocks gy apart
+  const uint64_t gy_cap = ((uint64_t)sm_count() * 3 + gx - 1) / gx;
+  if (gy > gy_cap) gy = gy_cap;
   if (gy > 65535) {
     return fail(POLAR_B200_ERR_UNSUPPORTED, "skinny matmul: more than 65535 row blocks");
   }
