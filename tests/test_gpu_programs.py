@@ -71,3 +71,51 @@ def test_mlp_step(env, batch, hidden):
     for g in ("dW1", "dW2", "W1", "W2"):
         want = cpu.output(g)
         assert np.max(np.abs(dev.output(g) - want)) / np.abs(want).max() <= 1e-4, g
+
+
+def test_full_batch_mlp_step_is_the_sum_of_its_halves():
+    # Config 4 at its full size (65536 rows on one GPU), checked through a property the CPU
+    # oracle is too slow to check directly: every row's loss is independent of the other rows,
+    # and the weight gradients (batch sums) of the whole batch equal the sum of the gradients
+    # of its two halves - the identity the data-parallel split relies on.
+    import torch
+    from polarai_framework_b200.program import DeviceExecutor, fuse_program, mlp_program
+    batch, hidden = 65536, 4096
+    g = torch.Generator(device="cuda").manual_seed(4)
+    X = torch.randn((batch, 784), device="cuda", generator=g)
+    Y = torch.nn.functional.one_hot(torch.randint(0, 10, (batch,), device="cuda", generator=g), 10).float()
+    a1, a2 = (6 / (784 + hidden)) ** 0.5, (6 / (hidden + 10)) ** 0.5
+    W1 = (torch.rand((784, hidden), device="cuda", generator=g) * 2 - 1) * a1
+    W2 = (torch.rand((hidden, 10), device="cuda", generator=g) * 2 - 1) * a2
+
+    def step(rows, fused):
+        prog = mlp_program(rows.stop - rows.start, 784, hidden, 10, 0.1)
+        ex = DeviceExecutor(fuse_program(prog) if fused else prog)
+        ex.set_inputs(X=X[rows], Y=Y[rows], W1=W1, W2=W2)
+        ex.run()
+        torch.cuda.synchronize()
+        out = {k: ex.t[k].clone() for k in ("L", "dW1", "dW2", "W1", "W2", "dZ1", "dZ2", "H")}
+        del ex
+        return out
+
+    whole = step(slice(0, batch), True)
+    lo, hi = step(slice(0, batch // 2), True), step(slice(batch // 2, batch), True)
+    assert torch.equal(torch.cat([lo["L"], hi["L"]]), whole["L"])
+    # Tolerance in the matmul tests' metric, |error| / sum_k |a||b|: the tensor-core accumulator
+    # rounds toward zero at every step, so a 65536-term sum carries about 4e-6 of it (measured
+    # against float64), far more than the 2e-8 of a round-to-nearest fp32 sum and still 20x inside 1e-4.
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for k, left, right in (("dW1", X, whole["dZ1"]), ("dW2", whole["H"], whole["dZ2"])):
+        both = lo[k] + hi[k]
+        mag = left.abs().t() @ right.abs()
+        assert float(((whole[k] - both).abs() / mag).max()) <= 2e-5, k
+        ref = (left[:, :8].double().t() @ right.double())          # eight full rows in float64
+        assert float(((whole[k][:8].double() - ref).abs() / mag[:8].double()).max()) <= 1e-5, k
+    # the extended builtins give the bits of the one-launch-per-builtin chain at this size too
+    chain = step(slice(0, batch), False)
+    for k in ("L", "dW1", "dW2", "W1", "W2"):
+        assert torch.equal(whole[k].view(torch.int32), chain[k].view(torch.int32)), k
+    # mean loss of an untrained 10-way sigmoid classifier with these initial weights
+    assert 0.6 < float(whole["L"].mean()) < 0.9
+    from polarai_framework_b200.capi import lib
+    assert lib().cdll.polar_b200_device_status() == 0
