@@ -474,6 +474,7 @@ def run_mlp(args):
                                          "all-reduce of dW2 and dW1, fadd updates"}
         del cex
     if rank == 0 and world == 1 and not args.no_extras:
+        line["e2e_plugin"] = plugin_e2e(program, Xs, Ys, W1, W2, per)
         line["cpu_baseline"] = cpu_mlp_baseline(2048, steps=1)[0]
         # the bandwidth numbers first: the GEMM loop leaves the GPU at its power cap
         ew = elementwise_numbers(torch, lib, 1 << 28, peaks, reps=10)
@@ -481,6 +482,38 @@ def run_mlp(args):
     if rank == 0:
         print(json.dumps(line), flush=True)
     shutdown(torch, dist, world, graph)
+
+
+def plugin_e2e(program, X, Y, W1, W2, rows, steps=5):
+    """The same step driven through the device-runtime plugin (libpolar_rt_cuda.so) the way
+    the reference's executor drives a runtime: X and Y written from pageable host arrays into
+    the records' host copies (ath_load's role), uploaded when the first launch locks them on
+    the device, one Device::launch per builtin, the loss tensor read back to the host.  Wall
+    clock around whole steps; everything in it is synchronous with the host."""
+    import numpy as np
+    from polarai_framework_b200.runtime import RuntimeProgramExecutor
+    ex = RuntimeProgramExecutor(program)
+    ex.set_inputs(W1=W1, W2=W2)
+    loss = np.empty(program.tensors["L"], np.float32)
+
+    def step():
+        ex.set_inputs(X=X, Y=Y)
+        ex.run()
+        ex.output("L", loss)
+        return float(loss.mean(dtype=np.float64))
+
+    step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        mean_loss = step()
+    dt = (time.perf_counter() - t0) / steps
+    ex.close()
+    ex.rt.close()
+    return {"value": rows / dt, "unit": "samples/s", "ms_per_step": dt * 1e3, "steps": steps,
+            "h2d_bytes_per_step": int(X.nbytes + Y.nbytes), "d2h_bytes_per_step": int(loss.nbytes),
+            "last_mean_loss": mean_loss,
+            "path": "numpy X,Y -> polar_b200_rt_write (host copy of the record) -> upload on first device lock -> "
+                    "Device::launch per builtin -> polar_b200_rt_read of the loss tensor"}
 
 
 def shutdown(torch, dist, world, graph):

@@ -353,6 +353,12 @@ int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t worl
                               const polar_b200_update_segment* segments, uint32_t n_segments,
                               float scale_w, float scale_g, void* stream);
 
+/* Scratch bytes the launch `nativeKernelName(args)` would take from the stream-ordered pool
+ * if polar_b200_launch_by_name were given no workspace (0 for every builtin but some
+ * fmatmul shapes).  Only shapes are read, not the data pointers. */
+uint64_t polar_b200_launch_workspace_bytes(const char* nativeKernelName,
+                                           const polar_b200_arg* args, uint64_t argsCount);
+
 /* Number of kernels this library has launched since it was loaded (all
  * threads), for launch accounting in benchmarks. */
 uint64_t polar_b200_launch_count(void);

@@ -95,12 +95,15 @@ using namespace polar_b200;
 
 extern "C" {
 
-uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
-  const float* al = reinterpret_cast<const float*>(256);
+// Scratch a matmul launch needs; `fused` as in fmatmul_impl below (only the sigmoid epilogue
+// of the tensor-core kernel changes the answer: it keeps rows past a tile boundary on the
+// tensor cores).
+static uint64_t workspace_need(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, int fused) {
+  const float* al = reinterpret_cast<const float*>(256);   // allocator buffers are 256-byte aligned
   int kind = skinny_kind(tl, tr, m, n, k, al, al, al);
   if (kind) return skinny_workspace_bytes(kind, m, n, k);
   if (choose_path(tl, tr, m, n, k, al, al, al) == kPathTc) {
-    const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, 0);
+    const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, fused == 1 ? 1 : 0);
     const uint64_t mm = m - rem;
     uint32_t s = tc_default_splits(mm, n, k);
     uint64_t need = s > 1 ? (uint64_t)s * mm * n * sizeof(float) : 0;
@@ -111,6 +114,22 @@ uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t
     return need;
   }
   return 0;
+}
+
+uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {
+  return workspace_need(tl, tr, m, n, k, 0);
+}
+
+uint64_t polar_b200_launch_workspace_bytes(const char* name, const polar_b200_arg* a, uint64_t argc) {
+  if (!name || !a || std::strncmp(name, "fmatmul_", 8) || std::strlen(name) < 11 || argc < 3) return 0;
+  const char* suffix = name + 11;
+  const int fused = !*suffix ? 0 : !std::strcmp(suffix, "_sigmoid") ? 1 : !std::strcmp(suffix, "_sigmoid_grad") ? 2 : -1;
+  if (fused < 0 || !a[0].is_tensor || !a[1].is_tensor || a[0].tensor.dims != 2 || a[1].tensor.dims != 2) return 0;
+  const int tl = name[8] == 't', tr = name[10] == 't';
+  const polar_b200_tensor &l = a[0].tensor, &r = a[1].tensor;
+  const uint64_t m = tl ? l.shape[1] : l.shape[0], k = tl ? l.shape[0] : l.shape[1];
+  const uint64_t n = tr ? r.shape[0] : r.shape[1];
+  return workspace_need(tl, tr, m, n, k, fused);
 }
 
 int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) {

@@ -198,6 +198,7 @@ B200Device::B200Device(int ordinal) : mOrdinal(ordinal) {
 B200Device::~B200Device() {
   cudaSetDevice(mOrdinal);
   if (mStream) cudaStreamSynchronize(mStream);
+  if (mWorkspace) cudaFree(mWorkspace);
   mAllocator.reset();
   for (cudaEvent_t e : mEventPool) cudaEventDestroy(e);
   if (mStream) cudaStreamDestroy(mStream);
@@ -322,7 +323,24 @@ auto B200Device::launch(BackendAllocator& allocator, LaunchCommand& cmd, Event* 
     }
   }
   if (status == POLAR_B200_OK) {
-    status = polar_b200_launch_by_name(name, args, cmd.argsCount, nullptr, 0, mStream);
+    // Scratch for split-k matmuls is kept for the life of the device and only ever grows:
+    // taking it from the stream-ordered pool per launch costs a physical allocation each
+    // time the pool has been trimmed at a synchronisation point.
+    const uint64_t need = polar_b200_launch_workspace_bytes(name, args, cmd.argsCount);
+    if (need > mWorkspaceBytes) {
+      if (mWorkspace) cudaFreeAsync(mWorkspace, mStream);
+      mWorkspace = nullptr;
+      mWorkspaceBytes = 0;
+      void* p = nullptr;
+      if (cudaMallocAsync(&p, need, mStream) == cudaSuccess) {
+        mWorkspace = p;
+        mWorkspaceBytes = need;
+      } else {
+        cudaGetLastError();   // the library then falls back to its own per-launch allocation
+      }
+    }
+    status = polar_b200_launch_by_name(name, args, cmd.argsCount, need <= mWorkspaceBytes ? mWorkspace : nullptr,
+                                       need <= mWorkspaceBytes ? mWorkspaceBytes : 0, mStream);
     if (status != POLAR_B200_OK) mLastError = polar_b200_last_error();
   }
   if (status != POLAR_B200_OK) {

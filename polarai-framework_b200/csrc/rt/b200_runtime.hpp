@@ -129,6 +129,8 @@ public:
 private:
   int mOrdinal;
   cudaStream_t mStream = nullptr;
+  void* mWorkspace = nullptr;        // scratch for split-k matmuls, grown on demand
+  uint64_t mWorkspaceBytes = 0;
   std::string mName;
   std::shared_ptr<B200Allocator> mAllocator;
   mutable int mLastStatus = 0;

@@ -9,8 +9,11 @@
 #include <polar_b200.h>
 #include <polar_b200_rt.h>
 
+#include <algorithm>
 #include <cstring>
 #include <string>
+#include <thread>
+#include <vector>
 
 using namespace polarai::backend::generic;
 using polarai::core::internal::LockType;
@@ -24,6 +27,29 @@ struct polar_b200_rt {
 };
 
 namespace {
+// A batch of inputs is hundreds of megabytes; one thread copies about 10 GB/s, well below what
+// the upload over PCIe that follows can take.  Large copies are cut over a few threads.
+void big_memcpy(void* dst, const void* src, uint64_t bytes) {
+  constexpr uint64_t kChunk = 8ull << 20;
+  unsigned hw = std::thread::hardware_concurrency();
+  uint64_t parts = std::min<uint64_t>({bytes / kChunk, hw ? hw : 1u, 8u});
+  if (parts <= 1) {
+    std::memcpy(dst, src, bytes);
+    return;
+  }
+  const uint64_t per = ((bytes / parts) + 63) & ~63ull;
+  std::vector<std::thread> workers;
+  for (uint64_t i = 1; i < parts; ++i) {
+    const uint64_t lo = i * per, hi = std::min(bytes, lo + per);
+    if (lo >= hi) break;
+    workers.emplace_back([=] {
+      std::memcpy(static_cast<char*>(dst) + lo, static_cast<const char*>(src) + lo, hi - lo);
+    });
+  }
+  std::memcpy(dst, src, std::min(bytes, per));
+  for (auto& w : workers) w.join();
+}
+
 B200Device* dev(polar_b200_rt* rt, int i) {
   if (!rt || i < 0 || i >= (int)rt->devices.size()) return nullptr;
   return static_cast<B200Device*>(rt->devices[i].get());
@@ -94,7 +120,7 @@ int polar_b200_rt_write(polar_b200_rt* rt, uint64_t va, uint64_t bytes, const vo
     rt->allocator->release(rec);
     return fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
   }
-  std::memcpy(host, src, bytes);
+  big_memcpy(host, src, bytes);
   rt->allocator->release(rec);
   return POLAR_B200_OK;
 }
@@ -109,7 +135,7 @@ int polar_b200_rt_read(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void* dst
     rt->allocator->release(rec);
     return fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
   }
-  std::memcpy(dst, host, bytes);
+  big_memcpy(dst, host, bytes);
   rt->allocator->release(rec);
   for (auto& d : rt->devices) {
     auto* bd = static_cast<B200Device*>(d.get());

@@ -317,16 +317,9 @@ class DeviceExecutor:
             self._keep.append(arr)
             self._compiled.append((kernel.encode(), arr, len(args)))
         self._fn = fn
-        # one scratch buffer, sized for the most demanding fmatmul of the program
-        need = 0
-        wsb = self.lib.cdll.polar_b200_fmatmul_workspace_bytes
-        for kernel, args in program.ops:
-            if kernel.startswith("fmatmul_"):
-                tl, tr = kernel[8] == "t", kernel[10] == "t"
-                ls, rs = program.tensors[args[0]], program.tensors[args[1]]
-                m, k = (ls[1], ls[0]) if tl else (ls[0], ls[1])
-                n = rs[0] if tr else rs[1]
-                need = max(need, int(wsb(int(tl), int(tr), m, n, k)))
+        # one scratch buffer, sized for the most demanding launch of the program
+        wsb = self.lib.cdll.polar_b200_launch_workspace_bytes
+        need = max([0] + [int(wsb(k, arr, n)) for k, arr, n in self._compiled if isinstance(k, bytes)])
         self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
         self._ws_ptr, self._ws_bytes = self.workspace.data_ptr(), need
         self.fill_constants()

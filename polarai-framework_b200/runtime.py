@@ -226,3 +226,37 @@ class RuntimeBuiltins:
         n = right.shape[0] if tr else right.shape[1]
         name = f"fmatmul_{'t' if tl else 'f'}_{'t' if tr else 'f'}"
         return self._run(name, [left, right], (m, n))
+
+
+class RuntimeProgramExecutor:
+    """Runs a builtin Program (program.py) through the device-runtime plugin, the way a PolarAI
+    executor drives a runtime: one record per tensor, inputs written from host buffers
+    (ath_load's role: host copy, uploaded when a launch first locks the record on the
+    device), one Device::launch per builtin by native name, outputs read back to the host.
+    Single device; ALLREDUCE steps of a program are no-ops here."""
+
+    def __init__(self, program, rt=None, device=0):
+        self.program = program
+        self.rt = rt or Runtime()
+        self.device = device
+        self.t = {name: self.rt.tensor(shape, device) for name, shape in program.tensors.items()}
+        for name, value in program.constants.items():
+            self.rt.launch("ffill", [float(value), self.t[name]], device)
+
+    def set_inputs(self, **arrays):
+        for name, a in arrays.items():
+            self.rt.write(self.t[name], a)
+
+    def run(self):
+        for kernel, args in self.program.ops:
+            if kernel == "ALLREDUCE":
+                continue
+            self.rt.launch(kernel, [self.t[a] if isinstance(a, str) else a for a in args], self.device)
+
+    def output(self, name, out=None):
+        return self.rt.read(self.t[name], out)
+
+    def close(self):
+        for t in self.t.values():
+            self.rt.free(t)
+        self.t = {}

@@ -123,3 +123,26 @@ def test_memory_limit_offloads_released_records(rtb):
     rt.set_memory_limit(0)
     for t in ts:
         rt.free(t)
+
+
+def test_mlp_program_through_the_plugin_equals_the_direct_executor(rtb):
+    # the same builtin program (extended builtins included) driven through Device::launch with
+    # host buffers on both sides gives the bits of the direct C-ABI path
+    from polarai_framework_b200.program import DeviceExecutor, fuse_program, mlp_program
+    from polarai_framework_b200.runtime import RuntimeProgramExecutor
+    rng = np.random.default_rng(3)
+    batch, hidden = 512, 1024
+    X = rng.standard_normal((batch, 784)).astype(np.float32)
+    Y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, batch)]
+    W1 = rng.uniform(-0.05, 0.05, (784, hidden)).astype(np.float32)
+    W2 = rng.uniform(-0.2, 0.2, (hidden, 10)).astype(np.float32)
+    for prog in (mlp_program(batch, 784, hidden, 10, 0.1), fuse_program(mlp_program(batch, 784, hidden, 10, 0.1))):
+        direct = DeviceExecutor(prog)
+        direct.set_inputs(X=X, Y=Y, W1=W1, W2=W2)
+        plugin = RuntimeProgramExecutor(prog, rtb.rt)
+        plugin.set_inputs(X=X, Y=Y, W1=W1, W2=W2)
+        for _ in range(2):
+            direct.run(), plugin.run()
+        for k in prog.outputs:
+            assert np.array_equal(bits(direct.output(k)), bits(plugin.output(k))), k
+        plugin.close()
