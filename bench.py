@@ -478,7 +478,8 @@ def run_mlp(args):
         line["cpu_baseline"] = cpu_mlp_baseline(2048, steps=1)[0]
         # the bandwidth numbers first: the GEMM loop leaves the GPU at its power cap
         ew = elementwise_numbers(torch, lib, 1 << 28, peaks, reps=10)
-        line["extras"] = {"elementwise_2pow28": ew, "gemm_8192": gemm_numbers(torch, lib, 8192, reps=3)}
+        line["extras"] = {"elementwise_2pow28": ew, "gemm_8192": gemm_numbers(torch, lib, 8192, reps=3),
+                          "latency_bound_programs": small_program_latencies(torch)}
     if rank == 0:
         print(json.dumps(line), flush=True)
     shutdown(torch, dist, world, graph)
@@ -593,6 +594,41 @@ def elementwise_numbers(torch, lib, n, peaks, reps):
         ms = event_time(torch, fn, reps)
         gbs = bpe * n / ms / 1e6
         out[name] = {"ms": ms, "gbs": gbs, "frac_of_measured_copy": gbs / peaks["hbm_gbs"], "frac_of_8tbs": gbs / 8000.0}
+    return out
+
+
+def small_program_latencies(torch, reps=200):
+    """The two latency-bound configurations: microseconds per evaluation of the four-builtin
+    elementwise chain on 2^20 elements and of the logistic-regression step on 256 x 784, launched
+    builtin by builtin and replayed as a CUDA graph; inputs resident (both fit in L2)."""
+    import numpy as np
+    from polarai_framework_b200.program import DeviceExecutor, elementwise_chain_program, fuse_program, logreg_program
+    rng = np.random.default_rng(0)
+    n = 1 << 20
+    chain_in = {k: rng.uniform(-1, 1, n).astype(np.float32) for k in "abc"}
+    chain_in["d"] = rng.uniform(0.5, 2, n).astype(np.float32)
+    lr_in = {"X": rng.standard_normal((256, 784)).astype(np.float32),
+             "W": (0.01 * rng.standard_normal((784, 1))).astype(np.float32),
+             "Y": (rng.random((256, 1)) < 0.5).astype(np.float32)}
+    out = {}
+    for name, prog, inputs in (("elementwise_chain_2pow20", elementwise_chain_program(n), chain_in),
+                               ("logreg_step_256x784", logreg_program(256, 784, 0.1), lr_in),
+                               ("logreg_step_256x784_extended", fuse_program(logreg_program(256, 784, 0.1)), lr_in)):
+        ex = DeviceExecutor(prog)
+        ex.set_inputs(**inputs)
+        eager_us = event_time(torch, ex.run, reps, warmup=10) * 1e3
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ex.run()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ex.run()
+        torch.cuda.synchronize()
+        graph_us = event_time(torch, g.replay, reps, warmup=10) * 1e3
+        out[name] = {"launches": prog.launches(), "us_per_eval": eager_us, "us_per_eval_cuda_graph": graph_us}
+        del g, ex
     return out
 
 
