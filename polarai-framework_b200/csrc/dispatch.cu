@@ -68,12 +68,13 @@ int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left
 // A t_f product whose row count is a few rows past a multiple of the 128-row tile would
 // spend a whole tile row of tensor-core work on them (784 rows: 7 tile rows for 6.1 of
 // work).  Those rows go to the bandwidth-bound kernel instead, which reads `right` once
-// more - cheaper than a tile row whenever there is more than one tile row.  Returns the
-// number of such rows (0: not applicable).
+// more.  That pays only for long sums: at k = 65536 the tile row costs 0.33 ms and the extra
+// pass 0.2-0.3 ms, at k = 8192 the extra pass (80 us, launch- and ramp-dominated) costs more
+// than the tile row (43 us).  Returns the number of such rows (0: not applicable).
 uint64_t ragged_rows(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* right, int fused) {
   const uint64_t rem = m & 127;
   if (!tl || tr || fused != 0 || m <= 128 || rem == 0 || rem > 16) return 0;
-  if ((n & 3) != 0 || !aligned16(right) || n * k < (1ull << 22)) return 0;
+  if ((n & 3) != 0 || !aligned16(right) || k < 49152) return 0;
   return rem;
 }
 

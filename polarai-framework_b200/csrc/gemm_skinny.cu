@@ -310,10 +310,13 @@ small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, 
     for (int kk = 0; kk < KP; ++kk)
       b[c][kk] = (j0 + c < n && (uint64_t)kk < k) ? right[(uint64_t)kk * rsk + (j0 + c) * rsj] : 0.f;
   const bool vec = vec_store && j0 + 4 <= n;
-  const uint64_t row_blocks = (m + RK - 1) / RK;
-  for (uint64_t rblk = blockIdx.y; rblk < row_blocks; rblk += gridDim.y) {
-    const uint64_t row0 = rblk * RK;
-    const int rows = (int)((m - row0 < RK) ? (m - row0) : RK);
+  // The gridDim.y CTAs of a column block split the rows evenly (contiguous ranges, a multiple
+  // of four rows each) and stage them RK at a time.
+  const uint64_t rows_per_cta = ((m + gridDim.y - 1) / gridDim.y + 3) & ~3ull;
+  const uint64_t row_begin = (uint64_t)blockIdx.y * rows_per_cta;
+  const uint64_t row_end = row_begin + rows_per_cta < m ? row_begin + rows_per_cta : m;
+  for (uint64_t row0 = row_begin; row0 < row_end; row0 += RK) {
+    const int rows = (int)((row_end - row0 < RK) ? (row_end - row0) : RK);
     __syncthreads();   // the previous block's rows are no longer read
     for (int e = threadIdx.x; e < RK * KP; e += kThreads) {
       int kk = e % KP, r = e / KP;
@@ -371,7 +374,7 @@ small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, 
         }
       }
     }
-  }   // row blocks
+  }   // row ranges
 }
 
 // ---------------------------------------------------------------- host side
@@ -520,7 +523,7 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
   // small k
   const uint64_t lsi = tl ? 1 : k, lsk = tl ? m : 1;
   uint64_t gx = ((n + 3) / 4 + kThreads - 1) / kThreads, gy = (m + RK - 1) / RK;
-  // about three CTAs per SM in all; each walks over the row blocks gy apart
+  // about three CTAs per SM in all; each takes an equal share of the rows
   const uint64_t gy_cap = ((uint64_t)sm_count() * 3 + gx - 1) / gx;
   if (gy > gy_cap) gy = gy_cap;
   if (gy > 65535) {
