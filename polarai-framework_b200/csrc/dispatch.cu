@@ -18,7 +18,7 @@ int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
                 const float* right, const float* out);
 uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k);
 int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                  const float* right, float* out, float* ws, cudaStream_t st, const float* sig);
+                  const float* right, float* out, float* ws, cudaStream_t st, const float* sig, int sigmoid_out = 0);
 uint64_t ragged_rows_workspace_bytes(uint64_t rem, uint64_t n, uint64_t k);
 int launch_ragged_rows(const float* left_tail, uint64_t left_pitch, const float* right, float* out_tail,
                        float* ws, uint64_t rem, uint64_t n, uint64_t k, cudaStream_t st);
@@ -157,7 +157,7 @@ static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, cons
   }
   const int path = choose_path(tl, tr, m, n, k, left, right, out);
   const int kind0 = path == kPathSkinny ? skinny_kind(tl, tr, m, n, k, left, right, out) : 0;
-  const bool fused_in_kernel = (fused == 1 && path == kPathTc) || (fused == 2 && kind0 == 3);
+  const bool fused_in_kernel = (fused == 1 && (path == kPathTc || kind0 == 1)) || (fused == 2 && kind0 == 3);
   if (fused != 0 && !fused_in_kernel) {
     rc = fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 0, nullptr);
     if (rc) return rc;
@@ -196,7 +196,7 @@ static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, cons
       const uint64_t need = skinny_workspace_bytes(kind, m, n, k);
       if (need == 0)
         return launch_skinny(kind, tl, tr, m, n, k, left, right, out, nullptr, as_stream(stream),
-                             fused == 2 ? sig : nullptr);
+                             fused == 2 ? sig : nullptr, fused == 1 ? 1 : 0);
       if (workspace) {
         if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
           return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");

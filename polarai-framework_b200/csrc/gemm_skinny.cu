@@ -34,11 +34,31 @@ constexpr int KT = 1024;          // k-slab staged in shared memory
 constexpr int KT_PAD = KT + 4;    // keeps float4 alignment, staggers banks between columns
 constexpr int ROWS_PER_WARP = 4;
 
+// After the xor-shuffle reduction every lane holds all ROWS_PER_WARP x NP sums.  The warp's
+// rows are contiguous in `out` (n values each), so lane l stores flat elements l, l + 32, ...:
+// coalesced stores, and a fused sigmoid costs each lane one or two evaluations, not forty.
+template <int NP>
+__device__ __forceinline__ void store_row_sums(const float (&acc)[ROWS_PER_WARP][NP], float* __restrict__ out,
+                                               uint64_t row0, uint64_t m, uint64_t n, int lane, int act) {
+  if (row0 >= m) return;
+  const uint32_t rows = (uint32_t)((m - row0 < ROWS_PER_WARP) ? (m - row0) : ROWS_PER_WARP);
+  const uint32_t total = rows * (uint32_t)n;
+  for (uint32_t f = lane; f < total; f += 32) {
+    float v = 0.f;
+#pragma unroll
+    for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+      for (int j = 0; j < NP; ++j)
+        if ((uint32_t)j < (uint32_t)n && (uint32_t)r * (uint32_t)n + (uint32_t)j == f) v = acc[r][j];
+    out[row0 * n + f] = act ? sigmoid_clamped(v) : v;
+  }
+}
+
 template <int NP>
 __global__ void __launch_bounds__(kThreads)
 small_n_kmajor_kernel(const float* __restrict__ left, const float* __restrict__ right,
                       float* __restrict__ out, uint64_t m, uint64_t n, uint64_t k, uint64_t rsk,
-                      uint64_t rsj) {
+                      uint64_t rsj, int act) {
   extern __shared__ float bs[];   // [NP][KT_PAD], k contiguous
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t rows_per_cta = (kThreads / 32) * ROWS_PER_WARP;
@@ -90,16 +110,7 @@ small_n_kmajor_kernel(const float* __restrict__ left, const float* __restrict__ 
       acc[r][j] = v;
     }
   }
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < ROWS_PER_WARP; ++r) {
-      uint64_t row = row0 + r;
-      if (row < m)
-#pragma unroll
-        for (int j = 0; j < NP; ++j)
-          if ((uint64_t)j < n) out[row * n + j] = acc[r][j];
-    }
-  }
+  store_row_sums<NP>(acc, out, row0, m, n, lane, act);
 }
 
 // ---------------------------------------------------------------- small n, K-major left, R resident
@@ -115,7 +126,7 @@ template <int NP>
 __global__ void __launch_bounds__(kResidentThreads, 1)
 small_n_kmajor_resident_kernel(const float* __restrict__ left, const float* __restrict__ right,
                                float* __restrict__ out, uint64_t m, uint64_t n, uint64_t k, uint64_t rsk,
-                               uint64_t rsj) {
+                               uint64_t rsj, int act) {
   extern __shared__ float bs[];   // [NP][k + 4], k contiguous
   const uint32_t kpad = (uint32_t)k + 4;
   for (uint64_t e = threadIdx.x; e < (uint64_t)NP * k; e += kResidentThreads) {
@@ -180,14 +191,7 @@ small_n_kmajor_resident_kernel(const float* __restrict__ left, const float* __re
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         acc[r][j] = v;
       }
-    if (lane == 0) {
-#pragma unroll
-      for (int r = 0; r < ROWS_PER_WARP; ++r)
-        if (row0 + r < m)
-#pragma unroll
-          for (int j = 0; j < NP; ++j)
-            if ((uint64_t)j < n) out[(row0 + r) * n + j] = acc[r][j];
-    }
+    store_row_sums<NP>(acc, out, row0, m, n, lane, act);
   }
 }
 
@@ -263,16 +267,30 @@ small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__
   }
 }
 
+// Sum of one element over the splits, ascending split index (a fixed order); the loads of
+// eight splits are issued together, the additions stay in order.
+__device__ __forceinline__ float sum_splits(const float* __restrict__ partial, uint64_t elems, uint64_t e,
+                                            uint32_t splits) {
+  float s = 0.f;
+  uint32_t sp = 0;
+  for (; sp + 8 <= splits; sp += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(partial + (uint64_t)(sp + u) * elems + e);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s += v[u];
+  }
+  for (; sp < splits; ++sp) s += __ldcg(partial + (uint64_t)sp * elems + e);
+  return s;
+}
+
 // out[e] = sum over splits, ascending split index: a fixed order.
 __global__ void __launch_bounds__(kThreads)
 reduce_splits_kernel(const float* __restrict__ partial, float* __restrict__ out, uint64_t elems,
                      uint32_t splits) {
   const uint64_t stride = (uint64_t)gridDim.x * kThreads;
-  for (uint64_t e = (uint64_t)blockIdx.x * kThreads + threadIdx.x; e < elems; e += stride) {
-    float s = 0.f;
-    for (uint32_t sp = 0; sp < splits; ++sp) s += partial[(uint64_t)sp * elems + e];
-    out[e] = s;
-  }
+  for (uint64_t e = (uint64_t)blockIdx.x * kThreads + threadIdx.x; e < elems; e += stride)
+    out[e] = sum_splits(partial, elems, e, splits);
 }
 
 // The same sum, stored transposed: partial is [split][m][n], out is [n][m].  Used for the
@@ -283,9 +301,7 @@ reduce_splits_transposed_kernel(const float* __restrict__ partial, float* __rest
                                 uint64_t n, uint32_t splits) {
   const uint64_t elems = m * n, stride = (uint64_t)gridDim.x * kThreads;
   for (uint64_t e = (uint64_t)blockIdx.x * kThreads + threadIdx.x; e < elems; e += stride) {
-    float s = 0.f;
-    for (uint32_t sp = 0; sp < splits; ++sp) s += partial[(uint64_t)sp * elems + e];
-    out[(e % n) * m + e / n] = s;
+    out[(e % n) * m + e / n] = sum_splits(partial, elems, e, splits);
   }
 }
 
@@ -393,7 +409,7 @@ uint32_t splits_for(uint64_t m, uint64_t k) {
 
 template <int NP>
 int launch_small_n_k(const float* l, const float* r, float* out, uint64_t m, uint64_t n, uint64_t k,
-                     uint64_t rsk, uint64_t rsj, cudaStream_t st) {
+                     uint64_t rsk, uint64_t rsj, cudaStream_t st, int act) {
   // whole small operand resident in shared memory when it fits (and there are rows
   // enough to keep every SM busy); otherwise k slabs
   const size_t resident = (size_t)NP * (k + 4) * sizeof(float);
@@ -408,7 +424,7 @@ int launch_small_n_k(const float* l, const float* r, float* out, uint64_t m, uin
       res_attr[d] = true;
     }
     small_n_kmajor_resident_kernel<NP><<<(unsigned)sm_count(), kResidentThreads, resident, st>>>(
-        l, r, out, m, n, k, rsk, rsj);
+        l, r, out, m, n, k, rsk, rsj, act);
     return check_launch("fmatmul_small_n_resident");
   }
   const size_t smem = (size_t)NP * KT_PAD * sizeof(float);
@@ -423,7 +439,7 @@ int launch_small_n_k(const float* l, const float* r, float* out, uint64_t m, uin
   uint64_t rows_per_cta = (kThreads / 32) * ROWS_PER_WARP;
   uint64_t grid = (m + rows_per_cta - 1) / rows_per_cta;
   if (grid > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many rows");
-  small_n_kmajor_kernel<NP><<<(unsigned)grid, kThreads, smem, st>>>(l, r, out, m, n, k, rsk, rsj);
+  small_n_kmajor_kernel<NP><<<(unsigned)grid, kThreads, smem, st>>>(l, r, out, m, n, k, rsk, rsj, act);
   return check_launch("fmatmul_small_n");
 }
 
@@ -498,8 +514,10 @@ uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k) {
   return s > 1 ? (uint64_t)s * m * n * sizeof(float) : 0;
 }
 
+// `sig` (small k only): fuse the Sigmoid derivative with this sigmoid output;
+// `sigmoid_out` (small n, K-major left only): store fsigmoid of the product.
 int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                  const float* right, float* out, float* ws, cudaStream_t st, const float* sig) {
+                  const float* right, float* out, float* ws, cudaStream_t st, const float* sig, int sigmoid_out) {
   using namespace skinny;
   const uint64_t rsk = tr ? 1 : n, rsj = tr ? k : 1;
   if (kind == 1 || kind == 2) {
@@ -507,7 +525,7 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
     const uint32_t splits = kind == 2 ? splits_for(m, k) : 1;
 #define POLAR_SKINNY_N(NP)                                                                   \
   case NP:                                                                                   \
-    return kind == 1 ? launch_small_n_k<NP>(left, right, out, m, n, k, rsk, rsj, st)          \
+    return kind == 1 ? launch_small_n_k<NP>(left, right, out, m, n, k, rsk, rsj, st, sigmoid_out) \
                      : launch_small_n_mn<NP>(left, right, out, ws, splits, m, n, k, rsk, rsj, st);
     switch (np) {
       POLAR_SKINNY_N(1)
@@ -606,7 +624,7 @@ int polar_b200_fmatmul_tn_small_n_static(int transRight, uint64_t m, uint64_t n,
   if (!scratch) return rc;
   // Every partial sum the reduction reads is written by the first kernel of this
   // call, so nothing in the scratch has to be cleared beforehand.
-  return launch_skinny(2, 1, transRight, m, n, k, left, right, out, scratch, as_stream(stream), nullptr);
+  return launch_skinny(2, 1, transRight, m, n, k, left, right, out, scratch, as_stream(stream), nullptr, 0);
 }
 
 }  // extern "C"

@@ -66,7 +66,9 @@ def test_fsigmoid_logloss_grad_equals_the_seven_launch_chain(env, n):
 SHAPES = [
     (0, 0, 512, 512, 256),      # tensor cores, one work unit per tile: sigmoid in the epilogue
     (0, 0, 1024, 1024, 2048),   # tensor cores, k cut into work units: sigmoid in the summing kernel
-    (0, 0, 300, 10, 512),       # small n: no fused form, second builtin in place
+    (0, 0, 300, 10, 512),       # small n, k slabs: sigmoid applied where the row sums are stored
+    (0, 0, 4100, 10, 4096),     # small n, small operand resident in shared memory: same
+    (1, 0, 1028, 5, 1000),      # small n, split k: no fused form, second builtin in place
     (0, 1, 1000, 512, 10),      # small k: sigmoid_grad fused
     (1, 1, 200, 301, 7),        # small k, ragged n (scalar stores)
     (1, 0, 33, 17, 50),         # FFMA fallback
