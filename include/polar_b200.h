@@ -195,8 +195,10 @@ int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
  * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi != 0 makes the
  * split warps store the masked high parts explicitly instead of relying on the
  * tensor core ignoring the low 13 mantissa bits; splits is the number of work
- * units the k range of each tile is cut into (1 = none, 0 = the automatic choice;
- * scratch for the partial products comes from the stream-ordered pool).  Fails with
+ * units the k range of each tile is cut into (1 = none, 0 = the automatic choice,
+ * -1 = stream mode: the CTAs take equal shares of all k slabs of all tiles and a tile
+ * may be finished by the next CTA - 128 x 256 tiles only; scratch for the partial
+ * products comes from the stream-ordered pool).  Fails with
  * POLAR_B200_ERR_UNSUPPORTED when the operands cannot be described to TMA
  * (bases not 16-byte aligned, or a contiguous extent that is not a multiple of
  * 4 floats). */

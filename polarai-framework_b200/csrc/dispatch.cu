@@ -10,6 +10,7 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
               uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch = 0);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k);
+uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits);
 int launch_tc_pair(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
                    float* out, float* ws, uint32_t splits, int epilogue, cudaStream_t stream);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -45,10 +46,12 @@ int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
 int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
            float* out, int bn, int bk, int passes, int write_hi, uint32_t splits, void* workspace,
            uint64_t workspace_bytes, cudaStream_t stream, int epilogue = 0, uint64_t left_pitch = 0) {
-  if (splits <= 1)
+  if (splits == 1)
     return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream,
                      left_pitch);
-  const uint64_t need = (uint64_t)splits * m * n * sizeof(float);
+  // splits == 0 is the stream mode of the 128 x 256 tile configuration
+  if (splits == 0 && bn != 256) splits = 1;
+  const uint64_t need = splits == 0 ? tc_workspace_bytes(m, n, k, 0) : (uint64_t)splits * m * n * sizeof(float);
   if (workspace) {
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
       return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
@@ -106,8 +109,7 @@ static uint64_t workspace_need(int tl, int tr, uint64_t m, uint64_t n, uint64_t 
   if (choose_path(tl, tr, m, n, k, al, al, al) == kPathTc) {
     const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, fused == 1 ? 1 : 0);
     const uint64_t mm = m - rem;
-    uint32_t s = tc_default_splits(mm, n, k);
-    uint64_t need = s > 1 ? (uint64_t)s * mm * n * sizeof(float) : 0;
+    uint64_t need = tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k));
     if (rem) {
       const uint64_t r = ragged_rows_workspace_bytes(rem, n, k);
       if (r > need) need = r;
@@ -264,9 +266,11 @@ int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, co
     return fail(POLAR_B200_ERR_INVALID, "passes must be 1 or 3 (13: issue-rate diagnostic)");
   if (!tc_shape_ok(tl, tr, m, n, k, left, right))
     return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
-  if (splits < 0 || splits > 64 || (splits > 1 && ((m * n) & 3)))
-    return fail(POLAR_B200_ERR_INVALID, "splits must be 0 (automatic) or 1..64, and m*n a multiple of 4 when > 1");
-  const uint32_t s = splits == 0 ? tc_default_splits(m, n, k) : (uint32_t)splits;
+  if (splits < -1 || splits > 64 || (splits > 1 && ((m * n) & 3)))
+    return fail(POLAR_B200_ERR_INVALID,
+                "splits must be -1 (stream), 0 (automatic) or 1..64, and m*n a multiple of 4 when > 1");
+  if (splits == -1 && tile_n != 256) return fail(POLAR_B200_ERR_INVALID, "stream mode needs tile_n = 256");
+  const uint32_t s = splits == -1 ? 0u : splits == 0 ? tc_default_splits(m, n, k) : (uint32_t)splits;
   return run_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, s, nullptr, 0, as_stream(stream));
 }
 

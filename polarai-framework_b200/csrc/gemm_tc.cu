@@ -83,6 +83,56 @@ struct Params {
   int epilogue;     // 0: store the product; 1: store fsigmoid(product) (only when splits == 1)
   uint32_t splits;  // work units per tile: the k range is cut into `splits` parts
   float* partial;   // [splits][m][n] partial products when splits > 1
+  // Stream mode (share > 0): the CTAs cut the sequence of all k slabs of all tiles into equal
+  // shares; a CTA's share may end inside a tile and the next CTA continues it.  A piece that is
+  // not a whole tile goes to slot (cta + tile) of `slots`, [slot][128][BN] floats.
+  uint32_t share;
+  float* slots;
+};
+
+constexpr uint32_t kNoSlot = 0xffffffffu;
+
+// One piece of work: slabs [kb0, kb1) of a tile.  Every warp role walks the same sequence.
+struct Piece {
+  uint32_t tile, kb0, kb1, slot;
+};
+
+struct PieceWalk {
+  uint32_t num_kb, splits, num_units, unit, stride, cta;
+  uint64_t g, g_end;
+  bool stream;
+  __device__ __forceinline__ PieceWalk(const Params& p, uint32_t nkb) {
+    num_kb = nkb;
+    splits = p.splits;
+    num_units = p.tiles_m * p.tiles_n * p.splits;
+    unit = blockIdx.x;
+    stride = gridDim.x;
+    cta = blockIdx.x;
+    stream = p.share != 0;
+    const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * nkb;
+    g = (uint64_t)blockIdx.x * p.share;
+    g_end = g + p.share < total ? g + p.share : total;
+  }
+  __device__ __forceinline__ bool next(Piece& pc) {
+    if (!stream) {
+      if (unit >= num_units) return false;
+      const uint32_t sp = unit % splits;
+      pc.tile = unit / splits;
+      pc.kb0 = (uint32_t)(((uint64_t)sp * num_kb) / splits);
+      pc.kb1 = (uint32_t)(((uint64_t)(sp + 1) * num_kb) / splits);
+      pc.slot = splits > 1 ? sp : kNoSlot;
+      unit += stride;
+      return true;
+    }
+    if (g >= g_end) return false;
+    pc.tile = (uint32_t)(g / num_kb);
+    pc.kb0 = (uint32_t)(g % num_kb);
+    const uint64_t left = g_end - g;
+    pc.kb1 = (uint64_t)pc.kb0 + left < num_kb ? (uint32_t)(pc.kb0 + left) : num_kb;
+    pc.slot = (pc.kb0 == 0 && pc.kb1 == num_kb) ? kNoSlot : cta + pc.tile;
+    g += pc.kb1 - pc.kb0;
+    return true;
+  }
 };
 
 // Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
@@ -120,11 +170,8 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
-  // A work unit is (tile, split): tile = unit / splits, the split takes slabs
-  // [split * num_kb / splits, (split + 1) * num_kb / splits).
-  const uint32_t num_tiles = p.tiles_m * p.tiles_n * p.splits;
-  auto slab_begin = [&](uint32_t unit) { return (uint32_t)(((uint64_t)(unit % p.splits) * num_kb) / p.splits); };
-  auto slab_end = [&](uint32_t unit) { return (uint32_t)(((uint64_t)(unit % p.splits + 1) * num_kb) / p.splits); };
+  // Work comes in pieces (PieceWalk): a (tile, split) unit with a fixed share of the k slabs,
+  // or, in stream mode, whatever part of a tile falls into this CTA's share of all slabs.
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -153,10 +200,12 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;   // k slabs issued so far, over all tiles of this CTA
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      PieceWalk walk(p, num_kb);
+      Piece pc;
+      while (ok && walk.next(pc)) {
         int m0, n0;
-        tile_coords(t / p.splits, p.tiles_m, p.tiles_n, BN, &m0, &n0);
-        for (uint32_t kb = slab_begin(t), kb_end = slab_end(t); kb < kb_end; ++kb, ++it) {
+        tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+        for (uint32_t kb = pc.kb0, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101)) { ok = false; break; }
@@ -197,15 +246,17 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t b_sbo = p.b_mn_major ? 512u : kRowGroup, b_lt = p.b_mn_major ? 1u : kKMajorLayout;
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      PieceWalk walk(p, num_kb);
+      Piece pc;
+      for (; ok && walk.next(pc); ++tile_iter) {
         const uint32_t as = tile_iter & 1u;
         // the epilogue must have drained this accumulator (two tiles ago)
         ok = mbar_wait(acc_empty(as), ((tile_iter >> 1) & 1u) ^ 1u, abort_flag, p.status, 106);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + as * BN;
-        const uint32_t kb_first = slab_begin(t);
-        for (uint32_t kb = kb_first, kb_end = slab_end(t); kb < kb_end; ++kb, ++it) {
+        const uint32_t kb_first = pc.kb0;
+        for (uint32_t kb = kb_first, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102);
@@ -258,8 +309,10 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (p.passes == 3) {
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (uint32_t kb = slab_begin(t), kb_end = slab_end(t); kb < kb_end; ++kb, ++it) {
+      PieceWalk walk(p, num_kb);
+      Piece pc;
+      while (ok && walk.next(pc)) {
+        for (uint32_t kb = pc.kb0, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) { ok = false; break; }
@@ -295,10 +348,15 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
     uint32_t tile_iter = 0;
-    for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_iter) {
+    PieceWalk walk(p, num_kb);
+    Piece pc;
+    for (; walk.next(pc); ++tile_iter) {
       int m0, n0;
-      tile_coords(t / p.splits, p.tiles_m, p.tiles_n, BN, &m0, &n0);
-      float* const out_base = p.splits > 1 ? p.partial + (uint64_t)(t % p.splits) * p.m * p.n : p.out;
+      tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+      const bool to_slot = p.share != 0 && pc.slot != kNoSlot;
+      float* const out_base = to_slot ? nullptr
+                              : (p.splits > 1 ? p.partial + (uint64_t)pc.slot * p.m * p.n : p.out);
+      const bool final_piece = !to_slot && p.splits <= 1;      // this store is the result itself
       const uint32_t as = tile_iter & 1u;
       if (!mbar_wait(acc_full(as), (tile_iter >> 1) & 1u, abort_flag, p.status, 105)) break;
       tc_fence_after();
@@ -309,11 +367,20 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
         tmem_ld_wait();
-        if (p.epilogue == 1) {
+        if (p.epilogue == 1 && final_piece) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sigmoid_clamped(__uint_as_float(r[j])));
         }
-        if (row < p.m) {
+        if (to_slot) {
+          // a whole 128 x BN tile per slot, padding rows and columns included (they hold zeros)
+          float* dst = p.slots + ((uint64_t)pc.slot * BM + (uint32_t)(q * 32 + lane)) * BN + c;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                        __uint_as_float(r[j + 3])};
+            *reinterpret_cast<float4*>(dst + j) = v;
+          }
+        } else if (row < p.m) {
           float* dst = out_base + row * p.n + n0 + c;
           if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
 #pragma unroll
@@ -444,9 +511,72 @@ int launch_add_splits(const float* ws, float* out, uint64_t m, uint64_t n, uint3
 // How many ways to cut k so that the persistent grid is evenly loaded: the smallest
 // count up to 8 whose last wave is at least 90 % full, else the best one.  Needs
 // m*n to be a multiple of 4 for the vectorised sum of the partial products.
+// Stream mode: the tiles whose slabs were shared between CTAs are summed from their slots,
+// in ascending CTA order (a fixed order).  Tiles that one CTA computed whole are in `out` already.
+template <int BN>
+__global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restrict__ slots, float* __restrict__ out,
+                                                            uint64_t m, uint64_t n, uint32_t tiles_m, uint32_t tiles_n,
+                                                            uint32_t num_kb, uint32_t share, int epilogue) {
+  constexpr uint32_t kVecsPerTile = BM * BN / 4;
+  constexpr uint32_t kBlocksPerTile = kVecsPerTile / 256;
+  const uint32_t tile = blockIdx.x / kBlocksPerTile;
+  const uint32_t v = (blockIdx.x % kBlocksPerTile) * 256 + threadIdx.x;
+  const uint32_t c_first = (uint32_t)(((uint64_t)tile * num_kb) / share);
+  const uint32_t c_last = (uint32_t)((((uint64_t)tile + 1) * num_kb - 1) / share);
+  if (c_first == c_last) return;
+  int m0, n0;
+  tile_coords(tile, tiles_m, tiles_n, BN, &m0, &n0);
+  const uint32_t r = v / (BN / 4), c = (v % (BN / 4)) * 4;
+  const uint64_t row = (uint64_t)m0 + r, col = (uint64_t)n0 + c;
+  if (row >= m || col >= n) return;
+  const float4* src = reinterpret_cast<const float4*>(slots) + ((uint64_t)(c_first + tile) * kVecsPerTile + v);
+  float4 acc = __ldcg(src);
+  for (uint32_t cta = c_first + 1; cta <= c_last; ++cta) {
+    src += kVecsPerTile;
+    const float4 x = __ldcg(src);
+    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+  }
+  if (epilogue == 1) {
+    acc.x = sigmoid_clamped(acc.x); acc.y = sigmoid_clamped(acc.y);
+    acc.z = sigmoid_clamped(acc.z); acc.w = sigmoid_clamped(acc.w);
+  }
+  float* dst = out + row * n + col;
+  if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    *reinterpret_cast<float4*>(dst) = acc;
+  } else {
+    dst[0] = acc.x;
+    if (col + 1 < n) dst[1] = acc.y;
+    if (col + 2 < n) dst[2] = acc.z;
+    if (col + 3 < n) dst[3] = acc.w;
+  }
+}
+
+// Stream mode geometry for `tiles` tiles of `num_kb` slabs: CTAs, slabs per CTA, scratch.
+struct StreamPlan {
+  uint32_t grid, share;
+  uint64_t bytes;
+};
+StreamPlan stream_plan(uint64_t tiles, uint64_t num_kb, int bn) {
+  const uint64_t total = tiles * num_kb;
+  uint64_t g = (uint64_t)sm_count();
+  if (g > total) g = total;
+  const uint64_t share = (total + g - 1) / g;
+  const uint64_t grid = (total + share - 1) / share;
+  return StreamPlan{(uint32_t)grid, (uint32_t)share, (grid + tiles) * (uint64_t)BM * (uint64_t)bn * sizeof(float)};
+}
+
 uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) {
   const uint64_t sms = (uint64_t)sm_count();
-  if (((m * n) & 3) != 0 || tiles >= 8 * sms) return 1;
+  if (tiles >= 8 * sms) return 1;
+  // last wave at least 95 % full with whole tiles: nothing to gain from cutting k
+  if ((double)tiles / (double)(((tiles + sms - 1) / sms) * sms) >= 0.95) return 1;
+  // Stream mode (0) balances perfectly but its CTAs sit at different k offsets of tiles that
+  // share operand panels, so the panels are re-read from DRAM (3.3x the operand bytes measured
+  // on 784 x 4096 x 8192).  In the MLP step it wins up to k = 16384 (step 0.703 vs 0.730 ms at
+  // 8192, 1.305 vs 1.340 ms at 16384), ties at 32768 and loses at 65536 (5.35 vs 5.17 ms: the
+  // extra traffic costs clock under the power cap), where fixed cuts keep tiles in lockstep.
+  if (num_kb <= 1024 && tiles * num_kb >= 64 * sms) return 0;
+  if (((m * n) & 3) != 0) return 1;
   double best_eff = 0.0;
   uint32_t best = 1;
   for (uint32_t s = 1; s <= 8; ++s) {
@@ -493,6 +623,24 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   if (tm * tn > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   p.tiles_m = (uint32_t)tm; p.tiles_n = (uint32_t)tn;
   const uint64_t num_kb = (k + BK - 1) / BK;
+  p.share = 0;
+  p.slots = nullptr;
+  if (splits == 0 && ws && tm * tn * num_kb < 0xffffffffull) {
+    // stream mode: equal shares of all slabs, partial tiles through slots, then one summing pass
+    const StreamPlan plan = stream_plan(tm * tn, num_kb, BN);
+    p.splits = 1;
+    p.partial = nullptr;
+    p.epilogue = epilogue;
+    p.share = plan.share;
+    p.slots = ws;
+    fmatmul_tc_kernel<BN, BK><<<plan.grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+    rc = check_launch("fmatmul_tc");
+    if (rc) return rc;
+    constexpr uint32_t kBlocksPerTile = BM * BN / 4 / 256;
+    stream_reduce_kernel<BN><<<(unsigned)(tm * tn * kBlocksPerTile), 256, 0, stream>>>(
+        ws, out, m, n, p.tiles_m, p.tiles_n, (uint32_t)num_kb, plan.share, epilogue);
+    return check_launch("fmatmul_stream_reduce");
+  }
   if (splits < 1 || !ws || splits > num_kb) splits = 1;
   p.splits = splits;
   p.partial = splits > 1 ? ws : nullptr;
@@ -526,6 +674,12 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
 // Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k) {
   return tc::choose_splits(((m + 127) / 128) * ((n + 255) / 256), (k + 15) / 16, m, n);
+}
+
+// Scratch the default configuration needs for `splits` (0 = stream mode) work units per tile.
+uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits) {
+  if (splits == 0) return tc::stream_plan(((m + 127) / 128) * ((n + 255) / 256), (k + 15) / 16, 256).bytes;
+  return splits > 1 ? (uint64_t)splits * m * n * sizeof(float) : 0;
 }
 
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,

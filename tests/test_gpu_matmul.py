@@ -88,6 +88,30 @@ def test_tensor_core_path(gpu, par_oracle, tl, tr, shape):
     assert gpu.d.device_status() == 0
 
 
+@pytest.mark.parametrize("tl", [0, 1])
+@pytest.mark.parametrize("tr", [0, 1])
+@pytest.mark.parametrize("shape", SHAPES + [(784, 4096, 8192), (300, 700, 5000), (128, 256, 16 * 1000)])
+def test_k_cut_into_work_units_and_stream_mode(gpu, par_oracle, tl, tr, shape):
+    # fixed cuts of k (2, 3, 8 units per tile) and stream mode (-1: equal shares of all slabs per
+    # CTA, tiles continued by the next CTA) give the product to the same accuracy, run to run
+    # the same bits, for every transpose form and ragged shape
+    m, n, k = shape
+    if m * n * k > 1 << 33 and (tl, tr) != (1, 0):
+        pytest.skip("the large case runs in the form the MLP's weight gradient uses")
+    rng = np.random.default_rng(m * 5 + n * 3 + k + tl * 2 + tr)
+    l, r = operands(rng, tl, tr, m, n, k)
+    ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
+    for splits in (-1, 2, 3, 8):
+        if splits > 1 and ((m * n) & 3 or (k + 15) // 16 < splits):
+            continue
+        for slab_k in ((16, 32) if splits == -1 else (16,)):
+            got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=256, slab_k=slab_k, splits=splits)
+            assert rel_err(got, ref, mag) <= 5e-6, (splits, slab_k)
+            again = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=256, slab_k=slab_k, splits=splits)
+            assert np.array_equal(got.view(np.uint32), again.view(np.uint32)), (splits, slab_k)
+    assert gpu.d.device_status() == 0
+
+
 @pytest.mark.parametrize("tl,tr,m,n,k", [
     (0, 0, 256, 1, 784),      # logistic regression forward
     (1, 0, 784, 1, 256),      # X^T dZ
