@@ -52,6 +52,9 @@ int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left
   // splits == 0 is the stream mode of the 128 x 256 tile configuration
   if (splits == 0 && bn != 256) splits = 1;
   const uint64_t need = splits == 0 ? tc_workspace_bytes(m, n, k, 0) : (uint64_t)splits * m * n * sizeof(float);
+  if (need == 0)   // stream mode asked for a shape it does not suit
+    return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream,
+                     left_pitch);
   if (workspace) {
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
       return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");

@@ -83,10 +83,14 @@ struct Params {
   int epilogue;     // 0: store the product; 1: store fsigmoid(product) (only when splits == 1)
   uint32_t splits;  // work units per tile: the k range is cut into `splits` parts
   float* partial;   // [splits][m][n] partial products when splits > 1
-  // Stream mode (share > 0): the CTAs cut the sequence of all k slabs of all tiles into equal
-  // shares; a CTA's share may end inside a tile and the next CTA continues it.  A piece that is
-  // not a whole tile goes to slot (cta + tile) of `slots`, [slot][128][BN] floats.
-  uint32_t share;
+  // Stream mode (share > 0): CTAs form teams of tiles_m, one CTA per row tile.  The teams cut
+  // the sequence (column tile 0, all its k slabs), (column tile 1, ...), ... into equal shares;
+  // a share may end inside a column and the next team continues it.  The CTAs of a team work
+  // on the same column and the same k at the same time, so they share the column's operand
+  // panel in L2.  A piece that is not a whole tile goes to a slot of `slots`,
+  // [row][team + column][128][BN] floats.
+  uint32_t share;   // slabs per team
+  uint32_t teams;
   float* slots;
 };
 
@@ -98,7 +102,8 @@ struct Piece {
 };
 
 struct PieceWalk {
-  uint32_t num_kb, splits, num_units, unit, stride, cta;
+  uint32_t num_kb, splits, num_units, unit, stride;
+  uint32_t row, team, tiles_m, slot_base;
   uint64_t g, g_end;
   bool stream;
   __device__ __forceinline__ PieceWalk(const Params& p, uint32_t nkb) {
@@ -107,11 +112,15 @@ struct PieceWalk {
     num_units = p.tiles_m * p.tiles_n * p.splits;
     unit = blockIdx.x;
     stride = gridDim.x;
-    cta = blockIdx.x;
     stream = p.share != 0;
-    const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * nkb;
-    g = (uint64_t)blockIdx.x * p.share;
+    tiles_m = p.tiles_m;
+    row = blockIdx.x % p.tiles_m;
+    team = blockIdx.x / p.tiles_m;
+    slot_base = row * (p.teams + p.tiles_n) + team;
+    const uint64_t total = (uint64_t)p.tiles_n * nkb;
+    g = (uint64_t)team * p.share;
     g_end = g + p.share < total ? g + p.share : total;
+    if (team >= p.teams) g = g_end = 0;
   }
   __device__ __forceinline__ bool next(Piece& pc) {
     if (!stream) {
@@ -125,11 +134,12 @@ struct PieceWalk {
       return true;
     }
     if (g >= g_end) return false;
-    pc.tile = (uint32_t)(g / num_kb);
+    const uint32_t col = (uint32_t)(g / num_kb);
+    pc.tile = col * tiles_m + row;        // tile_coords' raster when tiles_m <= kGroupM
     pc.kb0 = (uint32_t)(g % num_kb);
     const uint64_t left = g_end - g;
     pc.kb1 = (uint64_t)pc.kb0 + left < num_kb ? (uint32_t)(pc.kb0 + left) : num_kb;
-    pc.slot = (pc.kb0 == 0 && pc.kb1 == num_kb) ? kNoSlot : cta + pc.tile;
+    pc.slot = (pc.kb0 == 0 && pc.kb1 == num_kb) ? kNoSlot : slot_base + col;
     g += pc.kb1 - pc.kb0;
     return true;
   }
@@ -511,27 +521,30 @@ int launch_add_splits(const float* ws, float* out, uint64_t m, uint64_t n, uint3
 // How many ways to cut k so that the persistent grid is evenly loaded: the smallest
 // count up to 8 whose last wave is at least 90 % full, else the best one.  Needs
 // m*n to be a multiple of 4 for the vectorised sum of the partial products.
-// Stream mode: the tiles whose slabs were shared between CTAs are summed from their slots,
-// in ascending CTA order (a fixed order).  Tiles that one CTA computed whole are in `out` already.
+// Stream mode: the tiles whose slabs were shared between teams are summed from their slots,
+// in ascending team order (a fixed order).  Tiles that one CTA computed whole are in `out` already.
 template <int BN>
 __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restrict__ slots, float* __restrict__ out,
                                                             uint64_t m, uint64_t n, uint32_t tiles_m, uint32_t tiles_n,
-                                                            uint32_t num_kb, uint32_t share, int epilogue) {
+                                                            uint32_t num_kb, uint32_t share, uint32_t teams,
+                                                            int epilogue) {
   constexpr uint32_t kVecsPerTile = BM * BN / 4;
   constexpr uint32_t kBlocksPerTile = kVecsPerTile / 256;
   const uint32_t tile = blockIdx.x / kBlocksPerTile;
   const uint32_t v = (blockIdx.x % kBlocksPerTile) * 256 + threadIdx.x;
-  const uint32_t c_first = (uint32_t)(((uint64_t)tile * num_kb) / share);
-  const uint32_t c_last = (uint32_t)((((uint64_t)tile + 1) * num_kb - 1) / share);
-  if (c_first == c_last) return;
+  const uint32_t trow = tile % tiles_m, col_tile = tile / tiles_m;
+  const uint32_t t_first = (uint32_t)(((uint64_t)col_tile * num_kb) / share);
+  const uint32_t t_last = (uint32_t)((((uint64_t)col_tile + 1) * num_kb - 1) / share);
+  if (t_first == t_last) return;
   int m0, n0;
   tile_coords(tile, tiles_m, tiles_n, BN, &m0, &n0);
   const uint32_t r = v / (BN / 4), c = (v % (BN / 4)) * 4;
   const uint64_t row = (uint64_t)m0 + r, col = (uint64_t)n0 + c;
   if (row >= m || col >= n) return;
-  const float4* src = reinterpret_cast<const float4*>(slots) + ((uint64_t)(c_first + tile) * kVecsPerTile + v);
+  const uint64_t first_slot = (uint64_t)trow * (teams + tiles_n) + t_first + col_tile;
+  const float4* src = reinterpret_cast<const float4*>(slots) + (first_slot * kVecsPerTile + v);
   float4 acc = __ldcg(src);
-  for (uint32_t cta = c_first + 1; cta <= c_last; ++cta) {
+  for (uint32_t t = t_first + 1; t <= t_last; ++t) {
     src += kVecsPerTile;
     const float4 x = __ldcg(src);
     acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
@@ -551,18 +564,23 @@ __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restr
   }
 }
 
-// Stream mode geometry for `tiles` tiles of `num_kb` slabs: CTAs, slabs per CTA, scratch.
+// Stream mode geometry: teams of tiles_m CTAs, slabs per team, CTAs in all, scratch.
+// teams == 0: the shape does not suit the mode (more row tiles than the raster's group, or
+// than SMs).
 struct StreamPlan {
-  uint32_t grid, share;
+  uint32_t grid, share, teams;
   uint64_t bytes;
 };
-StreamPlan stream_plan(uint64_t tiles, uint64_t num_kb, int bn) {
-  const uint64_t total = tiles * num_kb;
-  uint64_t g = (uint64_t)sm_count();
-  if (g > total) g = total;
-  const uint64_t share = (total + g - 1) / g;
-  const uint64_t grid = (total + share - 1) / share;
-  return StreamPlan{(uint32_t)grid, (uint32_t)share, (grid + tiles) * (uint64_t)BM * (uint64_t)bn * sizeof(float)};
+StreamPlan stream_plan(uint64_t tiles_m, uint64_t tiles_n, uint64_t num_kb, int bn) {
+  const uint64_t sms = (uint64_t)sm_count();
+  if (tiles_m == 0 || tiles_m > (uint64_t)kGroupM || tiles_m > sms) return StreamPlan{0, 0, 0, 0};
+  const uint64_t total = tiles_n * num_kb;
+  uint64_t teams = sms / tiles_m;
+  if (teams > total) teams = total;
+  const uint64_t share = (total + teams - 1) / teams;
+  teams = (total + share - 1) / share;
+  return StreamPlan{(uint32_t)(teams * tiles_m), (uint32_t)share, (uint32_t)teams,
+                    tiles_m * (teams + tiles_n) * (uint64_t)BM * (uint64_t)bn * sizeof(float)};
 }
 
 uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) {
@@ -570,12 +588,15 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) 
   if (tiles >= 8 * sms) return 1;
   // last wave at least 95 % full with whole tiles: nothing to gain from cutting k
   if ((double)tiles / (double)(((tiles + sms - 1) / sms) * sms) >= 0.95) return 1;
-  // Stream mode (0) balances perfectly but its CTAs sit at different k offsets of tiles that
-  // share operand panels, so the panels are re-read from DRAM (3.3x the operand bytes measured
-  // on 784 x 4096 x 8192).  In the MLP step it wins up to k = 16384 (step 0.703 vs 0.730 ms at
-  // 8192, 1.305 vs 1.340 ms at 16384), ties at 32768 and loses at 65536 (5.35 vs 5.17 ms: the
-  // extra traffic costs clock under the power cap), where fixed cuts keep tiles in lockstep.
-  if (num_kb <= 1024 && tiles * num_kb >= 64 * sms) return 0;
+  // Stream mode (0): teams of CTAs in lockstep with perfectly even shares; taken when it keeps
+  // at least 95 % of the SMs busy and every team still gets a decent run of slabs.  Measured in
+  // the MLP step (dW1, 784 x 4096 x k) against the fixed cuts below: the step takes 0.714 vs
+  // 0.730 ms at k = 8192, 1.317 vs 1.340 ms at 16384, 2.58 vs 2.60 ms at 32768, but 5.21 vs
+  // 5.17 ms at 65536, where both balance equally well - so fixed cuts keep the long sums.
+  if (num_kb <= 2048) {
+    const StreamPlan plan = stream_plan((m + BM - 1) / BM, (n + 255) / 256, num_kb, 256);
+    if (plan.teams && plan.share >= 64 && (double)plan.grid >= 0.95 * (double)sms) return 0;
+  }
   if (((m * n) & 3) != 0) return 1;
   double best_eff = 0.0;
   uint32_t best = 1;
@@ -625,20 +646,22 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   const uint64_t num_kb = (k + BK - 1) / BK;
   p.share = 0;
   p.slots = nullptr;
-  if (splits == 0 && ws && tm * tn * num_kb < 0xffffffffull) {
+  p.teams = 0;
+  const StreamPlan plan = (splits == 0 && ws) ? stream_plan(tm, tn, num_kb, BN) : StreamPlan{0, 0, 0, 0};
+  if (plan.teams) {
     // stream mode: equal shares of all slabs, partial tiles through slots, then one summing pass
-    const StreamPlan plan = stream_plan(tm * tn, num_kb, BN);
     p.splits = 1;
     p.partial = nullptr;
     p.epilogue = epilogue;
     p.share = plan.share;
+    p.teams = plan.teams;
     p.slots = ws;
     fmatmul_tc_kernel<BN, BK><<<plan.grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
     rc = check_launch("fmatmul_tc");
     if (rc) return rc;
     constexpr uint32_t kBlocksPerTile = BM * BN / 4 / 256;
     stream_reduce_kernel<BN><<<(unsigned)(tm * tn * kBlocksPerTile), 256, 0, stream>>>(
-        ws, out, m, n, p.tiles_m, p.tiles_n, (uint32_t)num_kb, plan.share, epilogue);
+        ws, out, m, n, p.tiles_m, p.tiles_n, (uint32_t)num_kb, plan.share, plan.teams, epilogue);
     return check_launch("fmatmul_stream_reduce");
   }
   if (splits < 1 || !ws || splits > num_kb) splits = 1;
@@ -678,7 +701,7 @@ uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k) {
 
 // Scratch the default configuration needs for `splits` (0 = stream mode) work units per tile.
 uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits) {
-  if (splits == 0) return tc::stream_plan(((m + 127) / 128) * ((n + 255) / 256), (k + 15) / 16, 256).bytes;
+  if (splits == 0) return tc::stream_plan((m + 127) / 128, (n + 255) / 256, (k + 15) / 16, 256).bytes;
   return splits > 1 ? (uint64_t)splits * m * n * sizeof(float) : 0;
 }
 
