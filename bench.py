@@ -460,7 +460,7 @@ def run_mlp(args):
     line["device_status"] = status                          # 0: no bounded device-side wait gave up
     if fused and not args.no_extras:
         # The same step as the reference's own builtin chain, one launch per builtin (20 launches
-        # instead of 12-13) with NCCL all-reduces: same outputs bit for bit at one rank.  Every
+        # instead of 8-9) with NCCL all-reduces: same outputs bit for bit at one rank.  Every
         # rank runs it (its all-reduces are collective).
         cex = DeviceExecutor(chain, dev, make_allreduce(world))
         cex.t["X"].copy_(ex.t["X"]), cex.t["Y"].copy_(ex.t["Y"])

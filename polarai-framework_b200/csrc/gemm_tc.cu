@@ -32,9 +32,11 @@
 // descriptors, the instruction descriptor's major bits and the TMA boxes differ.
 //
 // Shapes with too few tiles to load every SM evenly (e.g. 784 x 4096 with a k of
-// 65536: 112 tiles on 148 SMs) are cut along k into up to 8 work units per tile;
-// each unit writes its partial product to scratch and a second kernel adds them
-// in a fixed order.
+// 65536: 112 tiles on 148 SMs) are cut along k, either into up to 8 work units per
+// tile whose partial products a second kernel adds in a fixed order, or - stream
+// mode, for k up to 32768 - into exactly equal shares per team of CTAs, a team
+// being one CTA per row tile working the same column tile and k range in lockstep
+// (see Params and PieceWalk).  Every warp role walks the same sequence of pieces.
 //
 // Every wait on an mbarrier is bounded: after about two seconds of polling the
 // waiter records a code in the status word, raises the CTA's abort flag, and
