@@ -199,20 +199,35 @@ small_n_kmajor_resident_kernel(const float* __restrict__ left, const float* __re
 
 constexpr int KS = 128;   // rows of R staged per pass
 
+// Two fused multiply-adds in one instruction (sm_100: fma.rn.f32x2 on register pairs), each
+// an IEEE fma like fmaf: (c.lo, c.hi) = (a.lo, a.hi) * (b.lo, b.hi) + (c.lo, c.hi).
+__device__ __forceinline__ void ffma2(unsigned long long& c, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// The kernel issues one instruction per two multiply-adds and reads each value of the staged
+// operand as a ready-made (b, b) pair: at 16 columns the plain form needs every issue slot of
+// the SM to keep up with HBM (64 FMA + 16 shared-memory loads per 16 bytes streamed).
 template <int NP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__ right,
                        float* __restrict__ partial, uint64_t m, uint64_t n, uint64_t k, uint64_t rsk,
                        uint64_t rsj, uint64_t k_per_split) {
-  __shared__ float bs[KS][NP];
+  __shared__ __align__(8) float2 bs[KS][NP];   // every value twice: one 64-bit load yields the pair
   const uint64_t m0 = ((uint64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
   const uint64_t kbeg = (uint64_t)blockIdx.y * k_per_split;
   const uint64_t kend = (kbeg + k_per_split < k) ? kbeg + k_per_split : k;
-  float acc[4][NP];
+  unsigned long long acc01[NP], acc23[NP];      // rows (0,1) and (2,3) of the thread's four
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < NP; ++j) acc[i][j] = 0.f;
+  for (int j = 0; j < NP; ++j) acc01[j] = acc23[j] = 0ull;
   const bool live = m0 < m;   // m is a multiple of 4
   for (uint64_t k0 = kbeg; k0 < kend; k0 += KS) {
     const int ks = (int)((kend - k0 < KS) ? (kend - k0) : KS);
@@ -221,7 +236,7 @@ small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__
       int j = e % NP, kk = e / NP;
       float v = 0.f;
       if (kk < ks && (uint64_t)j < n) v = right[(k0 + kk) * rsk + (uint64_t)j * rsj];
-      bs[kk][j] = v;
+      bs[kk][j] = make_float2(v, v);
     }
     __syncthreads();
     if (live) {
@@ -234,25 +249,24 @@ small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__
         for (int u = 0; u < 8; ++u)
           a[u] = __ldcs(reinterpret_cast<const float4*>(left + (k0 + kk + u) * m + m0));
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < 8; ++u) {
+          const unsigned long long a01 = pack2(a[u].x, a[u].y), a23 = pack2(a[u].z, a[u].w);
 #pragma unroll
           for (int j = 0; j < NP; ++j) {
-            float b = bs[kk + u][j];
-            acc[0][j] = fmaf(a[u].x, b, acc[0][j]);
-            acc[1][j] = fmaf(a[u].y, b, acc[1][j]);
-            acc[2][j] = fmaf(a[u].z, b, acc[2][j]);
-            acc[3][j] = fmaf(a[u].w, b, acc[3][j]);
+            const unsigned long long bb = *reinterpret_cast<const unsigned long long*>(&bs[kk + u][j]);
+            ffma2(acc01[j], a01, bb);
+            ffma2(acc23[j], a23, bb);
           }
+        }
       }
       for (; kk < ks; ++kk) {
-        float4 a = __ldcs(reinterpret_cast<const float4*>(left + (k0 + kk) * m + m0));
+        const float4 a = __ldcs(reinterpret_cast<const float4*>(left + (k0 + kk) * m + m0));
+        const unsigned long long a01 = pack2(a.x, a.y), a23 = pack2(a.z, a.w);
 #pragma unroll
         for (int j = 0; j < NP; ++j) {
-          float b = bs[kk][j];
-          acc[0][j] = fmaf(a.x, b, acc[0][j]);
-          acc[1][j] = fmaf(a.y, b, acc[1][j]);
-          acc[2][j] = fmaf(a.z, b, acc[2][j]);
-          acc[3][j] = fmaf(a.w, b, acc[3][j]);
+          const unsigned long long bb = *reinterpret_cast<const unsigned long long*>(&bs[kk][j]);
+          ffma2(acc01[j], a01, bb);
+          ffma2(acc23[j], a23, bb);
         }
       }
     }
@@ -260,10 +274,17 @@ small_n_mnmajor_kernel(const float* __restrict__ left, const float* __restrict__
   if (live) {
     float* dst = partial + ((uint64_t)blockIdx.y * m + m0) * n;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < NP; ++j)
-        if ((uint64_t)j < n) dst[(uint64_t)i * n + j] = acc[i][j];
+    for (int j = 0; j < NP; ++j) {
+      float r0, r1, r2, r3;
+      unpack2(acc01[j], r0, r1);
+      unpack2(acc23[j], r2, r3);
+      if ((uint64_t)j < n) {
+        dst[j] = r0;
+        dst[n + j] = r1;
+        dst[2 * n + j] = r2;
+        dst[3 * n + j] = r3;
+      }
+    }
   }
 }
 
