@@ -190,11 +190,12 @@ int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
                             const float* right, float* out, void* stream);
 
 /* The tensor-core path alone, with its tuning knobs exposed for tests and
- * benchmarks: tile_n is 128 or 256; slab_k is 16 or 32 (floats of k staged per
- * pipeline stage); passes is 3 (fp32-accurate three-product
- * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi != 0 makes the
+ * benchmarks: tile_n is 128 or 256 (128 x tile_n tiles), or 512 for 256 x 256 tiles
+ * (slab_k 16 only); slab_k is 16 or 32 (floats of k staged per pipeline stage); passes is 3 (fp32-accurate three-product
+ * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi == 1 makes the
  * split warps store the masked high parts explicitly instead of relying on the
- * tensor core ignoring the low 13 mantissa bits; splits is the number of work
+ * tensor core ignoring the low 13 mantissa bits (2: diagnostic, the result is not
+ * stored); splits is the number of work
  * units the k range of each tile is cut into (1 = none, 0 = the automatic choice,
  * -1 = stream mode: the CTAs take equal shares of all k slabs of all tiles and a tile
  * may be finished by the next CTA - 128 x 256 tiles only; scratch for the partial

@@ -60,8 +60,14 @@ constexpr int kGroupM = 16;                                     // tile raster: 
 
 // BN: tile width (256 or 128).  BK: floats per k slab (32 -> 128-byte rows, 16 ->
 // 64-byte rows); a shallower slab halves the stage and doubles the pipeline depth.
-template <int BN, int BK> struct Cfg {
-  static constexpr uint32_t kABytes = BM * BK * 4;
+// MT = row sub-tiles of 128 per CTA tile.  MT = 1: 128 x BN tiles, the two tensor-memory
+// accumulators alternate between consecutive tiles so the epilogue of one overlaps the k loop
+// of the next.  MT = 2: 256 x BN tiles, both accumulators belong to the current tile; every B
+// slab fetched from L2, and its split pass, then serves twice the multiply-adds (operand bytes
+// per flop drop by a third), at the price of an epilogue that is not overlapped.
+template <int BN, int BK, int MT = 1> struct Cfg {
+  static constexpr uint32_t kASubBytes = BM * BK * 4;      // one 128-row sub-tile of A
+  static constexpr uint32_t kABytes = MT * kASubBytes;
   static constexpr uint32_t kBBytes = BN * BK * 4;
   static constexpr uint32_t kRawBytes = kABytes + kBBytes;
   static constexpr uint32_t kStageBytes = 2 * kRawBytes;   // raw (hi) + lo
@@ -150,21 +156,24 @@ struct PieceWalk {
 // Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
 // CTAs running at the same time share A row panels and B column panels in L2.
 __device__ __forceinline__ void tile_coords(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, int bn,
-                                            int* m0, int* n0) {
+                                            int* m0, int* n0, int bm = BM) {
   const uint32_t per_group = kGroupM * tiles_n;
   const uint32_t g = t / per_group;
   const uint32_t first_m = g * kGroupM;
   const uint32_t rows = (tiles_m - first_m < (uint32_t)kGroupM) ? tiles_m - first_m : (uint32_t)kGroupM;
   const uint32_t r = t - g * per_group;
-  *m0 = (int)((first_m + r % rows) * BM);
+  *m0 = (int)((first_m + r % rows) * bm);
   *n0 = (int)((r / rows) * bn);
 }
 
-template <int BN, int BK>
+template <int BN, int BK, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const Params p) {
-  using C = Cfg<BN, BK>;
+  using C = Cfg<BN, BK, MT>;
+  constexpr int kTileM = BM * MT;
+  // accumulator columns of row sub-tile h of the tile held in buffer `as`
+  auto acc_col = [](uint32_t as, int h) { return (uint32_t)((MT == 1 ? as : (uint32_t)h) * BN); };
   constexpr int S = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -216,7 +225,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       Piece pc;
       while (ok && walk.next(pc)) {
         int m0, n0;
-        tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+        tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
         for (uint32_t kb = pc.kb0, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
@@ -225,9 +234,10 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           mbar_expect_tx(full_raw(s), C::kRawBytes);
           const int k0 = (int)(kb * BK);
           if (!p.a_mn_major) {
-            tma_load_2d(stage, &map_a, full_raw(s), k0, m0);          // box {BK k, 128 m}
+            for (int h = 0; h < MT; ++h)                               // boxes {BK k, 128 m}
+              tma_load_2d(stage + h * C::kASubBytes, &map_a, full_raw(s), k0, m0 + h * BM);
           } else {
-            for (int c = 0; c < BM / 32; ++c)                          // boxes {32 m, BK k}
+            for (int c = 0; c < kTileM / 32; ++c)                      // boxes {32 m, BK k}
               tma_load_2d(stage + c * C::kBoxBytes, &map_a, full_raw(s), m0 + 32 * c, k0);
           }
           const uint32_t bdst = stage + C::kABytes;
@@ -261,12 +271,13 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       PieceWalk walk(p, num_kb);
       Piece pc;
       for (; ok && walk.next(pc); ++tile_iter) {
-        const uint32_t as = tile_iter & 1u;
-        // the epilogue must have drained this accumulator (two tiles ago)
-        ok = mbar_wait(acc_empty(as), ((tile_iter >> 1) & 1u) ^ 1u, abort_flag, p.status, 106);
+        // MT = 1: the two accumulators alternate, the epilogue must have drained this one (two
+        // tiles ago).  MT = 2: one buffer of two accumulators, drained after every tile.
+        const uint32_t as = MT == 1 ? (tile_iter & 1u) : 0u;
+        const uint32_t use = MT == 1 ? (tile_iter >> 1) : tile_iter;   // how often this buffer was used
+        ok = mbar_wait(acc_empty(as), (use & 1u) ^ 1u, abort_flag, p.status, 106);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_acc = tmem_base + as * BN;
         const uint32_t kb_first = pc.kb0;
         for (uint32_t kb = kb_first, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
@@ -281,9 +292,13 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           // hi*hi needs only what TMA delivered: issue it while the split warps work
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
-            const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
             const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
-            tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, ((kb - kb_first) | (uint32_t)kk) ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              const uint64_t da_hi = make_desc(a_hi + h * C::kASubBytes + kk * a_step, a_lbo, a_sbo, a_lt);
+              tc_mma_tf32(tmem_base + acc_col(as, h), da_hi, db_hi, idesc,
+                          ((kb - kb_first) | (uint32_t)kk) ? 1u : 0u);
+            }
           }
           if (p.passes == 3) {
             ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103);
@@ -291,12 +306,16 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < BK / 8; ++kk) {
-              const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
               const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
-              const uint64_t da_lo = make_desc(a_lo + kk * a_step, a_lbo, a_sbo, a_lt);
               const uint64_t db_lo = make_desc(b_lo + kk * b_step, b_lbo, b_sbo, b_lt);
-              tc_mma_tf32(tmem_acc, da_lo, db_hi, idesc, 1u);
-              tc_mma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
+#pragma unroll
+              for (int h = 0; h < MT; ++h) {
+                const uint32_t sub = h * C::kASubBytes + kk * a_step;
+                const uint64_t da_hi = make_desc(a_hi + sub, a_lbo, a_sbo, a_lt);
+                const uint64_t da_lo = make_desc(a_lo + sub, a_lbo, a_sbo, a_lt);
+                tc_mma_tf32(tmem_base + acc_col(as, h), da_lo, db_hi, idesc, 1u);
+                tc_mma_tf32(tmem_base + acc_col(as, h), da_hi, db_lo, idesc, 1u);
+              }
             }
           }
           if (p.passes == 13) {
@@ -304,10 +323,13 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             // pass at all (the result is 3 x the plain TF32 product)
 #pragma unroll
             for (int kk = 0; kk < BK / 8; ++kk) {
-              const uint64_t da_hi = make_desc(a_hi + kk * a_step, a_lbo, a_sbo, a_lt);
               const uint64_t db_hi = make_desc(b_hi + kk * b_step, b_lbo, b_sbo, b_lt);
-              tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
-              tc_mma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
+#pragma unroll
+              for (int h = 0; h < MT; ++h) {
+                const uint64_t da_hi = make_desc(a_hi + h * C::kASubBytes + kk * a_step, a_lbo, a_sbo, a_lt);
+                tc_mma_tf32(tmem_base + acc_col(as, h), da_hi, db_hi, idesc, 1u);
+                tc_mma_tf32(tmem_base + acc_col(as, h), da_hi, db_hi, idesc, 1u);
+              }
             }
           }
           tc_commit(empty(s));   // frees the stage once these MMAs have read it
@@ -343,7 +365,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
             float4 l = {v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w};
             lo[e] = l;
-            if (p.write_hi) raw[e] = h;
+            if (p.write_hi == 1) raw[e] = h;
           }
           fence_async_smem();
           mbar_arrive(full_lo(s));
@@ -364,16 +386,20 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     Piece pc;
     for (; walk.next(pc); ++tile_iter) {
       int m0, n0;
-      tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0);
+      tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
       const bool to_slot = p.share != 0 && pc.slot != kNoSlot;
       float* const out_base = to_slot ? nullptr
                               : (p.splits > 1 ? p.partial + (uint64_t)pc.slot * p.m * p.n : p.out);
       const bool final_piece = !to_slot && p.splits <= 1;      // this store is the result itself
-      const uint32_t as = tile_iter & 1u;
-      if (!mbar_wait(acc_full(as), (tile_iter >> 1) & 1u, abort_flag, p.status, 105)) break;
+      const uint32_t as = MT == 1 ? (tile_iter & 1u) : 0u;
+      const uint32_t use = MT == 1 ? (tile_iter >> 1) : tile_iter;
+      if (!mbar_wait(acc_full(as), use & 1u, abort_flag, p.status, 105)) break;
       tc_fence_after();
-      const uint64_t row = (uint64_t)m0 + q * 32 + lane;
-      const uint32_t tmem_acc = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int h = 0; h < MT; ++h) {
+      const uint32_t tile_row = (uint32_t)(h * BM + q * 32 + lane);
+      const uint64_t row = (uint64_t)m0 + tile_row;
+      const uint32_t tmem_acc = tmem_base + acc_col(as, h) + ((uint32_t)(q * 32) << 16);
       for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
         if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
         uint32_t r[32];
@@ -383,9 +409,11 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sigmoid_clamped(__uint_as_float(r[j])));
         }
-        if (to_slot) {
-          // a whole 128 x BN tile per slot, padding rows and columns included (they hold zeros)
-          float* dst = p.slots + ((uint64_t)pc.slot * BM + (uint32_t)(q * 32 + lane)) * BN + c;
+        if (p.write_hi == 2) {
+          // diagnostic: the accumulator is drained but nothing is stored
+        } else if (to_slot) {
+          // a whole tile per slot, padding rows and columns included (they hold zeros)
+          float* dst = p.slots + ((uint64_t)pc.slot * kTileM + tile_row) * BN + c;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
@@ -408,6 +436,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
         }
       }
+      }   // row sub-tiles
       tc_fence_before();
       mbar_arrive(acc_empty(as));   // this accumulator may be overwritten
     }
@@ -525,12 +554,12 @@ int launch_add_splits(const float* ws, float* out, uint64_t m, uint64_t n, uint3
 // m*n to be a multiple of 4 for the vectorised sum of the partial products.
 // Stream mode: the tiles whose slabs were shared between teams are summed from their slots,
 // in ascending team order (a fixed order).  Tiles that one CTA computed whole are in `out` already.
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restrict__ slots, float* __restrict__ out,
                                                             uint64_t m, uint64_t n, uint32_t tiles_m, uint32_t tiles_n,
                                                             uint32_t num_kb, uint32_t share, uint32_t teams,
                                                             int epilogue) {
-  constexpr uint32_t kVecsPerTile = BM * BN / 4;
+  constexpr uint32_t kVecsPerTile = BM * MT * BN / 4;
   constexpr uint32_t kBlocksPerTile = kVecsPerTile / 256;
   const uint32_t tile = blockIdx.x / kBlocksPerTile;
   const uint32_t v = (blockIdx.x % kBlocksPerTile) * 256 + threadIdx.x;
@@ -539,7 +568,7 @@ __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restr
   const uint32_t t_last = (uint32_t)((((uint64_t)col_tile + 1) * num_kb - 1) / share);
   if (t_first == t_last) return;
   int m0, n0;
-  tile_coords(tile, tiles_m, tiles_n, BN, &m0, &n0);
+  tile_coords(tile, tiles_m, tiles_n, BN, &m0, &n0, BM * MT);
   const uint32_t r = v / (BN / 4), c = (v % (BN / 4)) * 4;
   const uint64_t row = (uint64_t)m0 + r, col = (uint64_t)n0 + c;
   if (row >= m || col >= n) return;
@@ -573,7 +602,7 @@ struct StreamPlan {
   uint32_t grid, share, teams;
   uint64_t bytes;
 };
-StreamPlan stream_plan(uint64_t tiles_m, uint64_t tiles_n, uint64_t num_kb, int bn) {
+StreamPlan stream_plan(uint64_t tiles_m, uint64_t tiles_n, uint64_t num_kb, int bn, int mt = 1) {
   const uint64_t sms = (uint64_t)sm_count();
   if (tiles_m == 0 || tiles_m > (uint64_t)kGroupM || tiles_m > sms) return StreamPlan{0, 0, 0, 0};
   const uint64_t total = tiles_n * num_kb;
@@ -582,10 +611,10 @@ StreamPlan stream_plan(uint64_t tiles_m, uint64_t tiles_n, uint64_t num_kb, int 
   const uint64_t share = (total + teams - 1) / teams;
   teams = (total + share - 1) / share;
   return StreamPlan{(uint32_t)(teams * tiles_m), (uint32_t)share, (uint32_t)teams,
-                    tiles_m * (teams + tiles_n) * (uint64_t)BM * (uint64_t)bn * sizeof(float)};
+                    tiles_m * (teams + tiles_n) * (uint64_t)(BM * mt) * (uint64_t)bn * sizeof(float)};
 }
 
-uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) {
+uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n, int mt = 1) {
   const uint64_t sms = (uint64_t)sm_count();
   if (tiles >= 8 * sms) return 1;
   // last wave at least 95 % full with whole tiles: nothing to gain from cutting k
@@ -596,7 +625,7 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) 
   // 0.730 ms at k = 8192, 1.317 vs 1.340 ms at 16384, 2.58 vs 2.60 ms at 32768, but 5.21 vs
   // 5.17 ms at 65536, where both balance equally well - so fixed cuts keep the long sums.
   if (num_kb <= 2048) {
-    const StreamPlan plan = stream_plan((m + BM - 1) / BM, (n + 255) / 256, num_kb, 256);
+    const StreamPlan plan = stream_plan((m + BM * mt - 1) / (BM * mt), (n + 255) / 256, num_kb, 256, mt);
     if (plan.teams && plan.share >= 64 && (double)plan.grid >= 0.95 * (double)sms) return 0;
   }
   if (((m * n) & 3) != 0) return 1;
@@ -612,17 +641,17 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n) 
   return best;
 }
 
-template <int BN, int BK>
+template <int BN, int BK, int MT = 1>
 static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                       const float* right, float* out, int passes, int write_hi, float* ws, uint32_t splits,
                       int epilogue, cudaStream_t stream, uint64_t left_pitch) {
-  using C = Cfg<BN, BK>;
+  using C = Cfg<BN, BK, MT>;
   static_assert(C::kStages >= 2 && C::kSmemBytes <= 227 * 1024, "stage ring must fit shared memory");
   int dev = 0;
   cudaGetDevice(&dev);
   static bool attr_done[64] = {false};
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fmatmul_tc_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fmatmul_tc_kernel<BN, BK, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)C::kSmemBytes);
     if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(smem)", e);
     attr_done[dev] = true;
@@ -642,14 +671,14 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   p.a_mn_major = tl ? 1 : 0;
   p.b_mn_major = tr ? 0 : 1;
   p.passes = passes; p.write_hi = write_hi; p.status = g_status_dev;
-  uint64_t tm = (m + BM - 1) / BM, tn = (n + BN - 1) / BN;
+  uint64_t tm = (m + BM * MT - 1) / (BM * MT), tn = (n + BN - 1) / BN;
   if (tm * tn > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   p.tiles_m = (uint32_t)tm; p.tiles_n = (uint32_t)tn;
   const uint64_t num_kb = (k + BK - 1) / BK;
   p.share = 0;
   p.slots = nullptr;
   p.teams = 0;
-  const StreamPlan plan = (splits == 0 && ws) ? stream_plan(tm, tn, num_kb, BN) : StreamPlan{0, 0, 0, 0};
+  const StreamPlan plan = (splits == 0 && ws) ? stream_plan(tm, tn, num_kb, BN, MT) : StreamPlan{0, 0, 0, 0};
   if (plan.teams) {
     // stream mode: equal shares of all slabs, partial tiles through slots, then one summing pass
     p.splits = 1;
@@ -658,11 +687,11 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
     p.share = plan.share;
     p.teams = plan.teams;
     p.slots = ws;
-    fmatmul_tc_kernel<BN, BK><<<plan.grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+    fmatmul_tc_kernel<BN, BK, MT><<<plan.grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
     rc = check_launch("fmatmul_tc");
     if (rc) return rc;
-    constexpr uint32_t kBlocksPerTile = BM * BN / 4 / 256;
-    stream_reduce_kernel<BN><<<(unsigned)(tm * tn * kBlocksPerTile), 256, 0, stream>>>(
+    constexpr uint32_t kBlocksPerTile = BM * MT * BN / 4 / 256;
+    stream_reduce_kernel<BN, MT><<<(unsigned)(tm * tn * kBlocksPerTile), 256, 0, stream>>>(
         ws, out, m, n, p.tiles_m, p.tiles_n, (uint32_t)num_kb, plan.share, plan.teams, epilogue);
     return check_launch("fmatmul_stream_reduce");
   }
@@ -673,7 +702,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   uint64_t units = tm * tn * splits;
   if (units > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   unsigned grid = (unsigned)(units < (uint64_t)sm_count() ? units : (uint64_t)sm_count());   // one CTA per SM
-  fmatmul_tc_kernel<BN, BK><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
+  fmatmul_tc_kernel<BN, BK, MT><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
   rc = check_launch("fmatmul_tc");
   if (rc || splits == 1) return rc;
   const uint64_t nvec = m * n / 4;
@@ -686,7 +715,9 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
 
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch) {
+              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch, int mt) {
+  if (mt == 2)   // 256 x 256 tiles, 16-float slabs
+    return tc::launch_cfg<256, 16, 2>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
   if (bn == 128 && bk == 32)
     return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
   if (bn == 128)
@@ -697,13 +728,16 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
 }
 
 // Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.
-uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k) {
-  return tc::choose_splits(((m + 127) / 128) * ((n + 255) / 256), (k + 15) / 16, m, n);
+// mt = row sub-tiles per CTA tile: 1 (128 x 256 tiles) or 2 (256 x 256).
+uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k, int mt) {
+  const uint64_t rows = 128ull * mt;
+  return tc::choose_splits(((m + rows - 1) / rows) * ((n + 255) / 256), (k + 15) / 16, m, n, mt);
 }
 
 // Scratch the default configuration needs for `splits` (0 = stream mode) work units per tile.
-uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits) {
-  if (splits == 0) return tc::stream_plan((m + 127) / 128, (n + 255) / 256, (k + 15) / 16, 256).bytes;
+uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits, int mt) {
+  const uint64_t rows = 128ull * mt;
+  if (splits == 0) return tc::stream_plan((m + rows - 1) / rows, (n + 255) / 256, (k + 15) / 16, 256, mt).bytes;
   return splits > 1 ? (uint64_t)splits * m * n * sizeof(float) : 0;
 }
 

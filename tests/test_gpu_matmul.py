@@ -77,8 +77,8 @@ def test_tensor_core_path(gpu, par_oracle, tl, tr, shape):
     rng = np.random.default_rng(m * 7 + n * 3 + k + tl * 2 + tr)
     l, r = operands(rng, tl, tr, m, n, k)
     ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
-    for tile_n in (256, 128):
-        for slab_k in (16, 32):
+    for tile_n in (256, 128, 512):          # 512: the 256 x 256 tile configuration
+        for slab_k in ((16,) if tile_n == 512 else (16, 32)):
             got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k)
             err = rel_err(got, ref, mag)
             assert err <= TOL, (tile_n, slab_k, err)
@@ -104,11 +104,11 @@ def test_k_cut_into_work_units_and_stream_mode(gpu, par_oracle, tl, tr, shape):
     for splits in (-1, 2, 3, 8):
         if splits > 1 and ((m * n) & 3 or (k + 15) // 16 < splits):
             continue
-        for slab_k in ((16, 32) if splits == -1 else (16,)):
-            got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=256, slab_k=slab_k, splits=splits)
-            assert rel_err(got, ref, mag) <= 5e-6, (splits, slab_k)
-            again = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=256, slab_k=slab_k, splits=splits)
-            assert np.array_equal(got.view(np.uint32), again.view(np.uint32)), (splits, slab_k)
+        for tile_n, slab_k in (((256, 16), (256, 32), (512, 16)) if splits == -1 else ((256, 16), (512, 16))):
+            got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k, splits=splits)
+            assert rel_err(got, ref, mag) <= 5e-6, (splits, tile_n, slab_k)
+            again = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k, splits=splits)
+            assert np.array_equal(got.view(np.uint32), again.view(np.uint32)), (splits, tile_n, slab_k)
     assert gpu.d.device_status() == 0
 
 
