@@ -86,15 +86,28 @@ uint64_t ragged_rows(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const f
 }
 
 // Row sub-tiles per CTA tile for the tensor-core path: 256 x 256 tiles (2) fetch a third fewer
-// operand bytes per flop than 128 x 256 (1) and are 12-50 % faster (8192^3: 283 vs 241 TFLOP/s,
-// t_f 273 vs 183), but pad m to a multiple of 256 and cannot overlap a tile's epilogue with the
-// next tile's k loop (both accumulators belong to one tile): taken when the padding adds at
-// most 10 % of rows and the k loop is long enough to dwarf the epilogue (with k = 784 and the
-// sigmoid in the epilogue the MLP's first layer takes 2.29 ms instead of 1.95 ms).
-int tc_tile_rows(uint64_t m, uint64_t k) {
-  if (m < 256 || k < 2048) return 1;
-  const uint64_t pad1 = (m + 127) / 128 * 128, pad2 = (m + 255) / 256 * 256;
-  return pad2 * 10 <= pad1 * 11 ? 2 : 1;
+// operand bytes per flop than 128 x 256 (1) and are 12-50 % faster on long sums (8192^3: 285
+// vs 242 TFLOP/s, t_f 275 vs 180), but pad m to a multiple of 256, cannot overlap a tile's
+// epilogue with the next tile's k loop (both accumulators belong to one tile), and make half
+// as many tiles, which matters when those fill the last wave badly and k is too short to cut.
+// The choice compares padded rows x relative cost per row / wave efficiency of both.
+int tc_tile_rows(uint64_t m, uint64_t n, uint64_t k) {
+  if (m < 256 || k < 512) return 1;
+  const double sms = (double)sm_count();
+  double est[3] = {0, 0, 0};
+  for (int mt = 1; mt <= 2; ++mt) {
+    const uint64_t rows = 128ull * mt;
+    const uint64_t tiles_m = (m + rows - 1) / rows, tiles = tiles_m * ((n + 255) / 256);
+    double eff = 1.0;
+    if (k < 2048 && (double)tiles < 8 * sms) {          // too short to cut: whole waves of tiles
+      const double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
+      eff = (double)tiles / (waves * sms);
+    }
+    // measured: 0.67-0.85 of the 128-row cost from k = 16384 up, 0.9-0.93 at k = 784 ... 8192
+    const double cost = mt == 1 ? 1.0 : (k < 16384 ? 0.9 : 0.75);
+    est[mt] = (double)(tiles_m * rows) * cost / eff;
+  }
+  return est[2] < est[1] ? 2 : 1;
 }
 
 int check_mm(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -125,7 +138,7 @@ static uint64_t workspace_need(int tl, int tr, uint64_t m, uint64_t n, uint64_t 
   if (choose_path(tl, tr, m, n, k, al, al, al) == kPathTc) {
     const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, fused == 1 ? 1 : 0);
     const uint64_t mm = m - rem;
-    const int mt = tc_tile_rows(mm, k);
+    const int mt = tc_tile_rows(mm, n, k);
     uint64_t need = tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt);
     if (rem) {
       const uint64_t r = ragged_rows_workspace_bytes(rem, n, k);
@@ -187,14 +200,14 @@ static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, cons
     case kPathTc: {
       const uint64_t rem = ragged_rows(tl, tr, m, n, k, right, fused);
       if (rem == 0) {
-        const int mt = tc_tile_rows(m, k);
+        const int mt = tc_tile_rows(m, n, k);
         return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k, mt), workspace,
                       workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0, 0, mt);
       }
       // whole tile rows on the tensor cores (left is stored [k, m]: the first m - rem columns
       // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel
       const uint64_t mm = m - rem;
-      const int mt = tc_tile_rows(mm, k);
+      const int mt = tc_tile_rows(mm, n, k);
       rc = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k, mt), workspace,
                   workspace_bytes, as_stream(stream), 0, m, mt);
       if (rc) return rc;

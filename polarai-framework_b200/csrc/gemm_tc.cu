@@ -202,7 +202,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full(a), 1);
-      mbar_init(acc_empty(a), kEpilogueWarps * 32);
+      mbar_init(acc_empty(a), (kEpilogueWarps + (MT == 2 ? kSplitWarps : 0)) * 32);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -215,6 +215,62 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  // Drains row sub-tiles [h0, h1) of the finished piece in accumulator buffer `as` for lane
+  // quarter q (a warp may only touch tensor-memory lanes [32*(warp%4), +32)) and one half of
+  // the columns: to the result, to the piece's partial-product buffer, or to its slot.
+  const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
+  auto drain = [&](const Piece& pc, uint32_t as, int h0, int h1, int q, int half) {
+      int m0, n0;
+      tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
+      const bool to_slot = p.share != 0 && pc.slot != kNoSlot;
+      float* const out_base = to_slot ? nullptr
+                              : (p.splits > 1 ? p.partial + (uint64_t)pc.slot * p.m * p.n : p.out);
+      const bool final_piece = !to_slot && p.splits <= 1;      // this store is the result itself
+#pragma unroll 1
+      for (int h = h0; h < h1; ++h) {
+      const uint32_t tile_row = (uint32_t)(h * BM + q * 32 + lane);
+      const uint64_t row = (uint64_t)m0 + tile_row;
+      const uint32_t tmem_acc = tmem_base + acc_col(as, h) + ((uint32_t)(q * 32) << 16);
+      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+        if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
+        tmem_ld_wait();
+        if (p.epilogue == 1 && final_piece) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sigmoid_clamped(__uint_as_float(r[j])));
+        }
+        if (p.write_hi == 2) {
+          // diagnostic: the accumulator is drained but nothing is stored
+        } else if (to_slot) {
+          // a whole tile per slot, padding rows and columns included (they hold zeros)
+          float* dst = p.slots + ((uint64_t)pc.slot * kTileM + tile_row) * BN + c;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                        __uint_as_float(r[j + 3])};
+            *reinterpret_cast<float4*>(dst + j) = v;
+          }
+        } else if (row < p.m) {
+          float* dst = out_base + row * p.n + n0 + c;
+          if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                          __uint_as_float(r[j + 3])};
+              *reinterpret_cast<float4*>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if ((uint64_t)n0 + c + j < p.n) dst[j] = __uint_as_float(r[j]);
+          }
+        }
+      }
+      }   // row sub-tiles
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -340,13 +396,13 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else if (warp < 2 + kSplitWarps) {
     // ---------------- split warps ----------------
     const int tid = threadIdx.x - 64;  // 0..255
-    if (p.passes == 3) {
-      uint32_t it = 0;
+    if (p.passes == 3 || MT == 2) {
+      uint32_t it = 0, tile_iter = 0;
       bool ok = true;
       PieceWalk walk(p, num_kb);
       Piece pc;
-      while (ok && walk.next(pc)) {
-        for (uint32_t kb = pc.kb0, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
+      for (; ok && walk.next(pc); ++tile_iter) {
+        for (uint32_t kb = pc.kb0, kb_end = pc.kb1; p.passes == 3 && kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) { ok = false; break; }
@@ -370,73 +426,33 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           fence_async_smem();
           mbar_arrive(full_lo(s));
         }
+        if (MT == 2 && ok) {
+          // 256-row tiles: nothing is left to split until this tile is drained, so these
+          // warps drain its lower sub-tile while the epilogue warps drain the upper one
+          if (!mbar_wait(acc_full(0), tile_iter & 1u, abort_flag, p.status, 107)) break;
+          tc_fence_after();
+          drain(pc, 0, 1, 2, warp & 3, (warp - 2) >> 2);
+          tc_fence_before();
+          mbar_arrive(acc_empty(0));
+        }
       }
     }
   } else {
     // ---------------- epilogue warps ----------------
-    // Warp w may touch tensor-memory lanes [32*(w%4), 32*(w%4)+32): four
-    // consecutive warps cover the 128 rows of the tile; the two warps of a lane
-    // quarter take half of the columns each.
+    // Four consecutive warps cover the 128 rows of a sub-tile; the two warps of a lane quarter
+    // take half of the columns each.  With 256-row tiles these warps drain the upper sub-tile
+    // and the split warps, idle at that point, the lower one.
     const int q = warp & 3;
     const int half = (warp - (2 + kSplitWarps)) >> 2;
-    const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
     uint32_t tile_iter = 0;
     PieceWalk walk(p, num_kb);
     Piece pc;
     for (; walk.next(pc); ++tile_iter) {
-      int m0, n0;
-      tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
-      const bool to_slot = p.share != 0 && pc.slot != kNoSlot;
-      float* const out_base = to_slot ? nullptr
-                              : (p.splits > 1 ? p.partial + (uint64_t)pc.slot * p.m * p.n : p.out);
-      const bool final_piece = !to_slot && p.splits <= 1;      // this store is the result itself
       const uint32_t as = MT == 1 ? (tile_iter & 1u) : 0u;
       const uint32_t use = MT == 1 ? (tile_iter >> 1) : tile_iter;
       if (!mbar_wait(acc_full(as), use & 1u, abort_flag, p.status, 105)) break;
       tc_fence_after();
-#pragma unroll 1
-      for (int h = 0; h < MT; ++h) {
-      const uint32_t tile_row = (uint32_t)(h * BM + q * 32 + lane);
-      const uint64_t row = (uint64_t)m0 + tile_row;
-      const uint32_t tmem_acc = tmem_base + acc_col(as, h) + ((uint32_t)(q * 32) << 16);
-      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-        if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
-        tmem_ld_wait();
-        if (p.epilogue == 1 && final_piece) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sigmoid_clamped(__uint_as_float(r[j])));
-        }
-        if (p.write_hi == 2) {
-          // diagnostic: the accumulator is drained but nothing is stored
-        } else if (to_slot) {
-          // a whole tile per slot, padding rows and columns included (they hold zeros)
-          float* dst = p.slots + ((uint64_t)pc.slot * kTileM + tile_row) * BN + c;
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                        __uint_as_float(r[j + 3])};
-            *reinterpret_cast<float4*>(dst + j) = v;
-          }
-        } else if (row < p.m) {
-          float* dst = out_base + row * p.n + n0 + c;
-          if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                          __uint_as_float(r[j + 3])};
-              *reinterpret_cast<float4*>(dst + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if ((uint64_t)n0 + c + j < p.n) dst[j] = __uint_as_float(r[j]);
-          }
-        }
-      }
-      }   // row sub-tiles
+      drain(pc, as, 0, 1, q, half);
       tc_fence_before();
       mbar_arrive(acc_empty(as));   // this accumulator may be overwritten
     }
