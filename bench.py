@@ -430,9 +430,9 @@ def run_mlp(args):
                 "launches_per_step": len(tc_ops), "avg_launch_ms": tc_ms / max(1, len(tc_ops)),
                 "share_of_step": tc_ms / total_ops_ms if total_ops_ms else None,
                 # dram__bytes_read + write per launch from the ncu capture at batch 8192
-                # (summarised under profiles/: 117.5 MB and 262.6 MB for the two launches),
+                # (summarised under profiles/: 118.4 MB and 174.3 MB for the two launches),
                 # scaled by rows: traffic grows in proportion with the batch.
-                "traffic": per * (117.5e6 + 262.6e6) / 2.0 / 8192.0,
+                "traffic": per * (118.4e6 + 174.3e6) / 2.0 / 8192.0,
                 "traffic_note": "ncu capture at batch 8192 scaled by rows; algorithmic 4(mk+kn+mn) is "
                                 f"{4.0 * (per * N_IN + N_IN * N_HIDDEN + per * N_HIDDEN):.3e} bytes per launch"}
 
