@@ -9,7 +9,10 @@
 // the truncation of x_lo to TF32 are each below 2^-21 relative to |a||b|.
 //
 // One persistent CTA per SM walks 128 x BN output tiles; two accumulators in
-// tensor memory let the epilogue of one tile overlap the k loop of the next.
+// tensor memory let the epilogue of one tile overlap the k loop of the next.  In
+// the 256 x BN configuration (MT = 2, see Cfg) both accumulators belong to one
+// tile and every B slab serves two row sub-tiles: a third fewer operand bytes per
+// flop, which is what limits the 128-row form (24 KB per slab per SM from L2).
 // Warp roles:
 //   warp 0     TMA producer: cp.async.bulk.tensor loads of the fp32 A and B
 //              slabs into 128-byte-swizzled shared memory (plain per-CTA loads:
