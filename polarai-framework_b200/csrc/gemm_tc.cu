@@ -50,6 +50,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tc_plan.hpp"
 #include "tc_ptx.cuh"
 
 namespace polar_b200 {
@@ -59,7 +60,7 @@ constexpr int BM = 128;
 constexpr int kSplitWarps = 8;                                  // warps 2..9
 constexpr int kEpilogueWarps = 8;                               // warps 10..17
 constexpr int kThreads = 32 * (2 + kSplitWarps + kEpilogueWarps);
-constexpr int kGroupM = 16;                                     // tile raster: 16 row tiles share their column tiles
+constexpr int kGroupM = kPlanGroupM;                            // tile raster: 16 row tiles share their column tiles
 
 // BN: tile width (256 or 128).  BK: floats per k slab (32 -> 128-byte rows, 16 ->
 // 64-byte rows); a shallower slab halves the stage and doubles the pipeline depth.
@@ -94,66 +95,11 @@ struct Params {
   int epilogue;     // 0: store the product; 1: store fsigmoid(product) (only when splits == 1)
   uint32_t splits;  // work units per tile: the k range is cut into `splits` parts
   float* partial;   // [splits][m][n] partial products when splits > 1
-  // Stream mode (share > 0): CTAs form teams of tiles_m, one CTA per row tile.  The teams cut
-  // the sequence (column tile 0, all its k slabs), (column tile 1, ...), ... into equal shares;
-  // a share may end inside a column and the next team continues it.  The CTAs of a team work
-  // on the same column and the same k at the same time, so they share the column's operand
-  // panel in L2.  A piece that is not a whole tile goes to a slot of `slots`,
-  // [row][team + column][128][BN] floats.
+  // Stream mode (share > 0; see PieceWalk in tc_plan.hpp): partial tiles go to `slots`,
+  // [slot][tile rows][BN] floats.
   uint32_t share;   // slabs per team
   uint32_t teams;
   float* slots;
-};
-
-constexpr uint32_t kNoSlot = 0xffffffffu;
-
-// One piece of work: slabs [kb0, kb1) of a tile.  Every warp role walks the same sequence.
-struct Piece {
-  uint32_t tile, kb0, kb1, slot;
-};
-
-struct PieceWalk {
-  uint32_t num_kb, splits, num_units, unit, stride;
-  uint32_t row, team, tiles_m, slot_base;
-  uint64_t g, g_end;
-  bool stream;
-  __device__ __forceinline__ PieceWalk(const Params& p, uint32_t nkb) {
-    num_kb = nkb;
-    splits = p.splits;
-    num_units = p.tiles_m * p.tiles_n * p.splits;
-    unit = blockIdx.x;
-    stride = gridDim.x;
-    stream = p.share != 0;
-    tiles_m = p.tiles_m;
-    row = blockIdx.x % p.tiles_m;
-    team = blockIdx.x / p.tiles_m;
-    slot_base = row * (p.teams + p.tiles_n) + team;
-    const uint64_t total = (uint64_t)p.tiles_n * nkb;
-    g = (uint64_t)team * p.share;
-    g_end = g + p.share < total ? g + p.share : total;
-    if (team >= p.teams) g = g_end = 0;
-  }
-  __device__ __forceinline__ bool next(Piece& pc) {
-    if (!stream) {
-      if (unit >= num_units) return false;
-      const uint32_t sp = unit % splits;
-      pc.tile = unit / splits;
-      pc.kb0 = (uint32_t)(((uint64_t)sp * num_kb) / splits);
-      pc.kb1 = (uint32_t)(((uint64_t)(sp + 1) * num_kb) / splits);
-      pc.slot = splits > 1 ? sp : kNoSlot;
-      unit += stride;
-      return true;
-    }
-    if (g >= g_end) return false;
-    const uint32_t col = (uint32_t)(g / num_kb);
-    pc.tile = col * tiles_m + row;        // tile_coords' raster when tiles_m <= kGroupM
-    pc.kb0 = (uint32_t)(g % num_kb);
-    const uint64_t left = g_end - g;
-    pc.kb1 = (uint64_t)pc.kb0 + left < num_kb ? (uint32_t)(pc.kb0 + left) : num_kb;
-    pc.slot = (pc.kb0 == 0 && pc.kb1 == num_kb) ? kNoSlot : slot_base + col;
-    g += pc.kb1 - pc.kb0;
-    return true;
-  }
 };
 
 // Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
@@ -196,6 +142,9 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t num_kb = (uint32_t)((p.k + BK - 1) / BK);
   // Work comes in pieces (PieceWalk): a (tile, split) unit with a fixed share of the k slabs,
   // or, in stream mode, whatever part of a tile falls into this CTA's share of all slabs.
+  auto make_walk = [&]() {
+    return PieceWalk(p.tiles_m, p.tiles_n, p.splits, p.share, p.teams, num_kb, blockIdx.x, gridDim.x);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -280,7 +229,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;   // k slabs issued so far, over all tiles of this CTA
       bool ok = true;
-      PieceWalk walk(p, num_kb);
+      PieceWalk walk = make_walk();
       Piece pc;
       while (ok && walk.next(pc)) {
         int m0, n0;
@@ -327,7 +276,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t b_sbo = p.b_mn_major ? 512u : kRowGroup, b_lt = p.b_mn_major ? 1u : kKMajorLayout;
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      PieceWalk walk(p, num_kb);
+      PieceWalk walk = make_walk();
       Piece pc;
       for (; ok && walk.next(pc); ++tile_iter) {
         // MT = 1: the two accumulators alternate, the epilogue must have drained this one (two
@@ -402,7 +351,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (p.passes == 3 || MT == 2) {
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      PieceWalk walk(p, num_kb);
+      PieceWalk walk = make_walk();
       Piece pc;
       for (; ok && walk.next(pc); ++tile_iter) {
         for (uint32_t kb = pc.kb0, kb_end = pc.kb1; p.passes == 3 && kb < kb_end; ++kb, ++it) {
@@ -448,7 +397,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int q = warp & 3;
     const int half = (warp - (2 + kSplitWarps)) >> 2;
     uint32_t tile_iter = 0;
-    PieceWalk walk(p, num_kb);
+    PieceWalk walk = make_walk();
     Piece pc;
     for (; walk.next(pc); ++tile_iter) {
       const uint32_t as = MT == 1 ? (tile_iter & 1u) : 0u;
@@ -583,8 +532,8 @@ __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restr
   const uint32_t tile = blockIdx.x / kBlocksPerTile;
   const uint32_t v = (blockIdx.x % kBlocksPerTile) * 256 + threadIdx.x;
   const uint32_t trow = tile % tiles_m, col_tile = tile / tiles_m;
-  const uint32_t t_first = (uint32_t)(((uint64_t)col_tile * num_kb) / share);
-  const uint32_t t_last = (uint32_t)((((uint64_t)col_tile + 1) * num_kb - 1) / share);
+  uint32_t t_first, t_last;
+  stream_teams_of_column(col_tile, num_kb, share, &t_first, &t_last);
   if (t_first == t_last) return;
   int m0, n0;
   tile_coords(tile, tiles_m, tiles_n, BN, &m0, &n0, BM * MT);
@@ -614,25 +563,6 @@ __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restr
   }
 }
 
-// Stream mode geometry: teams of tiles_m CTAs, slabs per team, CTAs in all, scratch.
-// teams == 0: the shape does not suit the mode (more row tiles than the raster's group, or
-// than SMs).
-struct StreamPlan {
-  uint32_t grid, share, teams;
-  uint64_t bytes;
-};
-StreamPlan stream_plan(uint64_t tiles_m, uint64_t tiles_n, uint64_t num_kb, int bn, int mt = 1) {
-  const uint64_t sms = (uint64_t)sm_count();
-  if (tiles_m == 0 || tiles_m > (uint64_t)kGroupM || tiles_m > sms) return StreamPlan{0, 0, 0, 0};
-  const uint64_t total = tiles_n * num_kb;
-  uint64_t teams = sms / tiles_m;
-  if (teams > total) teams = total;
-  const uint64_t share = (total + teams - 1) / teams;
-  teams = (total + share - 1) / share;
-  return StreamPlan{(uint32_t)(teams * tiles_m), (uint32_t)share, (uint32_t)teams,
-                    tiles_m * (teams + tiles_n) * (uint64_t)(BM * mt) * (uint64_t)bn * sizeof(float)};
-}
-
 uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n, int mt = 1) {
   const uint64_t sms = (uint64_t)sm_count();
   if (tiles >= 8 * sms) return 1;
@@ -644,7 +574,7 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n, 
   // 0.730 ms at k = 8192, 1.317 vs 1.340 ms at 16384, 2.58 vs 2.60 ms at 32768, but 5.21 vs
   // 5.17 ms at 65536, where both balance equally well - so fixed cuts keep the long sums.
   if (num_kb <= 2048) {
-    const StreamPlan plan = stream_plan((m + BM * mt - 1) / (BM * mt), (n + 255) / 256, num_kb, 256, mt);
+    const StreamPlan plan = stream_plan((m + BM * mt - 1) / (BM * mt), (n + 255) / 256, num_kb, 256, mt, sms);
     if (plan.teams && plan.share >= 64 && (double)plan.grid >= 0.95 * (double)sms) return 0;
   }
   if (((m * n) & 3) != 0) return 1;
@@ -697,7 +627,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   p.share = 0;
   p.slots = nullptr;
   p.teams = 0;
-  const StreamPlan plan = (splits == 0 && ws) ? stream_plan(tm, tn, num_kb, BN, MT) : StreamPlan{0, 0, 0, 0};
+  const StreamPlan plan = (splits == 0 && ws) ? stream_plan(tm, tn, num_kb, BN, MT, (uint64_t)sm_count()) : StreamPlan{0, 0, 0, 0};
   if (plan.teams) {
     // stream mode: equal shares of all slabs, partial tiles through slots, then one summing pass
     p.splits = 1;
@@ -756,7 +686,7 @@ uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k, int mt) {
 // Scratch the default configuration needs for `splits` (0 = stream mode) work units per tile.
 uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits, int mt) {
   const uint64_t rows = 128ull * mt;
-  if (splits == 0) return tc::stream_plan((m + rows - 1) / rows, (n + 255) / 256, (k + 15) / 16, 256, mt).bytes;
+  if (splits == 0) return tc::stream_plan((m + rows - 1) / rows, (n + 255) / 256, (k + 15) / 16, 256, mt, (uint64_t)sm_count()).bytes;
   return splits > 1 ? (uint64_t)splits * m * n * sizeof(float) : 0;
 }
 
