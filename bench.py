@@ -2,14 +2,18 @@
 """Benchmark of the PolarAI B200 runtime's hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload mlp|gemm|elementwise] [--no-graph] [--no-extras]
+                    [--workload mlp|gemm|elementwise] [--builtins extended|reference]
+                    [--collective peer|nccl] [--batch B] [--no-graph] [--no-extras]
 
 Default workload (the one that shards over 1/2/4/8 GPUs): one training step of the
 2-layer MLP 784-4096-10 (Sigmoid hidden layer, LogLoss on one-hot targets, fp32,
-global batch 65536 batch-sharded over the ranks, gradient all-reduce over NCCL,
-SGD update at lr = 0.1), expressed as the reference's builtins
-(polarai-framework_b200/program.py).  Data is synthetic: X ~ N(0,1), uniform
-labels, Xavier-uniform weights, seed 0.
+global batch 65536 batch-sharded over the ranks, sum of the weight gradients over
+the ranks, SGD update at lr = 0.1), expressed as the reference's builtins
+(polarai-framework_b200/program.py) - by default with the extended (fused)
+builtins, whose outputs are bit-identical to the one-launch-per-builtin chain, and
+at N > 1 with the gradient sum and the update as one kernel over NVLink peer memory
+(--collective nccl: NCCL all-reduces followed by fadd).  Data is synthetic:
+X ~ N(0,1), uniform labels, Xavier-uniform weights, seed 0.
 
 One JSON line is printed by rank 0.  `value` is samples/s with the inputs already
 in HBM; `e2e` is samples/s when every step also copies its X and Y shard from
