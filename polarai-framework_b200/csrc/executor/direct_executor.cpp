@@ -336,6 +336,44 @@ public:
     mGraphs[graph.getName().getString()] = recorder.graph;
     if (mDebug && recorder.graph)
       std::clog << "Recorded graph " << recorder.graph->name << ": " << recorder.graph->steps.size() << " steps\n";
+    if (recorder.graph && std::getenv("POLAR_B200_DUMP_PROGRAM")) dump(*recorder.graph);
+  }
+
+  // The recorded program as text, one line per runtime call, in the order evaluate() issues
+  // them (POLAR_B200_DUMP_PROGRAM=1): what the reference's lowering to its runtime dialect
+  // would contain for the same graph (utils/dialects/test/conversion/graph_to_runtime.mlir).
+  static void dump(const GraphRecord& g) {
+    std::printf("program %s\n", g.name.c_str());
+    for (const auto& step : g.steps) {
+      if (step.kind == Step::BARRIER) {
+        std::printf("  barrier cluster=%llu\n", (unsigned long long)step.clusterId);
+        continue;
+      }
+      const NodeRecord& n = *step.node;
+      std::printf("  node %s id=%zu cluster=%zu\n", n.name.c_str(), n.nodeId, n.clusterId);
+      for (const auto& c : n.commands) {
+        switch (c.kind) {
+          case Command::ALLOC: std::printf("    alloc va=%llu\n", (unsigned long long)c.tensor.virtAddr); break;
+          case Command::LOCK:
+            std::printf("    lock %s va=%llu\n", c.lockType == LockType::READ ? "read" : "read_write",
+                        (unsigned long long)c.tensor.virtAddr);
+            break;
+          case Command::RELEASE: std::printf("    release va=%llu\n", (unsigned long long)c.tensor.virtAddr); break;
+          case Command::LOAD: std::printf("    load va=%llu\n", (unsigned long long)c.tensor.virtAddr); break;
+          case Command::LAUNCH: {
+            std::printf("    launch %s", c.nativeName.c_str());
+            for (const auto& v : c.args) {
+              if (v.isTensor) std::printf(" T%llu", (unsigned long long)v.tensor.virtAddr);
+              else if (v.isInteger) std::printf(" i%lld", (long long)v.integer);
+              else std::printf(" f%g", v.scalar);
+            }
+            std::printf("\n");
+            break;
+          }
+        }
+      }
+    }
+    std::fflush(stdout);
   }
 
   void evaluate(Graph& graph) {

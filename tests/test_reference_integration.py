@@ -108,3 +108,48 @@ def test_pool_backend_allocator_host_logic():
     out = subprocess.run([ALLOC_TEST], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "4 ran, 0 failed, 0 skipped" in out.stdout
+
+
+@pytest.mark.skipif(not os.path.exists(PARITY), reason="autograd parity binary is not built")
+def test_recorded_program_has_the_call_sequence_the_reference_lowering_pins():
+    # The reference pins, per node, the order of runtime calls its graph lowering emits
+    # (utils/dialects/test/conversion/graph_to_runtime.mlir:52-110): an input node is
+    # alloc, lock read_write, invoke_loader, release; an operation node is alloc(out),
+    # lock read_write(out), lock read per operand, the launch with arguments in builtin order,
+    # release per operand, release(out); a barrier closes each cluster.  The Executor of this
+    # package replays exactly that, recorded through the reference's own Generator.
+    env = dict(os.environ, POLAR_B200_DUMP_PROGRAM="1")
+    out = subprocess.run([PARITY, "1"], capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stdout + out.stderr
+    text = out.stdout
+    first = text[text.index("program logreg\n"):text.index("program GradientGraph")]
+    lines = [l.strip() for l in first.splitlines()[1:]]
+    nodes, cur = {}, None
+    order = []
+    for l in lines:
+        if l.startswith("node "):
+            cur = l.split()[1]
+            nodes[cur] = []
+            order.append(cur)
+        elif l.startswith("barrier"):
+            order.append(l)
+        else:
+            nodes[cur].append(l)
+    va = {n: nodes[n][0].split("va=")[1] for n in nodes}            # every node allocates its result first
+    for n in ("X", "W", "Y"):
+        assert nodes[n] == [f"alloc va={va[n]}", f"lock read_write va={va[n]}", f"load va={va[n]}",
+                            f"release va={va[n]}"], n
+    assert nodes["matmul"] == [f"alloc va={va['matmul']}", f"lock read_write va={va['matmul']}",
+                               f"lock read va={va['W']}", f"lock read va={va['X']}",
+                               f"launch fmatmul_f_f T{va['X']} T{va['W']} T{va['matmul']}",
+                               f"release va={va['W']}", f"release va={va['X']}", f"release va={va['matmul']}"]
+    assert nodes["sigmoid"][3] == f"launch fsigmoid T{va['matmul']} T{va['sigmoid']}"
+    # LogLoss: predicted first, ground truth second, whatever the edge marks' numbering
+    assert f"launch flogloss T{va['sigmoid']} T{va['Y']} T{va['logloss']}" in nodes["logloss"]
+    # clusters: the three inputs, then one operation per cluster, a barrier after each
+    assert order[:4] == ["X", "W", "Y", "barrier cluster=0"]
+    assert order[4:10] == ["matmul", "barrier cluster=1", "sigmoid", "barrier cluster=2", "logloss",
+                           "barrier cluster=3"]
+    # the gradient graph's constants are recorded as loads too (they become ffill at run time)
+    grad = text[text.index("program GradientGraph"):]
+    assert "launch fmulconcat" in grad and "launch fdivide" in grad and "launch fadd" in grad
