@@ -153,3 +153,6 @@ def test_recorded_program_has_the_call_sequence_the_reference_lowering_pins():
     # the gradient graph's constants are recorded as loads too (they become ffill at run time)
     grad = text[text.index("program GradientGraph"):]
     assert "launch fmulconcat" in grad and "launch fdivide" in grad and "launch fadd" in grad
+    # fadd's argument order: tensor, scale, tensor, scale, result (kernel_materialize.mlir:36,73)
+    fadd = next(l.split()[2:] for l in grad.splitlines() if l.strip().startswith("launch fadd"))
+    assert [t[0] for t in fadd] == ["T", "f", "T", "f", "T"], fadd
