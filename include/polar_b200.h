@@ -126,6 +126,23 @@ int polar_b200_fpool(const float* in, uint64_t h, uint64_t w, uint64_t windowH,
 int polar_b200_fconv2d(const float* in, uint64_t h, uint64_t w, const float* kernel,
                        uint64_t kh, uint64_t kw, float* out, void* stream);
 
+/* ftranspose: out[c,r] = in[r,c] for a 2-D tensor in[rows,cols], bit-exact; out is
+ * [cols,rows] and must not alias in.  Args: T in, T out.  The reference lists the builtin
+ * (include/polarai/core/internal/GenBuiltins.hpp:50 "Transpose 2D tensor (matrix)";
+ * PolarGraphOps.td:507-527, kernel name "ftranspose", body empty) but no operation emits it. */
+int polar_b200_ftranspose(const float* in, uint64_t rows, uint64_t cols, float* out,
+                          void* stream);
+
+/* fslice: out = in[index], the sub-tensor at offset `index` of the first dimension
+ * (GenBuiltins.hpp:49 "Get subtensor"; PolarGraphOps.td:134-144 "by first dimension
+ * offset": the result has the remaining dimensions), as a bit-exact copy of `inner` =
+ * product of the remaining extents floats.  As a builtin: T in, one 8-byte integer DATA
+ * argument (index), T out.  The reference's generator functor for Slice returns no value
+ * (GenBuiltins.hpp:147-149), so no graph can consume a slice there; here it is reachable
+ * by name. */
+int polar_b200_fslice(const float* in, uint64_t first_dim, uint64_t inner, uint64_t index,
+                      float* out, void* stream);
+
 /* ---- matmul -------------------------------------------------------------- */
 
 /* fmatmul_{f,t}_{f,t}: out[i,j] = sum_k L'[i,k]*R'[k,j] in fp32 accuracy.
@@ -208,21 +225,28 @@ int polar_b200_fmatmul_tc(int transLeft, int transRight, uint64_t m, uint64_t n,
                           float* out, int tile_n, int slab_k, int passes,
                           int write_hi, int splits, void* stream);
 
-/* The tensor-core path with PAIRS of CTAs (tcgen05 cta_group::2): two CTAs of a
- * cluster compute one 256 x 256 tile, each staging only its half of the operands.
- * Same product and accuracy as polar_b200_fmatmul_tc with passes = 3; exposed for
- * tests and benchmarks.  splits as above (1..64); fuse_sigmoid != 0 stores
- * fsigmoid(product). */
-int polar_b200_fmatmul_tc_pair(int transLeft, int transRight, uint64_t m, uint64_t n,
-                               uint64_t k, const float* left, const float* right,
-                               float* out, int splits, int fuse_sigmoid, void* stream);
-
-/* Status word the kernels write when a bounded device-side wait gives up
- * (0 = none; 101..106 and 201..206 = which wait of the tensor-core matmuls).  It lives in
- * pinned host memory, so reading it needs no CUDA call; read it after the
- * stream has been synchronised. */
+/* Bounded device-side waits.  Every wait inside a kernel of this library (mbarriers of the
+ * tensor-core matmuls; the ranks of the gradient exchange waiting for one another) gives
+ * up after a limit, records a code in the status word of its device and lets the kernel
+ * end, so a lost peer or a stuck pipeline never hangs the GPU.  The reference has no
+ * counterpart: its runtimes terminate the process on any error
+ * (src/backend/generic/runtime/cuda/utils.hpp:20-28).
+ *  - Codes: 0 = none; 101..107 = which wait of the tensor-core matmul; 301 = a peer's
+ *    gradients never became ready, 302 = a peer never finished its slice (in both cases no
+ *    weight was updated).  The first code recorded since the last clear stays.
+ *  - The words live in pinned host memory: reading them needs no CUDA call.  Read after
+ *    the stream has been synchronised.  polar_b200_device_status() gives the first
+ *    non-zero word of any device, _of(device) one device's word, _clear() clears all.
+ *  - polar_b200_check_device_status() turns a non-zero word into POLAR_B200_ERR_TIMEOUT
+ *    (text in polar_b200_last_error); POLAR_B200_OK otherwise.
+ *  - polar_b200_set_wait_limit_ns sets the limit for launches made afterwards (0 = the
+ *    defaults: 2 s in the matmuls, 4 s in the exchange). */
 int polar_b200_device_status(void);
+int polar_b200_device_status_of(int device);
 void polar_b200_device_status_clear(void);
+int polar_b200_check_device_status(void);
+void polar_b200_set_wait_limit_ns(uint64_t ns);
+uint64_t polar_b200_wait_limit_ns(void);
 
 /* Which matmul path polar_b200_fmatmul would take for these sizes:
  * 0 = tcgen05 tensor-core tiles, 1 = skinny (bandwidth-bound CUDA-core) path,
@@ -297,8 +321,9 @@ typedef struct polar_b200_arg {
 } polar_b200_arg;
 
 /* Native names: the twelve of the benchmarked path, "frelu", "fsoftmax", "fpool",
- * "fconv2d" (the reference's own table names ReLU, Softmax and Transpose all
- * "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own here), and
+ * "fconv2d", "ftranspose", "fslice" (the reference's own table names ReLU, Softmax and
+ * Transpose all "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own
+ * here), and
  * the extended "fsigmoid_grad", "fsigmoid_logloss_grad", "fmatmul_x_y_sigmoid",
  * "fmatmul_x_y_sigmoid_grad".
  *
@@ -348,9 +373,10 @@ typedef struct polar_b200_update_segment {
  *   weights[i] <- fl(fl(weights[i]*scale_w) + fl(payload[offset+i]*scale_g))  per segment
  * `buffers[r]` is rank r's peer buffer as mapped in THIS process (own buffer at
  * buffers[rank]); `n` is the payload length in floats.  The ranks' kernels wait for one
- * another with a bound of 4 s; a wait that gives up sets polar_b200_device_status() to
- * 301 (a peer's gradient never became ready) or 302 (a peer never finished its slice)
- * and the launch still terminates.  The launches that produced the payload must precede
+ * another with a bound of 4 s (polar_b200_set_wait_limit_ns); a wait that gives up sets
+ * the device's status word to 301 (a peer's gradient never became ready) or 302 (a peer
+ * never finished its slice), the launch still terminates and NO weight is updated on any
+ * rank.  The launch is cooperative (all its CTAs resident at once).  The launches that produced the payload must precede
  * this one on `stream`.  world == 1 is valid (no exchange, update only). */
 int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
                               const polar_b200_update_segment* segments, uint32_t n_segments,

@@ -40,7 +40,9 @@ struct LaunchCommand;
 
 typedef struct polar_b200_rt polar_b200_rt;
 
-/* initContext() + a BackendAllocator with every device registered. */
+/* initContext() + a BackendAllocator with every device registered.  Enumerates the GPUs
+ * without touching them: a GPU gets its context, streams and pool when it is first used.
+ * No function of this header changes the calling thread's current CUDA device. */
 polar_b200_rt* polar_b200_rt_open(void);
 /* Releases devices, pools and pinned host memory, then closeContext(). */
 void polar_b200_rt_close(polar_b200_rt* rt);
@@ -54,20 +56,32 @@ int polar_b200_rt_allocate(polar_b200_rt* rt, int device, uint64_t virtAddr, uin
 /* BackendAllocator::deallocate on every layer that holds the record. */
 int polar_b200_rt_deallocate(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes);
 
-/* What ath_load does with a MemcpyLoader: host READ_WRITE lock, copy `bytes`
- * from `src` into the record's host memory, release.  The device copy becomes
- * stale and is refreshed by the next device lock (one host-to-device copy). */
+/* What ath_load does with a MemcpyLoader (routines.cpp:95-105 of the reference; the
+ * loader copies into the pointer BackendAllocator::get returns): host write lock, copy
+ * `bytes` from `src` into the record's pinned host memory, release.  The whole record is
+ * replaced, so the call never waits for the previous version's upload: the record keeps
+ * two pinned buffers and fills the one no copy is reading.  On return `src` may be reused,
+ * and the upload to every device that holds the record has been STARTED on that device's
+ * upload stream, into a fresh block - it overlaps kernels that still read the previous
+ * version; the next launch that uses the record waits for it on the device, not on the host. */
 int polar_b200_rt_write(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes, const void* src);
-/* What OutputNodeAccessor does: host READ lock (pulls the newest copy to the
- * host: one device-to-host copy, after the device's stream has drained), copy
- * out, release. */
+/* The same without the copy, for a loader that produces its data in place (what
+ * AbstractLoaderInternal::load does with the pointer it gets): begin hands out the pinned
+ * host buffer to fill, end publishes it and starts the upload. */
+int polar_b200_rt_host_begin_write(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes, void** host);
+int polar_b200_rt_host_end_write(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes);
+/* What OutputNodeAccessor does: host READ lock (pulls the newest copy to the host: one
+ * device-to-host copy on the device's download stream, which waits for the launch that
+ * last wrote the record - not for launches queued after it), copy out, release. */
 int polar_b200_rt_read(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes, void* dst);
 
 /* One builtin: READ_WRITE lock on the last tensor argument, READ locks on the
  * others (as the operations' gen() methods emit), Device::launch, release.
  * The launch is asynchronous; errors of the launch itself are returned. */
 int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cmd);
-/* ath_barrier over everything launched on the device so far. */
+/* ath_barrier over everything launched on the device so far.  Returns
+ * POLAR_B200_ERR_TIMEOUT when a kernel's bounded wait gave up on that GPU since the last
+ * polar_b200_device_status_clear() (polar_b200_rt_read reports the same). */
 int polar_b200_rt_barrier(polar_b200_rt* rt, int device);
 
 /* Device pointer of a record on a device (NULL if absent), and the device's

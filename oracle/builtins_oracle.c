@@ -164,6 +164,24 @@ void oracle_fpool(const float* in, uint64_t h, uint64_t w, uint64_t wh, uint64_t
     }
 }
 
+/* ftranspose: out[c,r] = in[r,c] for a 2-D tensor, bit-exact.  The reference only names the
+ * builtin - include/polarai/core/internal/GenBuiltins.hpp:50 ("Transpose 2D tensor (matrix)"),
+ * utils/dialects/include/PolarGraph/PolarGraphOps.td:507-527 (kernel body empty) - and holds no
+ * test or vector for it: the restatement is the definition of a matrix transpose. */
+void oracle_ftranspose(const float* in, uint64_t rows, uint64_t cols, float* out) {
+  PAR_FOR
+  for (int64_t r = 0; r < (int64_t)rows; ++r)
+    for (uint64_t c = 0; c < cols; ++c) out[c * rows + (uint64_t)r] = in[(uint64_t)r * cols + c];
+}
+
+/* fslice: out = the sub-tensor at offset `index` of the first dimension, `inner` floats,
+ * bit-exact.  GenBuiltins.hpp:49 ("Get subtensor"); PolarGraphOps.td:134-144 ("Get sub-tensor
+ * by first dimension offset"); the result shape drops the first dimension
+ * (utils/dialects/lib/PolarGraph/PolarGraphOps.cpp:157-170).  No reference test or vector. */
+void oracle_fslice(const float* in, uint64_t inner, uint64_t index, float* out) {
+  for (uint64_t i = 0; i < inner; ++i) out[i] = in[index * inner + i];
+}
+
 /* fconv2d: single-channel "valid" cross-correlation with an odd-sized kernel;
  * out[i,j] = sum over kernel rows a, columns b (in that order) of in[i+a, j+b]*ker[a,b],
  * each product rounded, then added; the result is [h-kh+1, w-kw+1].

@@ -63,6 +63,8 @@ class Oracle:
         L.oracle_fsoftmax.argtypes = [_F, _F, u]
         L.oracle_fpool.argtypes = [_F, u, u, u, u, u, u, _F]
         L.oracle_fconv2d.argtypes = [_F, u, u, _F, u, u, _F]
+        L.oracle_ftranspose.argtypes = [_F, u, u, _F]
+        L.oracle_fslice.argtypes = [_F, u, u, _F]
         L.oracle_fmatmul.argtypes = [ctypes.c_int, ctypes.c_int, u, u, u, _F, _F, _F]
         L.oracle_fmatmul_f64.argtypes = [ctypes.c_int, ctypes.c_int, u, u, u, _F, _F, _D, _D]
         L.oracle_fmatmul_entries_f64.argtypes = [ctypes.c_int, ctypes.c_int, u, u, u, _F, _F,
@@ -140,6 +142,19 @@ class Oracle:
         h, w = a.shape
         out = np.empty(((h - window[0]) // stride[0] + 1, (w - window[1]) // stride[1] + 1), np.float32)
         self.lib.oracle_fpool(_p(a), h, w, window[0], window[1], stride[0], stride[1], _p(out))
+        return out
+
+    def ftranspose(self, a):
+        a = _f32(a)
+        rows, cols = a.shape
+        out = np.empty((cols, rows), np.float32)
+        self.lib.oracle_ftranspose(_p(a), rows, cols, _p(out))
+        return out
+
+    def fslice(self, a, index):
+        a = _f32(a)
+        out = np.empty(a.shape[1:], np.float32)
+        self.lib.oracle_fslice(_p(a), out.size, int(index), _p(out))
         return out
 
     def fconv2d(self, a, kernel):

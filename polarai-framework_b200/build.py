@@ -23,7 +23,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++"] + ARCH
 
-KERNEL_SOURCES = ["common.cu", "elementwise.cu", "extra_builtins.cu", "gemm_ffma.cu", "gemm_skinny.cu", "gemm_tc.cu", "gemm_tc2.cu", "peer_collective.cu", "dispatch.cu"]
+KERNEL_SOURCES = ["common.cu", "elementwise.cu", "extra_builtins.cu", "gemm_ffma.cu", "gemm_skinny.cu", "gemm_tc.cu", "peer_collective.cu", "dispatch.cu"]
 
 
 def _newer(src, dst, extra=()):

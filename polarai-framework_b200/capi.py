@@ -48,6 +48,8 @@ SIGNATURES = {
     "polar_b200_fsoftmax": (_i, [_p, _p, _u64, _p, _u64, _p]),
     "polar_b200_fpool": (_i, [_p, _u64, _u64, _u64, _u64, _u64, _u64, _p, _p]),
     "polar_b200_fconv2d": (_i, [_p, _u64, _u64, _p, _u64, _u64, _p, _p]),
+    "polar_b200_ftranspose": (_i, [_p, _u64, _u64, _p, _p]),
+    "polar_b200_fslice": (_i, [_p, _u64, _u64, _u64, _p, _p]),
     "polar_b200_fmatmul": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid_grad": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
@@ -56,10 +58,13 @@ SIGNATURES = {
     "polar_b200_fmatmul_tc": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "polar_b200_fmatmul_tn_small_n_static": (_i, [_i, _u64, _u64, _u64, _p, _p, _p, _p]),
     "polar_b200_static_scratch_bytes": (_u64, []),
-    "polar_b200_fmatmul_tc_pair": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _p]),
     "polar_b200_fmatmul_path": (_i, [_i, _i, _u64, _u64, _u64]),
     "polar_b200_device_status": (_i, []),
     "polar_b200_device_status_clear": (None, []),
+    "polar_b200_device_status_of": (_i, [_i]),
+    "polar_b200_check_device_status": (_i, []),
+    "polar_b200_set_wait_limit_ns": (None, [_u64]),
+    "polar_b200_wait_limit_ns": (_u64, []),
     "polar_b200_fsum": (_i, [_p, _p, _u64, _p]),
     "polar_b200_peer_alloc": (_i, [_u64, ctypes.POINTER(_p)]),
     "polar_b200_peer_free": (_i, [_p]),

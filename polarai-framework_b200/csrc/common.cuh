@@ -26,9 +26,65 @@ inline int check_launch(const char* what) {
   return POLAR_B200_OK;
 }
 
+// ---- status words and wait limits of the bounded device-side waits -----------------------
+// One status word per device, in pinned host memory every device can write (so the host reads
+// it without a CUDA call, even while a kernel is still running).  A kernel whose wait gives
+// up stores its code with atomicCAS(word, 0, code): the first code since the last clear stays.
+// Returns the device-visible pointer of the CURRENT device's word (nullptr + *rc on failure).
+int* device_status_word(int* rc);
+int device_status_read(int device);     // device < 0: the first non-zero word of any device
+void device_status_clear_all();
+// The host's wait bound in nanoseconds, or `fallback` when none was set.
+unsigned long long wait_limit_ns(unsigned long long fallback);
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Every launching entry point opens one of these.  A kernel must be launched with the device
+// of its stream current; a caller that drives several GPUs from one thread (or a plugin that
+// enumerated them) may arrive with another device current.  With a real stream handle the
+// stream's own device is made current for the duration of the call; with the NULL (legacy
+// default) stream, which every device has, the device that owns `ptr` (one of the call's
+// device buffers) decides.  The caller's current device is put back on exit.  Costs two
+// runtime queries per launch when nothing needs switching.
+class LaunchDeviceScope {
+public:
+  LaunchDeviceScope(void* stream, const void* ptr) {
+    int want = -1, cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    if (stream && stream != (void*)cudaStreamLegacy && stream != (void*)cudaStreamPerThread) {
+      if (cudaStreamGetDevice(as_stream(stream), &want) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+      }
+    } else if (ptr) {
+      cudaPointerAttributes attr;
+      if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+      }
+      if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) return;
+      want = attr.device;
+    }
+    if (want >= 0 && want != cur && cudaSetDevice(want) == cudaSuccess) {
+      prev_ = cur;
+      switched_ = true;
+    }
+  }
+  ~LaunchDeviceScope() {
+    if (switched_ && cudaSetDevice(prev_) != cudaSuccess) cudaGetLastError();
+  }
+  LaunchDeviceScope(const LaunchDeviceScope&) = delete;
+  LaunchDeviceScope& operator=(const LaunchDeviceScope&) = delete;
+
+private:
+  int prev_ = -1;
+  bool switched_ = false;
+};
 
 #ifdef __CUDACC__
 // fsigmoid's arithmetic, shared by the elementwise builtin and the fused matmul

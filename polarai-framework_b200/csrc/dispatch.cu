@@ -11,8 +11,6 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
               uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch = 0, int mt = 1);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k, int mt = 1);
 uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits, int mt = 1);
-int launch_tc_pair(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
-                   float* out, float* ws, uint32_t splits, int epilogue, cudaStream_t stream);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
 int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -23,8 +21,6 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
 uint64_t ragged_rows_workspace_bytes(uint64_t rem, uint64_t n, uint64_t k);
 int launch_ragged_rows(const float* left_tail, uint64_t left_pitch, const float* right, float* out_tail,
                        float* ws, uint64_t rem, uint64_t n, uint64_t k, cudaStream_t st);
-int tc_status_word();
-void tc_status_clear();
 
 namespace {
 
@@ -256,12 +252,14 @@ extern "C" {
 int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                        const float* right, float* out, void* workspace, uint64_t workspace_bytes,
                        void* stream) {
+  LaunchDeviceScope on(stream, out);
   return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 0, nullptr);
 }
 
 int polar_b200_fmatmul_sigmoid(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                                const float* right, float* out, void* workspace, uint64_t workspace_bytes,
                                void* stream) {
+  LaunchDeviceScope on(stream, out);
   return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 1, nullptr);
 }
 
@@ -272,6 +270,7 @@ int polar_b200_fmatmul_sigmoid_grad(int tl, int tr, uint64_t m, uint64_t n, uint
     clear_error();
     return fail(POLAR_B200_ERR_INVALID, "null sigmoid-output pointer");
   }
+  LaunchDeviceScope on(stream, out);
   return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 2, sigmoidOut);
 }
 }
@@ -283,6 +282,7 @@ int polar_b200_fmatmul_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
   if (rc) return rc;
   if (m == 0 || n == 0) return POLAR_B200_OK;
   if (k == 0) return polar_b200_ffill(0.0f, out, m * n, stream);
+  LaunchDeviceScope on(stream, out);
   return launch_ffma(tl, tr, m, n, k, left, right, out, as_stream(stream));
 }
 
@@ -307,35 +307,11 @@ int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, co
     return fail(POLAR_B200_ERR_INVALID,
                 "splits must be -1 (stream), 0 (automatic) or 1..64, and m*n a multiple of 4 when > 1");
   if (splits == -1 && tile_n != 256) return fail(POLAR_B200_ERR_INVALID, "stream mode needs tile_n = 256");
+  LaunchDeviceScope on(stream, out);
   const uint32_t s = splits == -1 ? 0u : splits == 0 ? tc_default_splits(m, n, k, mt) : (uint32_t)splits;
   return run_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, s, nullptr, 0, as_stream(stream),
                 0, 0, mt);
 }
-
-int polar_b200_fmatmul_tc_pair(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
-                               const float* right, float* out, int splits, int fuse_sigmoid, void* stream) {
-  clear_error();
-  int rc = check_mm(tl, tr, m, n, k, left, right, out);
-  if (rc) return rc;
-  if (m == 0 || n == 0 || k == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "empty matrix");
-  if (!tc_shape_ok(tl, tr, m, n, k, left, right))
-    return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
-  if (splits < 1 || splits > 64 || (splits > 1 && ((m * n) & 3)))
-    return fail(POLAR_B200_ERR_INVALID, "splits must be 1..64, and m*n a multiple of 4 when > 1");
-  cudaStream_t st = as_stream(stream);
-  if (splits == 1) return launch_tc_pair(tl, tr, m, n, k, left, right, out, nullptr, 1, fuse_sigmoid & 3, st);
-  void* ws = nullptr;
-  cudaError_t e = cudaMallocAsync(&ws, (uint64_t)splits * m * n * sizeof(float), st);
-  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
-  rc = launch_tc_pair(tl, tr, m, n, k, left, right, out, static_cast<float*>(ws), (uint32_t)splits,
-                      fuse_sigmoid ? 1 : 0, st);
-  e = cudaFreeAsync(ws, st);
-  if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
-  return rc;
-}
-
-int polar_b200_device_status(void) { return tc_status_word(); }
-void polar_b200_device_status_clear(void) { tc_status_clear(); }
 
 static uint64_t numel(const polar_b200_tensor& t) {
   uint64_t n = 1;
@@ -409,6 +385,19 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     if (kh > h || kw > w || a[2].tensor.shape[0] != h - kh + 1 || a[2].tensor.shape[1] != w - kw + 1)
       return fail(bad_args, "fconv2d: shapes do not agree");
     return polar_b200_fconv2d(a[0].tensor.data, h, w, a[1].tensor.data, kh, kw, a[2].tensor.data, stream);
+  }
+  if (!std::strcmp(name, "ftranspose")) {
+    if (!pattern("TT") || a[0].tensor.dims != 2 || a[1].tensor.dims != 2 ||
+        a[1].tensor.shape[0] != a[0].tensor.shape[1] || a[1].tensor.shape[1] != a[0].tensor.shape[0])
+      return fail(bad_args, "ftranspose expects (T in[r,c], T out[c,r])");
+    return polar_b200_ftranspose(a[0].tensor.data, a[0].tensor.shape[0], a[0].tensor.shape[1], a[1].tensor.data, stream);
+  }
+  if (!std::strcmp(name, "fslice")) {
+    if (!pattern("TfT") || a[0].tensor.dims < 1 || a[0].tensor.shape[0] == 0 || a[1].integer < 0 ||
+        numel(a[2].tensor) * a[0].tensor.shape[0] != numel(a[0].tensor))
+      return fail(bad_args, "fslice expects (T in[d0,...], i64 index, T out[...]) with out one sub-tensor of in");
+    return polar_b200_fslice(a[0].tensor.data, a[0].tensor.shape[0], numel(a[2].tensor), (uint64_t)a[1].integer,
+                             a[2].tensor.data, stream);
   }
   if (!std::strcmp(name, "fsigmoid_grad")) {
     if (!pattern("TTT") || !same(0, 2) || !same(1, 2))

@@ -236,6 +236,7 @@ int launch_ew(const char* name, Op op, const float* in0, const float* in1, float
   if (!out || (NIN >= 1 && !in0) || (NIN >= 2 && !in1))
     return fail(POLAR_B200_ERR_INVALID, "null device pointer");
   if (n > (1ull << 40)) return fail(POLAR_B200_ERR_INVALID, "element count too large");
+  LaunchDeviceScope on(stream, out);
   bool vec = aligned16(out) && (NIN < 1 || aligned16(in0)) && (NIN < 2 || aligned16(in1)) && n >= 4;
   if (vec) {
     unsigned grid = tiles_for(n >> 2, Shape<Op>::kUnroll);
@@ -298,6 +299,7 @@ int polar_b200_fmulconcat(const float* gradient, const float* localDerivative, f
   if (n == 0) return POLAR_B200_OK;
   if (!gradient || !localDerivative || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
   if (n > (1ull << 40)) return fail(POLAR_B200_ERR_INVALID, "element count too large");
+  LaunchDeviceScope on(stream, out);
   if (aligned16(localDerivative) && aligned16(out) && n >= 4) {
     unsigned grid = tiles_for(n >> 2);
     mulconcat_vec_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(gradient, localDerivative, out, n);
@@ -313,6 +315,7 @@ int polar_b200_fsum(const float* in, double* sum, uint64_t n, void* stream) {
   if (!sum) return fail(POLAR_B200_ERR_INVALID, "null sum pointer");
   if (n == 0) return POLAR_B200_OK;
   if (!in) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  LaunchDeviceScope on(stream, in);
   int vec_ok = aligned16(in) && n >= 4;
   unsigned grid = grid_for(vec_ok ? (n >> 2) : n, (uint64_t)kThreads * 8);
   sum_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(in, sum, n, vec_ok);

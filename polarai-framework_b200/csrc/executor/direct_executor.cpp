@@ -272,10 +272,13 @@ private:
     g.registerFunctor<builtin::ReLU>(relu);
     builtin_functor_t<builtin::Softmax> sm = [this](GenValue in, GenValue out) { launch("fsoftmax", {in, out}); };
     g.registerFunctor<builtin::Softmax>(sm);
-    // Builtins no operation of the reference emits.
-    builtin_functor_t<builtin::Slice> sl = [this](GenValue, GenValue) { refuse("Slice"); };
+    // Builtins no operation of the reference emits.  Transpose has a tensor in and a tensor
+    // out like any other.  Slice's functor takes (index, tensor) and returns nothing
+    // (GenBuiltins.hpp:147-149), so a generator cannot hand the sub-tensor to a consumer: no
+    // launch can be recorded for it.  The device builtin "fslice" exists for callers by name.
+    builtin_functor_t<builtin::Slice> sl = [this](GenValue, GenValue) { refuse("Slice (no result value to launch into)"); };
     g.registerFunctor<builtin::Slice>(sl);
-    builtin_functor_t<builtin::Transpose> tp = [this](GenValue, GenValue) { refuse("Transpose"); };
+    builtin_functor_t<builtin::Transpose> tp = [this](GenValue in, GenValue out) { launch("ftranspose", {in, out}); };
     g.registerFunctor<builtin::Transpose>(tp);
   }
 };

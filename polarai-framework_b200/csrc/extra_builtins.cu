@@ -1,6 +1,6 @@
 // The remaining operation builtins of the catalogue
 // (include/polarai/core/internal/GenBuiltins.hpp:25-52 of the reference): frelu,
-// fsoftmax, fpool, fconv2d.  None of them is on the benchmarked path; they are here so
+// fsoftmax, fpool, fconv2d, ftranspose, fslice.  None of them is on the benchmarked path; they are here so
 // that any graph the reference's operations can express runs on this runtime.  Small
 // 2-D single-channel problems: one thread per output element.
 #include "common.cuh"
@@ -71,6 +71,25 @@ __global__ void __launch_bounds__(kThreads) conv2d_kernel(const float* in, uint6
   out[e] = acc;
 }
 
+// out[c, r] = in[r, c] through a 32 x 33 shared-memory tile: both the reads and the writes
+// are coalesced rows of 32 floats.  One tile per CTA (32 x 8 threads, four rows each).
+constexpr int kTile = 32;
+__global__ void __launch_bounds__(kTile * 8) transpose_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                              uint64_t rows, uint64_t cols, uint32_t tiles_c) {
+  __shared__ float tile[kTile][kTile + 1];
+  const uint64_t tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+  const uint64_t r0 = tr * kTile, c0 = tc * kTile;
+  for (int j = threadIdx.y; j < kTile; j += 8) {
+    const uint64_t r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = in[r * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < kTile; j += 8) {
+    const uint64_t c = c0 + j, r = r0 + threadIdx.x;      // out is [cols, rows]
+    if (c < cols && r < rows) out[c * rows + r] = tile[threadIdx.x][j];
+  }
+}
+
 unsigned blocks_for(uint64_t n) {
   uint64_t need = (n + kThreads - 1) / kThreads;
   uint64_t cap = (uint64_t)sm_count() * 8;
@@ -89,6 +108,7 @@ int polar_b200_frelu(const float* in, float* out, uint64_t n, void* stream) {
   clear_error();
   if (n == 0) return POLAR_B200_OK;
   if (!in || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  LaunchDeviceScope on(stream, out);
   relu_kernel<<<blocks_for(n), kThreads, 0, as_stream(stream)>>>(in, out, n);
   return check_launch("frelu");
 }
@@ -98,6 +118,7 @@ int polar_b200_fsoftmax(const float* in, float* out, uint64_t n, void* workspace
   clear_error();
   if (n == 0) return POLAR_B200_OK;
   if (!in || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  LaunchDeviceScope on(stream, out);
   cudaStream_t st = as_stream(stream);
   double* total = static_cast<double*>(workspace);
   bool own = false;
@@ -127,6 +148,7 @@ int polar_b200_fpool(const float* in, uint64_t h, uint64_t w, uint64_t windowH, 
     return fail(POLAR_B200_ERR_INVALID, "fpool: window and stride must be positive and fit the input");
   const uint64_t oh = (h - windowH) / strideH + 1, ow = (w - windowW) / strideW + 1;
   if (!in || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  LaunchDeviceScope on(stream, out);
   pool_kernel<<<(unsigned)((oh * ow + kThreads - 1) / kThreads), kThreads, 0, as_stream(stream)>>>(
       in, h, w, windowH, windowW, strideH, strideW, out, oh, ow);
   return check_launch("fpool");
@@ -140,9 +162,30 @@ int polar_b200_fconv2d(const float* in, uint64_t h, uint64_t w, const float* ker
   if ((kh & 1) == 0 || (kw & 1) == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "fconv2d: kernel extents must be odd");
   if (!in || !kernel || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
   const uint64_t oh = h - kh + 1, ow = w - kw + 1;
+  LaunchDeviceScope on(stream, out);
   conv2d_kernel<<<(unsigned)((oh * ow + kThreads - 1) / kThreads), kThreads, 0, as_stream(stream)>>>(
       in, h, w, kernel, kh, kw, out, oh, ow);
   return check_launch("fconv2d");
+}
+
+int polar_b200_ftranspose(const float* in, uint64_t rows, uint64_t cols, float* out, void* stream) {
+  clear_error();
+  if (rows == 0 || cols == 0) return POLAR_B200_OK;
+  if (!in || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  if (in == out) return fail(POLAR_B200_ERR_INVALID, "ftranspose cannot run in place");
+  const uint64_t tiles_r = (rows + kTile - 1) / kTile, tiles_c = (cols + kTile - 1) / kTile;
+  if (tiles_r * tiles_c > 0x7fffffffull) return fail(POLAR_B200_ERR_INVALID, "matrix too large");
+  LaunchDeviceScope on(stream, out);
+  transpose_kernel<<<(unsigned)(tiles_r * tiles_c), dim3(kTile, 8), 0, as_stream(stream)>>>(in, out, rows, cols,
+                                                                                         (uint32_t)tiles_c);
+  return check_launch("ftranspose");
+}
+
+int polar_b200_fslice(const float* in, uint64_t first_dim, uint64_t inner, uint64_t index, float* out, void* stream) {
+  clear_error();
+  if (index >= first_dim) return fail(POLAR_B200_ERR_INVALID, "fslice: index outside the first dimension");
+  if (inner && !in) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  return polar_b200_fcopy(in + index * inner, out, inner, stream);   // a bit-exact copy of one sub-tensor
 }
 
 }  // extern "C"

@@ -640,6 +640,7 @@ int polar_b200_fmatmul_tn_small_n_static(int transRight, uint64_t m, uint64_t n,
     return fail(POLAR_B200_ERR_WORKSPACE,
                 "this product needs more than the 16 MiB of built-in scratch; use polar_b200_fmatmul with a "
                 "caller workspace");
+  LaunchDeviceScope on(stream, out);   // the array's address is looked up on the device that will run the kernels
   int rc = POLAR_B200_OK;
   float* scratch = static_scratch_for_current_device(&rc);
   if (!scratch) return rc;

@@ -90,7 +90,8 @@ struct Params {
   int b_mn_major;   // right operand stored [k,n]
   int passes;       // 3 = fp32-accurate split, 1 = plain TF32 (diagnostic)
   int write_hi;     // split warps also store the masked hi part in place
-  int* status;      // device-visible status word
+  int* status;      // this device's status word (pinned host memory, device-visible)
+  unsigned long long wait_ns;   // bound of every mbarrier wait
   uint32_t tiles_m, tiles_n;
   int epilogue;     // 0: store the product; 1: store fsigmoid(product) (only when splits == 1)
   uint32_t splits;  // work units per tile: the k range is cut into `splits` parts
@@ -237,7 +238,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (uint32_t kb = pc.kb0, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101)) { ok = false; break; }
+          if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101, p.wait_ns)) { ok = false; break; }
           const uint32_t stage = smem_base + s * C::kStageBytes;
           mbar_expect_tx(full_raw(s), C::kRawBytes);
           const int k0 = (int)(kb * BK);
@@ -283,14 +284,14 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // tiles ago).  MT = 2: one buffer of two accumulators, drained after every tile.
         const uint32_t as = MT == 1 ? (tile_iter & 1u) : 0u;
         const uint32_t use = MT == 1 ? (tile_iter >> 1) : tile_iter;   // how often this buffer was used
-        ok = mbar_wait(acc_empty(as), (use & 1u) ^ 1u, abort_flag, p.status, 106);
+        ok = mbar_wait(acc_empty(as), (use & 1u) ^ 1u, abort_flag, p.status, 106, p.wait_ns);
         if (!ok) break;
         tc_fence_after();
         const uint32_t kb_first = pc.kb0;
         for (uint32_t kb = kb_first, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102);
+          ok = mbar_wait(full_raw(s), ph, abort_flag, p.status, 102, p.wait_ns);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_hi = smem_base + s * C::kStageBytes;
@@ -309,7 +310,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
           }
           if (p.passes == 3) {
-            ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103);
+            ok = mbar_wait(full_lo(s), ph, abort_flag, p.status, 103, p.wait_ns);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
@@ -357,7 +358,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (uint32_t kb = pc.kb0, kb_end = pc.kb1; p.passes == 3 && kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104)) { ok = false; break; }
+          if (!mbar_wait(full_raw(s), ph, abort_flag, p.status, 104, p.wait_ns)) { ok = false; break; }
           float4* raw = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes);
           float4* lo = reinterpret_cast<float4*>(smem_gen + s * C::kStageBytes + C::kRawBytes);
           constexpr int kVecs = C::kRawBytes / 16;
@@ -381,7 +382,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (MT == 2 && ok) {
           // 256-row tiles: nothing is left to split until this tile is drained, so these
           // warps drain its lower sub-tile while the epilogue warps drain the upper one
-          if (!mbar_wait(acc_full(0), tile_iter & 1u, abort_flag, p.status, 107)) break;
+          if (!mbar_wait(acc_full(0), tile_iter & 1u, abort_flag, p.status, 107, p.wait_ns)) break;
           tc_fence_after();
           drain(pc, 0, 1, 2, warp & 3, (warp - 2) >> 2);
           tc_fence_before();
@@ -402,7 +403,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     for (; walk.next(pc); ++tile_iter) {
       const uint32_t as = MT == 1 ? (tile_iter & 1u) : 0u;
       const uint32_t use = MT == 1 ? (tile_iter >> 1) : tile_iter;
-      if (!mbar_wait(acc_full(as), use & 1u, abort_flag, p.status, 105)) break;
+      if (!mbar_wait(acc_full(as), use & 1u, abort_flag, p.status, 105, p.wait_ns)) break;
       tc_fence_after();
       drain(pc, as, 0, 1, q, half);
       tc_fence_before();
@@ -465,23 +466,6 @@ int make_map(CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer
   return POLAR_B200_OK;
 }
 
-// Status word: pinned host memory mapped into the device, one per process.
-int* g_status_host = nullptr;
-int* g_status_dev = nullptr;
-int ensure_status() {
-  static std::once_flag once;
-  static cudaError_t err = cudaSuccess;
-  std::call_once(once, [] {
-    err = cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), 64, cudaHostAllocMapped | cudaHostAllocPortable);
-    if (err == cudaSuccess) {
-      g_status_host[0] = 0;
-      err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0);
-    }
-  });
-  if (err != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "status word allocation", err);
-  return POLAR_B200_OK;
-}
-
 bool shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right) {
   // TMA: 16-byte aligned base, row pitch a multiple of 16 bytes.
@@ -492,9 +476,11 @@ bool shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
   return m > 0 && n > 0 && k > 0;
 }
 
-// out[e] = sum of the splits' partial products, ascending split index (fixed order).
-__global__ void __launch_bounds__(256) add_splits_kernel(const float4* __restrict__ partial, float4* __restrict__ out,
-                                                         uint64_t nvec, uint32_t splits, int epilogue) {
+// out[e] = sum of the splits' partial products, ascending split index (fixed order).  The
+// partial products live in 16-byte aligned scratch; `out` is the caller's and may be only
+// 4-byte aligned, in which case the four sums are stored one by one.
+__global__ void __launch_bounds__(256) add_splits_kernel(const float4* __restrict__ partial, float* __restrict__ out,
+                                                         uint64_t nvec, uint32_t splits, int epilogue, int out_vec) {
   const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= nvec) return;
   float4 s = __ldcs(partial + i);
@@ -505,15 +491,19 @@ __global__ void __launch_bounds__(256) add_splits_kernel(const float4* __restric
   if (epilogue == 1) {
     s.x = sigmoid_clamped(s.x); s.y = sigmoid_clamped(s.y); s.z = sigmoid_clamped(s.z); s.w = sigmoid_clamped(s.w);
   }
-  out[i] = s;
+  if (out_vec) {
+    reinterpret_cast<float4*>(out)[i] = s;
+  } else {
+    float* o = out + 4 * i;
+    o[0] = s.x; o[1] = s.y; o[2] = s.z; o[3] = s.w;
+  }
 }
 
 int launch_add_splits(const float* ws, float* out, uint64_t m, uint64_t n, uint32_t splits, int epilogue,
                       cudaStream_t stream) {
   const uint64_t nvec = m * n / 4;
-  add_splits_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(ws),
-                                                                       reinterpret_cast<float4*>(out), nvec, splits,
-                                                                       epilogue);
+  add_splits_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(ws), out, nvec,
+                                                                       splits, epilogue, aligned16(out) ? 1 : 0);
   return check_launch("fmatmul_add_splits");
 }
 
@@ -605,8 +595,9 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
     if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFuncSetAttribute(smem)", e);
     attr_done[dev] = true;
   }
-  int rc = ensure_status();
-  if (rc) return rc;
+  int rc = POLAR_B200_OK;
+  int* status_word = device_status_word(&rc);
+  if (!status_word) return rc;
   CUtensorMap map_a, map_b;
   // left: stored [m,k] (K-major: inner k, box {BK, 128}) or [k,m] (MN-major: inner m, box {32, BK})
   rc = tl ? make_map(&map_a, left, m, k, 32, BK, true, BK, left_pitch)
@@ -619,7 +610,8 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   p.m = m; p.n = n; p.k = k; p.out = out;
   p.a_mn_major = tl ? 1 : 0;
   p.b_mn_major = tr ? 0 : 1;
-  p.passes = passes; p.write_hi = write_hi; p.status = g_status_dev;
+  p.passes = passes; p.write_hi = write_hi; p.status = status_word;
+  p.wait_ns = wait_limit_ns(2000000000ull);
   uint64_t tm = (m + BM * MT - 1) / (BM * MT), tn = (n + BN - 1) / BN;
   if (tm * tn > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   p.tiles_m = (uint32_t)tm; p.tiles_n = (uint32_t)tn;
@@ -654,10 +646,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   fmatmul_tc_kernel<BN, BK, MT><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
   rc = check_launch("fmatmul_tc");
   if (rc || splits == 1) return rc;
-  const uint64_t nvec = m * n / 4;
-  add_splits_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(ws),
-                                                                       reinterpret_cast<float4*>(out), nvec, splits, epilogue);
-  return check_launch("fmatmul_add_splits");
+  return launch_add_splits(ws, out, m, n, splits, epilogue, stream);
 }
 
 }  // namespace tc
@@ -695,7 +684,5 @@ bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float
   return tc::shape_ok(tl, tr, m, n, k, left, right);
 }
 
-int tc_status_word() { return tc::g_status_host ? *(volatile int*)tc::g_status_host : 0; }
-void tc_status_clear() { if (tc::g_status_host) *(volatile int*)tc::g_status_host = 0; }
 
 }  // namespace polar_b200

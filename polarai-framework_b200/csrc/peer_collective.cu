@@ -16,10 +16,16 @@
 // place.  No multicast object, no TMA: plain peer loads and stores.
 //
 // Flags are step numbers that only grow, so nothing is ever reset and a rank that is
-// one step ahead cannot confuse a slower one.  Every wait is bounded (kWaitNs); a wait
-// that gives up writes 301 (ready) or 302 (done) to the status word, the data phases
-// still run to completion on whatever is there, and the host reads the word after it
-// has synchronised the stream.
+// one step ahead cannot confuse a slower one.  Every wait is bounded (four seconds unless
+// the host set another limit with polar_b200_set_wait_limit_ns).  A wait that gives up
+// records 301 (a peer's gradients never became ready) or 302 (a peer never finished its
+// slice) in the device's status word and the launch ends WITHOUT touching the weights:
+// a CTA that gave up on "ready" skips its part of the sum and marks the step aborted, the
+// rank then never publishes "done", so every rank's second wait runs out too and no rank
+// applies an update computed from a partial sum.  The host reads the word after it has
+// synchronised the stream (polar_b200_check_device_status -> POLAR_B200_ERR_TIMEOUT).
+// All CTAs of a launch wait on other ranks, so the launch is cooperative: the driver starts
+// it only when every CTA can be resident at once.
 #include <cuda_runtime.h>
 
 #include <cstring>
@@ -27,17 +33,12 @@
 #include "common.cuh"
 
 namespace polar_b200 {
-namespace tc {
-extern int* g_status_dev;
-int ensure_status();
-}  // namespace tc
-
 namespace peer {
 
 constexpr int kMaxWorld = POLAR_B200_MAX_PEERS;
 constexpr int kMaxSegments = POLAR_B200_MAX_UPDATE_SEGMENTS;
 constexpr int kThreads = 512;
-constexpr unsigned long long kWaitNs = 4000000000ull;   // 4 s
+constexpr unsigned long long kDefaultWaitNs = 4000000000ull;   // 4 s
 
 // Control words at the head of every rank's buffer (uint32 each).
 constexpr int kReady = 0;                 // [kMaxWorld] written by peer p at index p
@@ -45,6 +46,7 @@ constexpr int kDone = kMaxWorld;          // [kMaxWorld]
 constexpr int kStep = 2 * kMaxWorld;      // local: last completed step
 constexpr int kTicketA = kStep + 1;       // local: CTAs that finished phase 2
 constexpr int kTicketB = kStep + 2;       // local: CTAs that finished phase 4
+constexpr int kAborted = kStep + 3;       // local: the step in which a CTA of this rank gave up waiting
 // %globaltimer (ns) of CTA 0 in the last launch: start, gradients of all ranks ready, slice
 // summed and stored, all slices in place, update done.  Five 64-bit words, for profiling.
 constexpr int kStamps = 40;
@@ -63,6 +65,7 @@ struct Params {
   uint32_t rank, world, n_seg;
   float scale_w, scale_g;
   int* status;
+  unsigned long long wait_ns;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -93,21 +96,24 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 
 // Threads 0..world-1 of the CTA each watch one peer's word until it reaches `step`.
-__device__ __forceinline__ void wait_all(const uint32_t* words, uint32_t world, uint32_t step, int* status,
-                                         int code) {
+// Returns false (to every thread of the CTA) when a wait ran out.
+__device__ __forceinline__ bool wait_all(const uint32_t* words, uint32_t world, uint32_t step, int* status,
+                                         int code, unsigned long long limit_ns) {
+  int gave_up = 0;
   if (threadIdx.x < world) {
     const uint32_t* w = words + threadIdx.x;
     const unsigned long long t0 = now_ns();
     // step numbers wrap after 2^32 steps: compare as a signed distance
     while ((int32_t)(ld_acquire_sys(w) - step) < 0) {
-      if (now_ns() - t0 > kWaitNs) {
-        *(volatile int*)status = code;
+      if (now_ns() - t0 > limit_ns) {
+        atomicCAS(status, 0, code);   // the first code since the last clear stays
+        gave_up = 1;
         break;
       }
       __nanosleep(64);
     }
   }
-  __syncthreads();
+  return __syncthreads_or(gave_up) == 0;
 }
 
 template <int WORLD>   // 0 = any world size up to kMaxWorld
@@ -124,11 +130,12 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kReady + p.rank, step);
   }
-  wait_all(ctl + kReady, world, step, p.status, 301);
+  const bool ready = wait_all(ctl + kReady, world, step, p.status, 301, p.wait_ns);
+  if (!ready && threadIdx.x == 0) *(volatile uint32_t*)(ctl + kAborted) = step;
   if (stamper) stamps[1] = now_ns();
 
   // 2. slice `rank`, summed in rank order, to everyone
-  {
+  if (ready) {
     const uint64_t per = (p.n4 + world - 1) / world;
     const uint64_t lo = (uint64_t)p.rank * per;
     const uint64_t hi = lo + per < p.n4 ? lo + per : p.n4;
@@ -179,14 +186,16 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
   if (last && threadIdx.x < world) {
     if (threadIdx.x == 0) ctl[kTicketA] = 0;
     __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kDone + p.rank, step);
+    // "slice in place" is only said when every CTA of this rank did its part of the sum
+    if (*(volatile uint32_t*)(ctl + kAborted) != step)
+      st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kDone + p.rank, step);
   }
-  wait_all(ctl + kDone, world, step, p.status, 302);
+  const bool done = wait_all(ctl + kDone, world, step, p.status, 302, p.wait_ns);
   if (stamper) stamps[3] = now_ns();
 
-  // 4. fadd(W, sw, G, sg) -> W on this rank's replica
+  // 4. fadd(W, sw, G, sg) -> W on this rank's replica; skipped when the sum is not complete
   const float* g = reinterpret_cast<const float*>(p.base[p.rank] + POLAR_B200_PEER_CONTROL_BYTES);
-  for (uint32_t sidx = 0; sidx < p.n_seg; ++sidx) {
+  for (uint32_t sidx = 0; done && sidx < p.n_seg; ++sidx) {
     const Segment sg = p.seg[sidx];
     const float4* g4 = reinterpret_cast<const float4*>(g + sg.offset);
     float4* w4 = reinterpret_cast<float4*>(sg.w);
@@ -300,23 +309,31 @@ int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t worl
       return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: segment outside the vector, or not 16-byte aligned");
     p.seg[s] = peer::Segment{g.weights, g.offset, g.count};
   }
-  int rc = tc::ensure_status();
-  if (rc) return rc;
+  LaunchDeviceScope on(stream, buffers[rank]);
+  int rc = POLAR_B200_OK;
+  p.status = device_status_word(&rc);
+  if (!p.status) return rc;
+  p.wait_ns = wait_limit_ns(peer::kDefaultWaitNs);
   p.n4 = (n + 3) / 4;   // the buffer is padded to 16 bytes by polar_b200_peer_alloc
   p.rank = rank; p.world = world; p.n_seg = n_segments;
   p.scale_w = scale_w; p.scale_g = scale_g;
-  p.status = tc::g_status_dev;
-  // Every CTA waits on the other ranks, so all of them must be resident at once: one per SM.
+  // Every CTA waits on the other ranks, so all of them must be resident at once: at most one
+  // per SM, launched cooperatively (the driver then starts the grid only as a whole, also
+  // when other kernels are holding SMs at that moment).
   uint64_t most = p.n4;
   uint64_t want = (most + peer::kThreads - 1) / peer::kThreads;
   unsigned grid = (unsigned)(want < (uint64_t)sm_count() ? (want ? want : 1) : (uint64_t)sm_count());
   cudaStream_t st = as_stream(stream);
+  const void* fn = nullptr;
   switch (world) {
-    case 2: peer::allreduce_fadd_kernel<2><<<grid, peer::kThreads, 0, st>>>(p); break;
-    case 4: peer::allreduce_fadd_kernel<4><<<grid, peer::kThreads, 0, st>>>(p); break;
-    case 8: peer::allreduce_fadd_kernel<8><<<grid, peer::kThreads, 0, st>>>(p); break;
-    default: peer::allreduce_fadd_kernel<0><<<grid, peer::kThreads, 0, st>>>(p); break;
+    case 2: fn = reinterpret_cast<const void*>(&peer::allreduce_fadd_kernel<2>); break;
+    case 4: fn = reinterpret_cast<const void*>(&peer::allreduce_fadd_kernel<4>); break;
+    case 8: fn = reinterpret_cast<const void*>(&peer::allreduce_fadd_kernel<8>); break;
+    default: fn = reinterpret_cast<const void*>(&peer::allreduce_fadd_kernel<0>); break;
   }
+  void* kargs[] = {&p};
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(peer::kThreads), kargs, 0, st);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "allreduce_fadd cooperative launch", e);
   return check_launch("allreduce_fadd launch");
 }
 

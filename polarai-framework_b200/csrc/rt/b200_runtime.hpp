@@ -16,7 +16,11 @@
 //    not the address of a handle;
 //  - launch() is stream-ordered and does not synchronise; the returned Event
 //    completes when the kernel has;
-//  - memory comes from a per-device cudaMallocAsync pool that keeps freed blocks.
+//  - memory comes from a per-device cudaMallocAsync pool that keeps freed blocks;
+//  - the calling thread's current CUDA device is never changed: every method makes
+//    its GPU current for its own duration only (device_scope.hpp), and a GPU is not
+//    touched at all (no context, stream or pool on it) until it is first used, so a
+//    host that enumerates eight devices and computes on one pays for one.
 #pragma once
 
 #include <polarai/backend/generic/AllocatorLayerBase.hpp>
@@ -42,7 +46,7 @@ class B200Device;
 // Per-device memory layer on a stream-ordered pool.
 class B200Allocator final : public AllocatorLayerBase {
 public:
-  B200Allocator(int ordinal, cudaStream_t stream);
+  explicit B200Allocator(B200Device& owner);
   ~B200Allocator() override;
 
   void registerMemoryOffloadCallback(MemoryOffloadCallbackT cb) override { mOffload = std::move(cb); }
@@ -55,20 +59,42 @@ public:
   size_t getTag(MemoryRecord record) override;
   void setTag(MemoryRecord record, size_t tag) override;
 
-  // Not part of the reference interface.
+  // ---- not part of the reference interface ----
   size_t bytesInUse() const { return mBytes; }
   void setLimit(size_t bytes) { mLimit = bytes; }   // 0 = no limit
   int lastError() const { return mLastError; }
+  // Frees everything; the layer stays valid but empty (see ~B200Device).
+  void shutdown();
+
+  // "The record's block was just written by work queued on the device's main stream."
+  // A later copyToHost of the record waits for exactly that work instead of for
+  // everything queued on the stream.
+  void markWritten(const MemoryRecord& record);
+  // The event of the last markWritten (nullptr: never marked).
+  cudaEvent_t writtenEvent(const MemoryRecord& record);
+
+  // Upload ahead of use: version `tag` of the record is copied from pinned host memory
+  // into a FRESH block on the device's upload stream, while kernels on the main stream
+  // may still be reading the current block.  adoptStaged() swaps the fresh block in
+  // (the main stream waits for the upload; the old block is freed in stream order).
+  // `uploaded` receives an event (owned by the callee) that completes with the copy.
+  bool stage(const MemoryRecord& record, const void* pinnedSrc, size_t tag, cudaEvent_t* uploaded);
+  bool adoptStaged(const MemoryRecord& record, size_t tag);
 
 private:
-  struct Block { void* ptr; size_t size; size_t tag; int locks; };
+  struct Block { void* ptr; size_t size; size_t tag; int locks; cudaEvent_t written; };
+  struct Staged { void* ptr; size_t size; size_t tag; cudaEvent_t done; };
   bool evictFor(size_t bytes);
+  bool ensurePool();
+  void dropStaged(size_t va);
 
-  int mOrdinal;
-  cudaStream_t mStream;
+  B200Device& mOwner;
   cudaMemPool_t mPool = nullptr;
+  bool mPoolTried = false;
+  bool mDead = false;
   MemoryOffloadCallbackT mOffload;
   std::unordered_map<size_t, Block> mBlocks;          // by virtual address
+  std::unordered_map<size_t, Staged> mStaged;         // uploaded ahead, not yet adopted
   std::unordered_set<size_t> mReleased;               // allocated, unlocked: may be evicted
   size_t mBytes = 0;
   size_t mLimit = 0;
@@ -115,28 +141,40 @@ public:
   // Kernels are precompiled for sm_100a; there is nothing to select.
   void selectBinary(std::vector<std::shared_ptr<ProgramDesc>>&) override {}
 
-  // Not part of the reference interface.
+  // ---- not part of the reference interface ----
   int ordinal() const { return mOrdinal; }
-  cudaStream_t stream() const { return mStream; }
+  // The three streams of the device, created on first use: `stream` carries kernels and
+  // ordinary copies; uploads ahead of use and targeted read-backs have their own so
+  // that they overlap the kernels.
+  cudaStream_t stream() const { ensureReady(); return mStream; }
+  cudaStream_t uploadStream() const { ensureReady(); return mUpload; }
+  cudaStream_t downloadStream() const { ensureReady(); return mDownload; }
+  bool ready() const { return mReady; }
+  B200Allocator& pool() { return *mAllocator; }
   int lastStatus() const { return mLastStatus; }
   // Returns the last error status and clears it, so that one failure is reported once.
   int takeStatus() { int s = mLastStatus; mLastStatus = 0; return s; }
   const std::string& lastError() const { return mLastError; }
   void synchronize() const;
-  cudaEvent_t takeEvent();
-  void giveEvent(cudaEvent_t e);
+  // Newest copy of the record lives on `src`: fetch it device to device, ordered after
+  // the producer on src's stream and before later work on this device's stream.
+  void copyFromPeer(MemoryRecord record, B200Device& src);
 
 private:
+  void ensureReady() const;
+
   int mOrdinal;
-  cudaStream_t mStream = nullptr;
+  mutable bool mReady = false;
+  mutable std::mutex mInitMutex;
+  mutable cudaStream_t mStream = nullptr;
+  mutable cudaStream_t mUpload = nullptr;
+  mutable cudaStream_t mDownload = nullptr;
   void* mWorkspace = nullptr;        // scratch for split-k matmuls, grown on demand
   uint64_t mWorkspaceBytes = 0;
   std::string mName;
   std::shared_ptr<B200Allocator> mAllocator;
   mutable int mLastStatus = 0;
   mutable std::string mLastError;
-  std::vector<cudaEvent_t> mEventPool;
-  std::mutex mEventMutex;
 };
 
 class B200Context final : public Context {

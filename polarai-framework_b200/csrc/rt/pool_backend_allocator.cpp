@@ -1,5 +1,7 @@
 #include "pool_backend_allocator.hpp"
 
+#include "b200_runtime.hpp"
+
 #include <cuda_runtime.h>
 #include <polar_b200.h>
 
@@ -10,12 +12,39 @@ namespace polarai::backend::generic {
 
 using core::internal::LockType;
 
+namespace {
+// The CUDA devices an allocator of this plugin meets are the plugin's own (the build has no
+// RTTI; the provider tag is the reference's way to tell device kinds apart).
+B200Device* asB200(Device& d) {
+  return d.getProvider() == DeviceProvider::CUDA ? static_cast<B200Device*>(&d) : nullptr;
+}
+}  // namespace
+
 void PoolBackendAllocator::freeHost(HostBlock& b) {
-  if (b.pinned) {
-    cudaFreeHost(b.ptr);
-  } else {
-    std::free(b.ptr);
+  // an upload may still be reading either buffer
+  b.reading.settle();
+  b.spareReading.settle();
+  for (void* p : {b.ptr, b.spare}) {
+    if (!p) continue;
+    if (b.pinned) {
+      cudaFreeHost(p);
+    } else {
+      std::free(p);
+    }
   }
+  b.ptr = b.spare = nullptr;
+}
+
+void* PoolBackendAllocator::allocHost(size_t bytes, bool* pinned) {
+  void* p = nullptr;
+  // Pinned, so that host<->device copies run at full PCIe/C2C rate and can be
+  // asynchronous.
+  if (*pinned && cudaMallocHost(&p, bytes) == cudaSuccess) return p;
+  // No CUDA driver (a host-only process) or no pinnable memory left: pageable
+  // memory holds the same data, copies are just slower.
+  cudaGetLastError();
+  *pinned = false;
+  return std::malloc(bytes);
 }
 
 PoolBackendAllocator::~PoolBackendAllocator() {
@@ -66,23 +95,18 @@ bool PoolBackendAllocator::toRecord(const TensorInternal& t, MemoryRecord& out) 
 
 void PoolBackendAllocator::ensureHost(const MemoryRecord& record) {
   if (mHost.count(record.virtualAddress)) return;
-  void* p = nullptr;
   size_t bytes = record.allocationSize ? record.allocationSize : 4;
-  // Pinned, so that host<->device copies run at full PCIe/C2C rate and can be
-  // asynchronous.
   bool pinned = true;
-  if (cudaMallocHost(&p, bytes) != cudaSuccess) {
-    // No CUDA driver (a host-only process) or no pinnable memory left: pageable
-    // memory holds the same data, copies are just slower.
-    cudaGetLastError();
-    pinned = false;
-    p = std::malloc(bytes);
-    if (!p) {
-      fail(POLAR_B200_ERR_CUDA, "host allocation failed");
-      return;
-    }
+  void* p = allocHost(bytes, &pinned);
+  if (!p) {
+    fail(POLAR_B200_ERR_CUDA, "host allocation failed");
+    return;
   }
-  mHost[record.virtualAddress] = HostBlock{p, bytes, 0, pinned};
+  HostBlock& hb = mHost[record.virtualAddress];
+  hb.ptr = p;
+  hb.size = bytes;
+  hb.tag = 0;
+  hb.pinned = pinned;
 }
 
 void PoolBackendAllocator::updateHost(const MemoryRecord& record) {
@@ -90,6 +114,7 @@ void PoolBackendAllocator::updateHost(const MemoryRecord& record) {
   ensureHost(record);
   auto hit = mHost.find(record.virtualAddress);
   if (hit == mHost.end() || hit->second.tag == e.tag) return;
+  hit->second.reading.settle();   // nothing may still be reading the buffer that is about to be refilled
   for (auto& l : mLayers) {
     if (l.layer->isAllocated(record) && l.layer->getTag(record) == e.tag) {
       l.device->copyToHost(record, hit->second.ptr);   // synchronises that device's stream
@@ -179,13 +204,21 @@ void PoolBackendAllocator::lock(const MemoryRecord& record, Device& device, Lock
     if (!host_has)
       for (auto& o : mLayers)
         if (&o != l && o.layer->isAllocated(record) && o.layer->getTag(record) == e.tag) src = &o;
+    B200Device* cuda = asB200(device);
     if (host_has) {
-      device.copyToDevice(record, hit->second.ptr);
-    } else if (src && src->device->getProvider() == DeviceProvider::CUDA &&
-               device.getProvider() == DeviceProvider::CUDA) {
-      // CUDA device to CUDA device: a peer copy, no RAM staging
-      cudaMemcpy(l->layer->getPtr(record), src->layer->getPtr(record), record.allocationSize,
-                 cudaMemcpyDefault);
+      // The new version may already be on its way (endOverwrite uploads ahead of use).
+      if (!(cuda && cuda->pool().adoptStaged(record, e.tag))) {
+        device.copyToDevice(record, hit->second.ptr);
+        // From pinned memory that copy is asynchronous: the host block must not be written
+        // or freed before it has run.
+        if (cuda && hit->second.pinned) hit->second.reading.mark(cuda->ordinal(), cuda->stream());
+      }
+    } else if (src && mPeerCopy && mPeerCopy(device, *src->device, record)) {
+      // copied by the installed hook
+    } else if (src && cuda && asB200(*src->device)) {
+      // CUDA device to CUDA device: a peer copy on the destination's stream, ordered after
+      // the producer on the source's stream; no RAM staging, no host wait
+      cuda->copyFromPeer(record, *asB200(*src->device));
     } else if (src) {
       // devices of another provider only promise copyToHost/copyToDevice
       updateHost(record);
@@ -212,9 +245,61 @@ void PoolBackendAllocator::lock(const MemoryRecord& record, LockType type) {
   if (type == LockType::READ_WRITE) {
     e.tag++;
     auto hit = mHost.find(record.virtualAddress);
-    if (hit != mHost.end()) hit->second.tag = e.tag;
+    if (hit != mHost.end()) {
+      hit->second.tag = e.tag;
+      // The caller is about to write this buffer: an upload queued earlier must have read it.
+      hit->second.reading.settle();
+    }
   }
   e.locks.push_back(Lock{type, nullptr});
+}
+
+void* PoolBackendAllocator::beginOverwrite(const MemoryRecord& record) {
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
+  Entry& e = mEntries[record.virtualAddress];
+  if (!e.locks.empty()) {
+    fail(POLAR_B200_ERR_INVALID, "overwrite requested for a record that is locked");
+    return nullptr;
+  }
+  ensureHost(record);
+  auto hit = mHost.find(record.virtualAddress);
+  if (hit == mHost.end()) return nullptr;
+  HostBlock& hb = hit->second;
+  if (hb.reading.pending()) {
+    // An upload is still reading the current buffer: take the other one (the old contents
+    // are not needed), waiting only if that one is being read as well.
+    if (!hb.spare) {
+      bool pinned = hb.pinned;
+      hb.spare = pinned ? allocHost(hb.size, &pinned) : nullptr;
+      if (hb.spare && !pinned) {   // mixed kinds would confuse freeHost: do without a spare
+        std::free(hb.spare);
+        hb.spare = nullptr;
+      }
+    }
+    if (hb.spare) {
+      std::swap(hb.ptr, hb.spare);
+      std::swap(hb.reading, hb.spareReading);
+    }
+    hb.reading.settle();
+  }
+  e.tag++;
+  hb.tag = e.tag;
+  e.locks.push_back(Lock{LockType::READ_WRITE, nullptr});
+  return hb.ptr;
+}
+
+void PoolBackendAllocator::endOverwrite(const MemoryRecord& record) {
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
+  release(record);
+  auto it = mEntries.find(record.virtualAddress);
+  auto hit = mHost.find(record.virtualAddress);
+  if (it == mEntries.end() || hit == mHost.end() || !hit->second.pinned) return;
+  for (auto& l : mLayers) {
+    B200Device* cuda = asB200(*l.device);
+    if (!cuda || !l.layer->isAllocated(record)) continue;
+    if (cuda->pool().stage(record, hit->second.ptr, it->second.tag, nullptr))
+      hit->second.reading.mark(cuda->ordinal(), cuda->uploadStream());
+  }
 }
 
 void PoolBackendAllocator::lock(const TensorInternal& tensor, Device& device, LockType type) {

@@ -13,6 +13,8 @@
 
 #include <polarai/backend/generic/BackendAllocator.hpp>
 
+#include "cuda_api.hpp"
+
 #include <functional>
 #include <mutex>
 #include <unordered_map>
@@ -52,6 +54,22 @@ public:
   void* get(const MemoryRecord& record) override;
   void* get(const TensorInternal& tensor) override;
 
+  // ---- beyond the reference interface ----
+  // Whole-record overwrite from the host (what a loader does): like a host READ_WRITE
+  // lock, except that the old contents are NOT preserved, which lets the record keep TWO
+  // pinned buffers and hand out the one no upload is still reading - the host fills
+  // version v+1 while version v is still crossing PCIe.  endOverwrite() releases the lock
+  // and starts uploading the new version to every CUDA device that holds the record, on
+  // that device's upload stream and into a fresh block, so that the copy overlaps kernels
+  // still reading the old version; the next device lock adopts the fresh block.
+  void* beginOverwrite(const MemoryRecord& record);
+  void endOverwrite(const MemoryRecord& record);
+  // Device-to-device refresh used when both devices are CUDA devices of this plugin;
+  // replaceable so that host-only tests can observe the choice.  Returns false when it
+  // did not do the copy (the allocator then stages through host memory).
+  using PeerCopyFn = std::function<bool(Device& dst, Device& src, const MemoryRecord&)>;
+  void setPeerCopy(PeerCopyFn fn) { mPeerCopy = std::move(fn); }
+
   // Error state (the reference terminates the process instead).
   int lastStatus() const { return mStatus; }
   const char* lastError() const { return mError; }
@@ -62,8 +80,20 @@ protected:
   void* getImpl(const MemoryRecord& record, Device& device) override;
 
 private:
-  struct HostBlock { void* ptr; size_t size; size_t tag; bool pinned; };
+  // Host copy of a record.  `ptr` is the current buffer; `spare` a second one that
+  // beginOverwrite() alternates with (allocated on first need).  `reading` / `spareReading`
+  // track asynchronous uploads that may still be reading the respective buffer: the host
+  // must not write or free a buffer before they have run.
+  struct HostBlock {
+    void* ptr = nullptr;
+    size_t size = 0;
+    size_t tag = 0;
+    bool pinned = false;
+    void* spare = nullptr;
+    PendingRead<CudaApi> reading, spareReading;
+  };
   static void freeHost(HostBlock& b);
+  static void* allocHost(size_t bytes, bool* pinned);
   struct Lock { LockType type; Device* device; };  // device == nullptr: host
   struct Entry {
     size_t tag = 1;                       // newest version of the record
@@ -81,6 +111,7 @@ private:
   std::unordered_map<size_t, HostBlock> mHost;
   std::unordered_map<size_t, Entry> mEntries;
   TensorToRecord mToRecord;
+  PeerCopyFn mPeerCopy;
   std::recursive_mutex mMutex;
   int mStatus = 0;
   const char* mError = "";

@@ -58,6 +58,13 @@ int fail(polar_b200_rt* rt, int status, const std::string& msg) {
   if (rt) rt->error = msg;
   return status;
 }
+// After a synchronisation point: did a bounded device-side wait give up on that GPU?
+int device_wait_status(polar_b200_rt* rt, B200Device* d) {
+  if (int code = polar_b200_device_status_of(d->ordinal()))
+    return fail(rt, POLAR_B200_ERR_TIMEOUT, d->getDeviceName() + ": a bounded device-side wait gave up (code " +
+                                                std::to_string(code) + ")");
+  return POLAR_B200_OK;
+}
 int allocator_status(polar_b200_rt* rt) {
   int s = rt->allocator->lastStatus();
   if (s) {
@@ -113,16 +120,25 @@ int polar_b200_rt_deallocate(polar_b200_rt* rt, uint64_t va, uint64_t bytes) {
 int polar_b200_rt_write(polar_b200_rt* rt, uint64_t va, uint64_t bytes, const void* src) {
   if (!rt || (!src && bytes)) return fail(rt, POLAR_B200_ERR_INVALID, "null source");
   MemoryRecord rec{va, bytes};
-  rt->allocator->lock(rec, LockType::READ_WRITE);
+  void* host = rt->allocator->beginOverwrite(rec);
   if (int s = allocator_status(rt)) return s;
-  void* host = rt->allocator->get(rec);
-  if (!host) {
-    rt->allocator->release(rec);
-    return fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
-  }
+  if (!host) return fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
   big_memcpy(host, src, bytes);
-  rt->allocator->release(rec);
-  return POLAR_B200_OK;
+  rt->allocator->endOverwrite(rec);   // the upload to the devices that hold the record starts here
+  return allocator_status(rt);
+}
+
+int polar_b200_rt_host_begin_write(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void** host) {
+  if (!rt || !host) return fail(rt, POLAR_B200_ERR_INVALID, "null handle or result pointer");
+  *host = rt->allocator->beginOverwrite(MemoryRecord{va, bytes});
+  if (int s = allocator_status(rt)) return s;
+  return *host ? POLAR_B200_OK : fail(rt, POLAR_B200_ERR_CUDA, "no host memory for the record");
+}
+
+int polar_b200_rt_host_end_write(polar_b200_rt* rt, uint64_t va, uint64_t bytes) {
+  if (!rt) return POLAR_B200_ERR_INVALID;
+  rt->allocator->endOverwrite(MemoryRecord{va, bytes});
+  return allocator_status(rt);
 }
 
 int polar_b200_rt_read(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void* dst) {
@@ -140,6 +156,8 @@ int polar_b200_rt_read(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void* dst
   for (auto& d : rt->devices) {
     auto* bd = static_cast<B200Device*>(d.get());
     if (int s = bd->takeStatus()) return fail(rt, s, bd->lastError());
+    if (bd->ready())
+      if (int s = device_wait_status(rt, bd)) return s;
   }
   return POLAR_B200_OK;
 }
@@ -194,7 +212,7 @@ int polar_b200_rt_barrier(polar_b200_rt* rt, int device) {
   if (!d) return fail(rt, POLAR_B200_ERR_INVALID, "no such device");
   d->synchronize();
   if (int s = d->takeStatus()) return fail(rt, s, d->lastError());
-  return POLAR_B200_OK;
+  return device_wait_status(rt, d);
 }
 
 void* polar_b200_rt_device_ptr(polar_b200_rt* rt, int device, uint64_t va, uint64_t bytes) {

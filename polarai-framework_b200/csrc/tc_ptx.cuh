@@ -35,18 +35,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
-// Bounded wait.  Returns false when the CTA is aborting.
+// Bounded wait: gives up after `limit_ns` nanoseconds of polling (the host's setting, two
+// seconds unless changed with polar_b200_set_wait_limit_ns), records `code` in the device's
+// status word (the first code wins) and raises the CTA's abort flag.  Returns false when the
+// CTA is aborting.  The clock is read once per 256 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
+  const unsigned long long start = global_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - start > kWaitLimitCycles) {
+      if (global_ns() - start > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

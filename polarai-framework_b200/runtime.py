@@ -45,6 +45,8 @@ RT_SIGNATURES = {
     "polar_b200_rt_allocate": (_i, [_p, _i, _u64, _u64]),
     "polar_b200_rt_deallocate": (_i, [_p, _u64, _u64]),
     "polar_b200_rt_write": (_i, [_p, _u64, _u64, _p]),
+    "polar_b200_rt_host_begin_write": (_i, [_p, _u64, _u64, ctypes.POINTER(_p)]),
+    "polar_b200_rt_host_end_write": (_i, [_p, _u64, _u64]),
     "polar_b200_rt_read": (_i, [_p, _u64, _u64, _p]),
     "polar_b200_rt_launch": (_i, [_p, _i, ctypes.POINTER(LaunchCommand)]),
     "polar_b200_rt_barrier": (_i, [_p, _i]),

@@ -34,6 +34,7 @@ void oracle_frelu(const float* in, float* out, uint64_t n);
 void oracle_fsoftmax(const float* in, float* out, uint64_t n);
 void oracle_fpool(const float* in, uint64_t h, uint64_t w, uint64_t wh, uint64_t ww, uint64_t sh, uint64_t sw, float* out);
 void oracle_fconv2d(const float* in, uint64_t h, uint64_t w, const float* ker, uint64_t kh, uint64_t kw, float* out);
+void oracle_ftranspose(const float* in, uint64_t rows, uint64_t cols, float* out);
 void oracle_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l, const float* r, float* out);
 }
 
@@ -152,6 +153,7 @@ public:
       oracle_fpool(t[0], ti[0]->shape[0], ti[0]->shape[1], iv[1], iv[2], iv[3], iv[4], t[5]);
     else if (name == "fconv2d")
       oracle_fconv2d(t[0], ti[0]->shape[0], ti[0]->shape[1], t[1], ti[1]->shape[0], ti[1]->shape[1], t[2]);
+    else if (name == "ftranspose") oracle_ftranspose(t[0], ti[0]->shape[0], ti[0]->shape[1], t[1]);
     else if (name.rfind("fmatmul_", 0) == 0 && name.size() == 11) {
       int tl = name[8] == 't', tr = name[10] == 't';
       uint64_t m = tl ? ti[0]->shape[1] : ti[0]->shape[0], k = tl ? ti[0]->shape[0] : ti[0]->shape[1];

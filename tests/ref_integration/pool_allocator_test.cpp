@@ -96,3 +96,58 @@ TEST_F(PoolAllocatorTest, DoubleAllocationIsANoOpAndUnknownDevicesAreRefused) {
   alloc.allocate(r, stranger);
   EXPECT_TRUE_(alloc.lastStatus() != 0);
 }
+
+TEST_F(PoolAllocatorTest, DeviceToDeviceRefreshGoesThroughThePeerCopyNotThroughRam) {
+  // The CUDA plugin copies device to device on the destination's stream, ordered after the
+  // producer; the allocator's part is to choose that path with the right pair of devices.
+  MemoryRecord r{300, 8 * sizeof(float)};
+  int calls = 0;
+  std::string route;
+  alloc.setPeerCopy([&](Device& dst, Device& src, const MemoryRecord& rec) {
+    ++calls;
+    route = src.getDeviceName() + "->" + dst.getDeviceName();
+    std::memcpy(dst.getAllocator()->getPtr(rec), src.getAllocator()->getPtr(rec), rec.allocationSize);
+    return true;
+  });
+  alloc.allocate(r, devA);
+  alloc.lock(r, devA, LockType::READ_WRITE);
+  for (int i = 0; i < 8; ++i) ptr(alloc, r, devA)[i] = 3.0f + i;
+  alloc.release(r, devA);
+  alloc.lock(r, devB, LockType::READ);
+  EXPECT_TRUE_(calls == 1 && route == "fake-gpu-0->fake-gpu-1");
+  for (int i = 0; i < 8; ++i) EXPECT_FLOAT_EQ(ptr(alloc, r, devB)[i], 3.0f + i);
+  alloc.release(r, devB);
+  EXPECT_TRUE_(alloc.get(r) == nullptr);               // no host copy was ever made
+  // a hook that declines leaves the staging path through host memory in charge
+  alloc.setPeerCopy([&](Device&, Device&, const MemoryRecord&) { ++calls; return false; });
+  alloc.lock(r, devB, LockType::READ_WRITE);
+  for (int i = 0; i < 8; ++i) ptr(alloc, r, devB)[i] = -2.0f * i;
+  alloc.release(r, devB);
+  alloc.lock(r, devA, LockType::READ);
+  EXPECT_TRUE_(calls == 2);
+  for (int i = 0; i < 8; ++i) EXPECT_FLOAT_EQ(ptr(alloc, r, devA)[i], -2.0f * i);
+  alloc.release(r, devA);
+  EXPECT_TRUE_(alloc.lastStatus() == 0);
+}
+
+TEST_F(PoolAllocatorTest, OverwriteReplacesTheRecordAndRespectsLocks) {
+  MemoryRecord r{400, 4 * sizeof(float)};
+  alloc.allocate(r, devA);
+  for (int version = 1; version <= 3; ++version) {
+    auto* h = static_cast<float*>(alloc.beginOverwrite(r));
+    EXPECT_TRUE_(h != nullptr);
+    for (int i = 0; i < 4; ++i) h[i] = 10.0f * version + i;
+    alloc.endOverwrite(r);
+    alloc.lock(r, devA, LockType::READ);                 // the device sees each new version
+    for (int i = 0; i < 4; ++i) EXPECT_FLOAT_EQ(ptr(alloc, r, devA)[i], 10.0f * version + i);
+    alloc.release(r, devA);
+  }
+  alloc.lock(r, devA, LockType::READ);
+  EXPECT_TRUE_(alloc.beginOverwrite(r) == nullptr);      // locked on a device: refused, not aborted
+  EXPECT_TRUE_(alloc.lastStatus() != 0);
+  alloc.clearError();
+  alloc.release(r, devA);
+  EXPECT_TRUE_(alloc.beginOverwrite(r) != nullptr);
+  alloc.endOverwrite(r);
+  EXPECT_TRUE_(alloc.lastStatus() == 0);
+}

@@ -223,17 +223,71 @@ def test_linearity_at_8192(gpu):
     assert d.device_status() == 0
 
 
+@pytest.mark.parametrize("tl,tr", [(0, 0), (1, 1)])
+def test_full_compare_at_2048(gpu, par_oracle, tl, tr):
+    # every entry of a 2048^3 product against the double-accumulated oracle
+    m = n = k = 2048
+    rng = np.random.default_rng(2048 + 2 * tl + tr)
+    l, r = operands(rng, tl, tr, m, n, k)
+    ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
+    got = gpu.fmatmul(tl, tr, l, r)
+    err = rel_err(got, ref, mag)
+    assert err <= TOL and err <= 5e-6, err
+    assert gpu.d.device_status() == 0
+
+
 @pytest.mark.parametrize("tl,tr", [(0, 0), (0, 1), (1, 0), (1, 1)])
-def test_cta_pair_kernel(gpu, par_oracle, tl, tr):
-    # the experimental cta_group::2 kernel: two CTAs per 256 x 256 tile
+def test_8192_sampled_against_f64(gpu, par_oracle, tl, tr):
+    # 8192^3 in the configuration the dispatch picks (256 x 256 tiles): 4096 seeded entries,
+    # 4 full rows and 4 full columns (first and last included) against double dot products
     import torch
-    for (m, n, k, splits) in ((256, 256, 64, 1), (200, 300, 100, 1), (1300, 1028, 520, 1), (1024, 512, 2048, 4)):
-        rng = np.random.default_rng(m + n + k + 2 * tl + tr)
+    m = n = k = 8192
+    torch.manual_seed(8192 + tl * 2 + tr)
+    L = torch.empty((k, m) if tl else (m, k), device="cuda").uniform_(-1, 1)
+    R = torch.empty((n, k) if tr else (k, n), device="cuda").uniform_(-1, 1)
+    out = torch.empty((m, n), device="cuda")
+    gpu.d.fmatmul(tl, tr, L, R, out)
+    torch.cuda.synchronize()
+    assert gpu.d.device_status() == 0
+    l, r, got = L.cpu().numpy(), R.cpu().numpy(), out.cpu().numpy()
+    del L, R, out
+    rng = np.random.default_rng(2)
+    rows = rng.integers(0, m, 4096).astype(np.uint64)
+    cols = rng.integers(0, n, 4096).astype(np.uint64)
+    fr = np.array([0, m - 1] + list(rng.integers(0, m, 2)), np.uint64)
+    fc = np.array([0, n - 1] + list(rng.integers(0, n, 2)), np.uint64)
+    rows = np.concatenate([rows, np.repeat(fr, n), np.tile(np.arange(m, dtype=np.uint64), 4)])
+    cols = np.concatenate([cols, np.tile(np.arange(n, dtype=np.uint64), 4), np.repeat(fc, m)])
+    ref, mag = par_oracle.fmatmul_entries_f64(tl, tr, l, r, rows, cols)
+    g = got[rows.astype(np.int64), cols.astype(np.int64)].astype(np.float64)
+    err = float(np.max(np.abs(g - ref) / mag))
+    assert err <= TOL and err <= 1e-5, err
+
+
+def test_result_that_is_only_4_byte_aligned(gpu, par_oracle):
+    # `out` one float past a 16-byte boundary, on shapes whose k range is cut into work units
+    # (fixed cuts: the partial products are summed by a second kernel; stream mode: slots) and
+    # on the whole-tile path: every store to the result must fall back to 4-byte stores
+    import torch
+    d = gpu.d
+    for (tl, tr, m, n, k, splits) in ((0, 1, 512, 512, 4096, 4), (1, 0, 512, 256, 8192, 8), (0, 0, 640, 512, 2048, -1),
+                                      (0, 0, 384, 512, 512, 1)):
+        rng = np.random.default_rng(m + n + k)
         l, r = operands(rng, tl, tr, m, n, k)
         ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
         L, R = torch.from_numpy(l).cuda(), torch.from_numpy(r).cuda()
-        out = torch.full((m, n), float("nan"), device="cuda")
-        gpu.d.fmatmul_tc_pair(tl, tr, L, R, out, splits=splits)
+        for tile_n in (256, 512):
+            base = torch.full((m * n + 8,), float("nan"), device="cuda")
+            out = base[1:1 + m * n].view(m, n)
+            assert out.data_ptr() % 16 == 4
+            d.fmatmul_tc(tl, tr, L, R, out, tile_n=tile_n, slab_k=16, splits=splits)
+            torch.cuda.synchronize()
+            assert d.device_status() == 0
+            assert rel_err(out.cpu().numpy(), ref, mag) <= 5e-6, (m, n, k, splits, tile_n)
+            assert bool(torch.isnan(base[0])) and bool(torch.isnan(base[1 + m * n:]).all())   # nothing outside
+        # and through the dispatch, which plans the cuts itself
+        base = torch.full((m * n + 8,), float("nan"), device="cuda")
+        out = base[1:1 + m * n].view(m, n)
+        d.fmatmul(tl, tr, L, R, out)
         torch.cuda.synchronize()
-        assert gpu.d.device_status() == 0
         assert rel_err(out.cpu().numpy(), ref, mag) <= 5e-6

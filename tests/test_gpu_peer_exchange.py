@@ -79,6 +79,57 @@ def test_bad_arguments_are_statuses():
     peers.close()
 
 
+def test_a_peer_that_never_arrives_is_a_timeout_status_and_leaves_the_weights_alone():
+    # One GPU, one launch: this rank is told it has a peer (a second buffer on the same GPU that
+    # nothing ever signals).  With the wait limit set to 50 ms the kernel gives up on "ready",
+    # skips the sum, never publishes "done", gives up on that too, and ends without touching W.
+    # The status word says 301, the status check returns POLAR_B200_ERR_TIMEOUT, and after
+    # a clear the library works as before.  Nothing here traps, faults or waits without a bound.
+    import time
+    import torch
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    from polarai_framework_b200.capi import PolarB200Error
+    from polarai_framework_b200.peer_gradients import CONTROL_BYTES, PeerGradients
+    lib = pkg.lib()
+    c = lib.cdll
+    c.polar_b200_device_status_clear()
+    assert c.polar_b200_wait_limit_ns() == 0
+    mine = PeerGradients({"g": (1 << 16,)}, 0, 1, "cuda:0")
+    silent = ctypes.c_void_p()
+    lib.check(c.polar_b200_peer_alloc(mine.n * 4, ctypes.byref(silent)))
+    try:
+        w = torch.full((1 << 16,), 1.0, device="cuda")
+        mine.tensors["g"].fill_(3.0)
+        seg = mine.segments([(w, "g")])
+        buffers = (ctypes.c_void_p * 2)(mine.own, silent.value)
+        st = torch.cuda.current_stream().cuda_stream
+        c.polar_b200_set_wait_limit_ns(50_000_000)
+        t0 = time.perf_counter()
+        assert c.polar_b200_allreduce_fadd(buffers, 0, 2, mine.n, seg, 1, 1.0, -0.5, st) == 0   # the launch itself is fine
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+        assert 0.09 <= elapsed < 2.0, elapsed                       # two waits of 50 ms, not the 4 s default
+        assert c.polar_b200_device_status() == 301 and c.polar_b200_device_status_of(0) == 301
+        assert c.polar_b200_check_device_status() == 4                 # POLAR_B200_ERR_TIMEOUT
+        assert "301" in lib.last_error()
+        with pytest.raises(PolarB200Error) as err:
+            lib.call("polar_b200_check_device_status")
+        assert err.value.status == 4
+        assert bool(torch.all(w == 1.0))                               # no update from a sum that never completed
+        assert bool(torch.all(mine.tensors["g"] == 3.0))               # and the gradient is as it was
+    finally:
+        c.polar_b200_set_wait_limit_ns(0)
+        c.polar_b200_device_status_clear()
+    assert c.polar_b200_check_device_status() == 0
+    # the context is intact: a one-rank step on the same buffer works (its step counter moved on)
+    assert c.polar_b200_allreduce_fadd(buffers, 0, 1, mine.n, seg, 1, 1.0, -0.5, st) == 0
+    torch.cuda.synchronize()
+    assert bool(torch.all(w == -0.5)) and c.polar_b200_device_status() == 0
+    c.polar_b200_peer_free(silent)
+    mine.close()
+
+
 def _rank_main(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",

@@ -146,3 +146,120 @@ def test_mlp_program_through_the_plugin_equals_the_direct_executor(rtb):
         for k in prog.outputs:
             assert np.array_equal(bits(direct.output(k)), bits(plugin.output(k))), k
         plugin.close()
+
+
+def _cuda_current_device():
+    """The calling thread's current device as the CUDA runtime torch uses reports it."""
+    import ctypes
+    import torch
+    cur = ctypes.c_int(-1)
+    for name in ("libcudart.so.12", "libcudart.so"):
+        try:
+            rc = ctypes.CDLL(name).cudaGetDevice(ctypes.byref(cur))
+        except OSError:
+            continue
+        assert rc == 0
+        assert cur.value == torch.cuda.current_device()
+        return cur.value
+    return torch.cuda.current_device()
+
+
+def test_write_launch_write_again_keeps_the_first_launch_input(rtb):
+    # A host write returns before the upload of the previous version has necessarily run (the
+    # upload is asynchronous, from pinned memory): the second write must not disturb what the
+    # first launch reads.  Large enough that the copies take milliseconds.
+    rt = rtb.rt
+    n = 16 << 20
+    v1 = np.arange(n, dtype=np.float32)
+    v2 = -v1
+    x, a, b = rt.tensor((n,)), rt.tensor((n,)), rt.tensor((n,))
+    for _ in range(3):                                     # repeated: buffers alternate
+        rt.write(x, v1)
+        rt.launch("fcopy", [x, a])
+        rt.write(x, v2)
+        rt.launch("fcopy", [x, b])
+        assert np.array_equal(rt.read(a), v1)
+        assert np.array_equal(rt.read(b), v2)
+    # in-place production through the record's own pinned buffer
+    import ctypes
+    host = ctypes.c_void_p()
+    rt._check(rt.cdll.polar_b200_rt_host_begin_write(rt.h, x.virt_addr, x.bytes, ctypes.byref(host)))
+    np.ctypeslib.as_array(ctypes.cast(host, ctypes.POINTER(ctypes.c_float)), (n,))[:] = 7.0
+    rt._check(rt.cdll.polar_b200_rt_host_end_write(rt.h, x.virt_addr, x.bytes))
+    rt.launch("fcopy", [x, a])
+    assert np.all(rt.read(a) == 7.0)
+    for t in (x, a, b):
+        rt.free(t)
+
+
+def test_read_waits_for_the_writer_of_the_record_not_for_later_launches(rtb):
+    # the value read is the one the record had when read() was called, whatever was queued
+    # for OTHER records afterwards
+    rt = rtb.rt
+    n = 8 << 20
+    s, big1, big2 = rt.tensor((4,)), rt.tensor((n,)), rt.tensor((n,))
+    rt.launch("ffill", [1.5, big1])
+    rt.launch("ffill", [2.5, s])
+    for _ in range(20):                                    # work queued behind the writer of `s`
+        rt.launch("fcopy", [big1, big2])
+    assert np.all(rt.read(s) == 2.5)
+    assert np.all(rt.read(big2) == 1.5)
+    for t in (s, big1, big2):
+        rt.free(t)
+
+
+def test_plugin_leaves_the_callers_device_alone():
+    # A host that enumerates all GPUs through the plugin, computes on the LAST one and closes
+    # must find its own current device unchanged after every call: the reference's driver
+    # calls initContext() on the host's thread (RuntimeDriver.cpp:39-50) and a changed device
+    # makes the host's next launch run on the wrong GPU.
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import __graft_entry__ as ge
+    ge.load_package()
+    from polarai_framework_b200.runtime import Runtime
+    torch.cuda.set_device(0)
+    mine = torch.ones(1024, device="cuda:0")
+    assert _cuda_current_device() == 0
+    rt = Runtime()
+    assert _cuda_current_device() == 0
+    last = rt.device_count() - 1
+    assert last >= 1
+    t = rt.tensor((1 << 16,), device=last)
+    assert _cuda_current_device() == 0
+    rt.launch("ffill", [3.0, t], device=last)
+    assert _cuda_current_device() == 0
+    assert np.all(rt.read(t) == 3.0)
+    assert _cuda_current_device() == 0
+    rt.barrier(last)
+    rt.free(t)
+    rt.close()
+    assert _cuda_current_device() == 0
+    assert float((mine * 2).sum().item()) == 2048.0      # the host's own tensors still work
+
+
+def test_record_written_on_one_gpu_is_read_on_another():
+    # device-to-device refresh: ordered after the producer kernel on the source GPU's stream
+    # and before the consumer on the destination's, with no host synchronisation in between
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import __graft_entry__ as ge
+    ge.load_package()
+    from polarai_framework_b200.runtime import Runtime
+    rt = Runtime()
+    n = 32 << 20
+    a = rt.tensor((n,), device=0)
+    b = rt.tensor((n,), device=0)
+    out = rt.tensor((n,), device=1)
+    rt.cdll.polar_b200_rt_allocate(rt.h, 1, b.virt_addr, b.bytes)      # the same record, known to GPU 1 as well
+    for k in range(3):
+        rt.launch("ffill", [float(k + 1), a], device=0)
+        rt.launch("fadd", [a, 1.0, a, 1.0, b], device=0)               # b = 2(k+1), produced on GPU 0
+        rt.launch("fadd", [b, 1.0, b, 0.5, out], device=1)             # consumed on GPU 1: 3(k+1)
+        rt.launch("ffill", [-1.0, b], device=0)                        # GPU 0 overwrites b right away
+        assert np.all(rt.read(out) == 3.0 * (k + 1))
+    for t in (a, b, out):
+        rt.free(t)
+    rt.close()

@@ -1,4 +1,4 @@
-"""frelu, fsoftmax, fpool, fconv2d: the oracle against the targets the reference's own
+"""frelu, fsoftmax, fpool, fconv2d, ftranspose, fslice: the oracle against the targets the reference's own
 tests write out (tests/integration/operations/{ReLU,Softmax,Pool2D,Conv2D}Operation.cpp),
 and the CUDA builtins against the oracle."""
 import numpy as np
@@ -38,6 +38,18 @@ def test_oracle_meets_the_reference_targets(oracle):
     assert oracle.frelu(np.array([np.nan, -0.0, 3.0], np.float32)).tolist() == [0.0, 0.0, 3.0]
 
 
+def test_oracle_transpose_and_slice_are_what_numpy_says(oracle):
+    # the reference holds no vector for these two (it names the builtins and leaves the kernels
+    # empty), so the restatement is checked against the definitions themselves
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((37, 53)).astype(np.float32)
+    a[0, 0], a[1, 2] = np.nan, -0.0
+    assert np.array_equal(oracle.ftranspose(a).view(np.uint32), np.ascontiguousarray(a.T).view(np.uint32))
+    t = rng.standard_normal((5, 7, 3)).astype(np.float32)
+    for i in (0, 2, 4):
+        assert np.array_equal(oracle.fslice(t, i), t[i])
+
+
 @pytest.fixture(scope="module")
 def gpu():
     import __graft_entry__ as ge
@@ -67,6 +79,24 @@ def test_cuda_against_oracle_on_seeded_inputs(gpu, oracle):
     for kshape in ((3, 3), (5, 1), (1, 7), (67, 131)):
         ker = rng.uniform(-1, 1, kshape).astype(np.float32)
         assert np.array_equal(gpu.fconv2d(img, ker).view(np.uint32), oracle.fconv2d(img, ker).view(np.uint32))
+
+
+@pytest.mark.gpu
+def test_transpose_and_slice_against_oracle(gpu, oracle):
+    rng = np.random.default_rng(6)
+    for shape in ((1, 1), (32, 32), (33, 31), (1, 1000), (1000, 1), (257, 4099), (4096, 10)):
+        a = rng.standard_normal(shape).astype(np.float32)
+        a.ravel()[:2] = [np.nan, -0.0][:a.size]
+        assert np.array_equal(gpu.ftranspose(a).view(np.uint32), oracle.ftranspose(a).view(np.uint32)), shape
+    t = rng.standard_normal((6, 17, 5)).astype(np.float32)
+    for i in (0, 3, 5):
+        assert np.array_equal(gpu.fslice(t, i).view(np.uint32), oracle.fslice(t, i).view(np.uint32))
+    v = rng.standard_normal((9,)).astype(np.float32)          # a vector slices into scalars
+    assert gpu.fslice(v, 4).reshape(()) == v[4]
+    import torch
+    from polarai_framework_b200.capi import PolarB200Error
+    with pytest.raises(PolarB200Error):
+        gpu.d.fslice(torch.zeros((3, 4), device="cuda"), 3, torch.zeros(4, device="cuda"))   # index out of range
 
 
 @pytest.mark.gpu

@@ -107,7 +107,7 @@ def test_pool_backend_allocator_host_logic():
     # coherence, lock conflicts and error statuses of the BackendAllocator, with fake devices (no CUDA needed)
     out = subprocess.run([ALLOC_TEST], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stdout + out.stderr
-    assert "4 ran, 0 failed, 0 skipped" in out.stdout
+    assert "6 ran, 0 failed, 0 skipped" in out.stdout
 
 
 @pytest.mark.skipif(not os.path.exists(PARITY), reason="autograd parity binary is not built")
