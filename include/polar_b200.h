@@ -37,7 +37,9 @@ typedef enum polar_b200_status {
   POLAR_B200_ERR_INVALID = 1,     /* null pointer, bad flag, size overflow */
   POLAR_B200_ERR_CUDA = 2,        /* a CUDA call failed; see polar_b200_last_error */
   POLAR_B200_ERR_UNSUPPORTED = 3, /* unknown kernel name or argument pattern */
-  POLAR_B200_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up */
+  POLAR_B200_ERR_TIMEOUT = 4,     /* a bounded wait gave up: a device-side wait (see
+                                     polar_b200_check_device_status) or a collective's
+                                     time limit on the host */
   POLAR_B200_ERR_WORKSPACE = 5    /* caller's workspace is too small */
 } polar_b200_status;
 
@@ -305,6 +307,16 @@ int polar_b200_fmatmul_sigmoid_grad(int transLeft, int transRight, uint64_t m,
  * elementwise flogloss output; the reference has no reduction builtin. */
 int polar_b200_fsum(const float* in, double* sum, uint64_t n, void* stream);
 
+/* The same as an extended builtin with a tensor result, "fsum" (T in, T out): out[0] =
+ * (float) of the sum accumulated in double; one partial sum per CTA in scratch, added in a
+ * fixed order by a second small kernel, so the result is the same bits run to run.  Lets a
+ * host that drives the runtime plugin read a loss back as 4 bytes instead of the whole loss
+ * tensor.  Scratch: polar_b200_fsum_f32_workspace_bytes(n) bytes, 8-byte aligned (NULL: the
+ * stream-ordered pool). */
+int polar_b200_fsum_f32(const float* in, float* out, uint64_t n, void* workspace,
+                        uint64_t workspace_bytes, void* stream);
+uint64_t polar_b200_fsum_f32_workspace_bytes(uint64_t n);
+
 /* ---- dispatch by native kernel name -------------------------------------- */
 
 typedef struct polar_b200_tensor {
@@ -325,7 +337,7 @@ typedef struct polar_b200_arg {
  * Transpose all "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own
  * here), and
  * the extended "fsigmoid_grad", "fsigmoid_logloss_grad", "fmatmul_x_y_sigmoid",
- * "fmatmul_x_y_sigmoid_grad".
+ * "fmatmul_x_y_sigmoid_grad", "fsum".
  *
  * Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
  * on arguments in LaunchCommand order; this is what Device::launch forwards to

@@ -75,6 +75,24 @@ int polar_b200_rt_host_end_write(polar_b200_rt* rt, uint64_t virtAddr, uint64_t 
  * last wrote the record - not for launches queued after it), copy out, release. */
 int polar_b200_rt_read(polar_b200_rt* rt, uint64_t virtAddr, uint64_t bytes, void* dst);
 
+/* Makes device memory the caller owns the record's copy on `device` (the runtime never
+ * frees or moves it): for tensors that must live in special memory, such as the weight
+ * gradients of a data-parallel step in NVLink peer memory (polar_b200_peer_alloc). */
+int polar_b200_rt_adopt(polar_b200_rt* rt, int device, uint64_t virtAddr, uint64_t bytes, void* device_ptr);
+
+/* The gradient exchange of a data-parallel step as a runtime call: polar_b200_allreduce_fadd
+ * (polar_b200.h) on the device's stream, with the weights named as records - each is locked
+ * READ_WRITE for the launch like a builtin's output, so other copies of it become stale.
+ * No counterpart in the reference (one device, no collective: ExecutorImpl.cpp:71-75). */
+typedef struct polar_b200_rt_update {
+  uint64_t weight_va;    /* record of one weight tensor (count floats) */
+  uint64_t grad_offset;  /* where its gradient starts in the peer payload, in floats */
+  uint64_t count;
+} polar_b200_rt_update;
+int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, uint32_t rank,
+                                 uint32_t world, uint64_t n, const polar_b200_rt_update* updates,
+                                 uint32_t n_updates, float scale_w, float scale_g);
+
 /* One builtin: READ_WRITE lock on the last tensor argument, READ locks on the
  * others (as the operations' gen() methods emit), Device::launch, release.
  * The launch is asynchronous; errors of the launch itself are returned. */

@@ -66,6 +66,8 @@ SIGNATURES = {
     "polar_b200_set_wait_limit_ns": (None, [_u64]),
     "polar_b200_wait_limit_ns": (_u64, []),
     "polar_b200_fsum": (_i, [_p, _p, _u64, _p]),
+    "polar_b200_fsum_f32": (_i, [_p, _p, _u64, _p, _u64, _p]),
+    "polar_b200_fsum_f32_workspace_bytes": (_u64, [_u64]),
     "polar_b200_peer_alloc": (_i, [_u64, ctypes.POINTER(_p)]),
     "polar_b200_peer_free": (_i, [_p]),
     "polar_b200_peer_export": (_i, [_p, ctypes.POINTER(ctypes.c_ubyte)]),

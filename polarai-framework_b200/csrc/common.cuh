@@ -57,6 +57,14 @@ public:
       return;
     }
     if (stream && stream != (void*)cudaStreamLegacy && stream != (void*)cudaStreamPerThread) {
+      // A stream under capture is left alone (only the capture-status query is allowed on it
+      // without risk to the capture): whoever captures has made the stream's device current.
+      cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(as_stream(stream), &capturing) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+      }
+      if (capturing != cudaStreamCaptureStatusNone) return;
       if (cudaStreamGetDevice(as_stream(stream), &want) != cudaSuccess) {
         cudaGetLastError();
         return;

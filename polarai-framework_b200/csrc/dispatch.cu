@@ -150,6 +150,11 @@ uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t
 }
 
 uint64_t polar_b200_launch_workspace_bytes(const char* name, const polar_b200_arg* a, uint64_t argc) {
+  if (name && a && !std::strcmp(name, "fsum") && argc == 2 && a[0].is_tensor && (!a[0].tensor.dims || a[0].tensor.shape)) {
+    uint64_t n = 1;
+    for (uint64_t d = 0; d < a[0].tensor.dims; ++d) n *= a[0].tensor.shape[d];
+    return polar_b200_fsum_f32_workspace_bytes(n);
+  }
   if (!name || !a || std::strncmp(name, "fmatmul_", 8) || std::strlen(name) < 11 || argc < 3) return 0;
   const char* suffix = name + 11;
   const int fused = !*suffix ? 0 : !std::strcmp(suffix, "_sigmoid") ? 1 : !std::strcmp(suffix, "_sigmoid_grad") ? 2 : -1;
@@ -385,6 +390,11 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     if (kh > h || kw > w || a[2].tensor.shape[0] != h - kh + 1 || a[2].tensor.shape[1] != w - kw + 1)
       return fail(bad_args, "fconv2d: shapes do not agree");
     return polar_b200_fconv2d(a[0].tensor.data, h, w, a[1].tensor.data, kh, kw, a[2].tensor.data, stream);
+  }
+  if (!std::strcmp(name, "fsum")) {
+    if (!pattern("TT") || numel(a[1].tensor) < 1) return fail(bad_args, "fsum expects (T in, T out[1])");
+    return polar_b200_fsum_f32(a[0].tensor.data, a[1].tensor.data, numel(a[0].tensor), workspace, workspace_bytes,
+                               stream);
   }
   if (!std::strcmp(name, "ftranspose")) {
     if (!pattern("TT") || a[0].tensor.dims != 2 || a[1].tensor.dims != 2 ||

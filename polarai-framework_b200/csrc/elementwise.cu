@@ -52,10 +52,31 @@ struct SigmoidOp {
   }
 };
 struct LogLossOp {
+  // out = fl(fl(-y * log(p + eps)) - fl((1 - y) * log(1 - p + eps))), eps = 1e-5.
+  // Two full-precision logf per element make the kernel issue-bound rather than HBM-bound.
+  // For a label that is exactly 0 or 1 - what LogLoss is fed - one of the two products is a
+  // signed zero whatever its logarithm is (as long as that logarithm is finite), so only the
+  // other logarithm is computed; the zero gets the sign the product would have had
+  // (log x < 0 for x < 1, +0 at x = 1).  Same bits as the two-logarithm form, half the
+  // arithmetic.  Any other label, or an argument whose logarithm is not finite (<= 0, inf,
+  // NaN, where 0 * log is NaN), takes the general form.
   __device__ __forceinline__ float operator()(float p, float y) const {
     const float eps = 1e-5f;
-    float t0 = __fmul_rn(-y, logf(__fadd_rn(p, eps)));
-    float t1 = __fmul_rn(__fadd_rn(1.0f, -y), logf(__fadd_rn(__fadd_rn(1.0f, -p), eps)));
+    const float a0 = __fadd_rn(p, eps);
+    const float a1 = __fadd_rn(__fadd_rn(1.0f, -p), eps);
+    const float w0 = -y, w1 = __fadd_rn(1.0f, -y);       // the two weights
+    const bool one = (y == 1.0f), zero = (y == 0.0f);
+    const float other = one ? a1 : a0;                     // the argument whose product is a zero
+    if ((one || zero) && other > 0.0f && other < __int_as_float(0x7f800000)) {
+      const float l = logf(one ? a0 : a1);
+      // stand-in with the sign of log(other): the product with a zero weight is the same signed zero
+      const float s = other < 1.0f ? -1.0f : (other > 1.0f ? 1.0f : 0.0f);
+      const float t0 = __fmul_rn(w0, one ? l : s);
+      const float t1 = __fmul_rn(w1, one ? s : l);
+      return __fadd_rn(t0, -t1);
+    }
+    float t0 = __fmul_rn(w0, logf(a0));
+    float t1 = __fmul_rn(w1, logf(a1));
     return __fadd_rn(t0, -t1);
   }
 };
@@ -214,6 +235,42 @@ sum_kernel(const float* in, double* sum, uint64_t n, int vec_ok) {
   }
 }
 
+// fsum as a builtin with a tensor result: stage 1 leaves one double per CTA in scratch, stage 2
+// (one CTA) adds them in index order and stores the rounded float - the same bits run to run.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+sum_partials_kernel(const float* in, double* partials, uint64_t n, int vec_ok) {
+  double acc = 0.0;
+  const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+  if (vec_ok) {
+    const uint64_t nvec = n >> 2;
+    const float4* v = reinterpret_cast<const float4*>(in);
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += stride) {
+      float4 x = ld_stream(v + i);
+      acc += (double)((x.x + x.y) + (x.z + x.w));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) acc += (double)in[(nvec << 2) + threadIdx.x];
+  } else {
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) acc += (double)in[i];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  __shared__ double warp_sums[kThreads / 32];
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double w = 0.0;
+    for (int i = 0; i < kThreads / 32; ++i) w += warp_sums[i];
+    partials[blockIdx.x] = w;
+  }
+}
+__global__ void __launch_bounds__(32) sum_finish_kernel(const double* partials, uint32_t count, float* out) {
+  if (threadIdx.x == 0) {
+    double s = 0.0;
+    for (uint32_t i = 0; i < count; ++i) s += partials[i];
+    out[0] = (float)s;
+  }
+}
+
 // Grid-stride kernels (scalar fallback, fsum): a few CTAs per SM.
 unsigned grid_for(uint64_t work_items, uint64_t per_cta) {
   uint64_t need = (work_items + per_cta - 1) / per_cta;
@@ -320,6 +377,41 @@ int polar_b200_fsum(const float* in, double* sum, uint64_t n, void* stream) {
   unsigned grid = grid_for(vec_ok ? (n >> 2) : n, (uint64_t)kThreads * 8);
   sum_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(in, sum, n, vec_ok);
   return check_launch("fsum");
+}
+
+uint64_t polar_b200_fsum_f32_workspace_bytes(uint64_t n) {
+  // one double per CTA; the grid depends on n alone (not on the pointer's alignment)
+  return (uint64_t)grid_for(n >> 2, (uint64_t)kThreads * 8) * sizeof(double);
+}
+
+int polar_b200_fsum_f32(const float* in, float* out, uint64_t n, void* workspace, uint64_t workspace_bytes,
+                        void* stream) {
+  clear_error();
+  if (!out) return fail(POLAR_B200_ERR_INVALID, "null result pointer");
+  if (n == 0) return polar_b200_ffill(0.0f, out, 1, stream);
+  if (!in) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  LaunchDeviceScope on(stream, in);
+  const int vec_ok = aligned16(in) && n >= 4;
+  const unsigned grid = grid_for(n >> 2, (uint64_t)kThreads * 8);
+  const uint64_t need = (uint64_t)grid * sizeof(double);
+  cudaStream_t st = as_stream(stream);
+  double* partials = static_cast<double*>(workspace);
+  bool own = false;
+  if (!partials) {
+    cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&partials), need, st);
+    if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(fsum partial sums)", e);
+    own = true;
+  } else if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 7)) {
+    return fail(POLAR_B200_ERR_WORKSPACE, "fsum needs 8-byte aligned workspace of polar_b200_fsum_f32_workspace_bytes");
+  }
+  sum_partials_kernel<<<grid, kThreads, 0, st>>>(in, partials, n, vec_ok);
+  int rc = check_launch("fsum_partials");
+  if (rc == POLAR_B200_OK) {
+    sum_finish_kernel<<<1, 32, 0, st>>>(partials, grid, out);
+    rc = check_launch("fsum");
+  }
+  if (own) cudaFreeAsync(partials, st);
+  return rc;
 }
 
 }  // extern "C"

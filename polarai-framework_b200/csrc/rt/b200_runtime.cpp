@@ -73,7 +73,7 @@ void B200Allocator::shutdown() {
     CudaApi::giveEvent(mOwner.ordinal(), kv.second.done);
   }
   for (auto& kv : mBlocks) {
-    cudaFreeAsync(kv.second.ptr, s);
+    if (!kv.second.external) cudaFreeAsync(kv.second.ptr, s);
     CudaApi::giveEvent(mOwner.ordinal(), kv.second.written);
   }
   cudaStreamSynchronize(s);
@@ -93,7 +93,7 @@ bool B200Allocator::evictFor(size_t bytes) {
     size_t va = *mReleased.begin();
     auto it = mBlocks.find(va);
     mReleased.erase(mReleased.begin());
-    if (it == mBlocks.end() || it->second.locks > 0) continue;
+    if (it == mBlocks.end() || it->second.locks > 0 || it->second.external) continue;
     MemoryRecord victim{va, it->second.size};
     if (mOffload) {
       mMutex.unlock();
@@ -158,11 +158,22 @@ void B200Allocator::deallocate(MemoryRecord record) {
   }
   ScopedDevice on(mOwner.ordinal());
   dropStaged(record.virtualAddress);
-  cudaFreeAsync(it->second.ptr, mOwner.stream());
+  if (!it->second.external) {
+    cudaFreeAsync(it->second.ptr, mOwner.stream());
+    mBytes -= it->second.size;
+  }
   CudaApi::giveEvent(mOwner.ordinal(), it->second.written);
-  mBytes -= it->second.size;
   mReleased.erase(record.virtualAddress);
   mBlocks.erase(it);
+}
+
+bool B200Allocator::adoptExternal(const MemoryRecord& record, void* devicePtr) {
+  std::unique_lock<std::mutex> guard(mMutex);
+  if (mDead || !devicePtr || mBlocks.count(record.virtualAddress)) return false;
+  Block b{devicePtr, record.allocationSize, 1, 0, nullptr};
+  b.external = true;
+  mBlocks[record.virtualAddress] = b;
+  return true;
 }
 
 void B200Allocator::lock(MemoryRecord record) {
@@ -224,7 +235,7 @@ bool B200Allocator::stage(const MemoryRecord& record, const void* pinnedSrc, siz
   std::unique_lock<std::mutex> guard(mMutex);
   if (uploaded) *uploaded = nullptr;
   auto it = mBlocks.find(record.virtualAddress);
-  if (mDead || it == mBlocks.end() || it->second.locks > 0 || !pinnedSrc) return false;
+  if (mDead || it == mBlocks.end() || it->second.locks > 0 || it->second.external || !pinnedSrc) return false;
   ScopedDevice on(mOwner.ordinal());
   const size_t va = record.virtualAddress, bytes = it->second.size;
   dropStaged(va);

@@ -81,8 +81,13 @@ public:
   bool stage(const MemoryRecord& record, const void* pinnedSrc, size_t tag, cudaEvent_t* uploaded);
   bool adoptStaged(const MemoryRecord& record, size_t tag);
 
+  // Registers device memory the CALLER owns as the record's block (never freed, evicted or
+  // replaced by this layer): how a gradient that must live in NVLink peer memory becomes a
+  // record that launches can name.  False when the record already exists.
+  bool adoptExternal(const MemoryRecord& record, void* devicePtr);
+
 private:
-  struct Block { void* ptr; size_t size; size_t tag; int locks; cudaEvent_t written; };
+  struct Block { void* ptr; size_t size; size_t tag; int locks; cudaEvent_t written; bool external = false; };
   struct Staged { void* ptr; size_t size; size_t tag; cudaEvent_t done; };
   bool evictFor(size_t bytes);
   bool ensurePool();

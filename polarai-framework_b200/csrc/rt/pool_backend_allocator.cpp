@@ -140,6 +140,17 @@ void PoolBackendAllocator::allocate(const MemoryRecord& record, Device& device) 
   l->layer->setTag(record, ins.second ? ins.first->second.tag : 0);
 }
 
+void PoolBackendAllocator::adoptExternal(const MemoryRecord& record, Device& device, void* devicePtr) {
+  std::unique_lock<std::recursive_mutex> guard(mMutex);
+  DeviceLayer* l = layerOf(device);
+  B200Device* cuda = asB200(device);
+  if (!l || !cuda) return fail(POLAR_B200_ERR_INVALID, "adopt: not a registered CUDA device of this plugin");
+  if (mEntries.count(record.virtualAddress) || !cuda->pool().adoptExternal(record, devicePtr))
+    return fail(POLAR_B200_ERR_INVALID, "adopt: the record exists already, or the pointer is null");
+  auto ins = mEntries.emplace(record.virtualAddress, Entry{});
+  l->layer->setTag(record, ins.first->second.tag);   // this device holds the newest (only) version
+}
+
 void PoolBackendAllocator::allocate(const MemoryRecord& record) {
   std::unique_lock<std::recursive_mutex> guard(mMutex);
   if (mHost.count(record.virtualAddress)) return;

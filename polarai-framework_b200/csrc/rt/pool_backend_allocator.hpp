@@ -67,6 +67,9 @@ public:
   // Device-to-device refresh used when both devices are CUDA devices of this plugin;
   // replaceable so that host-only tests can observe the choice.  Returns false when it
   // did not do the copy (the allocator then stages through host memory).
+  // Makes caller-owned device memory the record's copy on `device` (see
+  // B200Allocator::adoptExternal); the record starts as "newest on that device".
+  void adoptExternal(const MemoryRecord& record, Device& device, void* devicePtr);
   using PeerCopyFn = std::function<bool(Device& dst, Device& src, const MemoryRecord&)>;
   void setPeerCopy(PeerCopyFn fn) { mPeerCopy = std::move(fn); }
 

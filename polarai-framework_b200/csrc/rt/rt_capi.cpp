@@ -10,6 +10,7 @@
 #include <polar_b200_rt.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <thread>
@@ -30,9 +31,15 @@ namespace {
 // A batch of inputs is hundreds of megabytes; one thread copies about 10 GB/s, well below what
 // the upload over PCIe that follows can take.  Large copies are cut over a few threads.
 void big_memcpy(void* dst, const void* src, uint64_t bytes) {
-  constexpr uint64_t kChunk = 8ull << 20;
-  unsigned hw = std::thread::hardware_concurrency();
-  uint64_t parts = std::min<uint64_t>({bytes / kChunk, hw ? hw : 1u, 8u});
+  constexpr uint64_t kChunk = 4ull << 20;
+  // POLAR_B200_COPY_THREADS overrides the number of copying threads (default: the cores, at most 16)
+  static const unsigned limit = [] {
+    const char* e = std::getenv("POLAR_B200_COPY_THREADS");
+    unsigned v = e ? (unsigned)std::strtoul(e, nullptr, 10) : 0u;
+    unsigned hw = std::thread::hardware_concurrency();
+    return v ? v : std::min(hw ? hw : 1u, 16u);
+  }();
+  uint64_t parts = std::min<uint64_t>(bytes / kChunk, limit);
   if (parts <= 1) {
     std::memcpy(dst, src, bytes);
     return;
@@ -204,6 +211,40 @@ int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cm
   // Stream order protects the buffers; the locks can go as soon as the work is queued.
   unlock_all();
   delete evt;
+  return status;
+}
+
+int polar_b200_rt_adopt(polar_b200_rt* rt, int device, uint64_t va, uint64_t bytes, void* device_ptr) {
+  B200Device* d = dev(rt, device);
+  if (!d) return fail(rt, POLAR_B200_ERR_INVALID, "no such device");
+  rt->allocator->adoptExternal(MemoryRecord{va, bytes}, *d, device_ptr);
+  return allocator_status(rt);
+}
+
+int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, uint32_t rank, uint32_t world,
+                                 uint64_t n, const polar_b200_rt_update* updates, uint32_t n_updates, float scale_w,
+                                 float scale_g) {
+  B200Device* d = dev(rt, device);
+  if (!d || (n_updates && !updates) || n_updates > POLAR_B200_MAX_UPDATE_SEGMENTS)
+    return fail(rt, POLAR_B200_ERR_INVALID, "no such device, or a bad update list");
+  // The kernel rewrites every weight record in place: taken READ_WRITE like any builtin's
+  // output, so that host copies and other devices' copies become stale.
+  std::vector<MemoryRecord> locked;
+  polar_b200_update_segment seg[POLAR_B200_MAX_UPDATE_SEGMENTS];
+  auto unlock_all = [&] { for (auto& r : locked) rt->allocator->release(r, *d); };
+  for (uint32_t i = 0; i < n_updates; ++i) {
+    MemoryRecord r{updates[i].weight_va, updates[i].count * sizeof(float)};
+    rt->allocator->lock(r, *d, LockType::READ_WRITE);
+    if (int s = allocator_status(rt)) { unlock_all(); return s; }
+    locked.push_back(r);
+    seg[i].weights = static_cast<float*>(d->getAllocator()->getPtr(r));
+    seg[i].offset = updates[i].grad_offset;
+    seg[i].count = updates[i].count;
+  }
+  int status = polar_b200_allreduce_fadd(buffers, rank, world, n, seg, n_updates, scale_w, scale_g, d->stream());
+  if (status) rt->error = polar_b200_last_error();
+  else for (auto& r : locked) d->pool().markWritten(r);
+  unlock_all();
   return status;
 }
 

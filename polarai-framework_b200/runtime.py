@@ -37,6 +37,10 @@ class LaunchCommand(ctypes.Structure):
                 ("nativeKernelName", ctypes.c_char_p)]
 
 
+class RtUpdate(ctypes.Structure):
+    _fields_ = [("weight_va", _u64), ("grad_offset", _u64), ("count", _u64)]
+
+
 RT_SIGNATURES = {
     "polar_b200_rt_open": (_p, []),
     "polar_b200_rt_close": (None, [_p]),
@@ -49,6 +53,9 @@ RT_SIGNATURES = {
     "polar_b200_rt_host_end_write": (_i, [_p, _u64, _u64]),
     "polar_b200_rt_read": (_i, [_p, _u64, _u64, _p]),
     "polar_b200_rt_launch": (_i, [_p, _i, ctypes.POINTER(LaunchCommand)]),
+    "polar_b200_rt_adopt": (_i, [_p, _i, _u64, _u64, _p]),
+    "polar_b200_rt_allreduce_fadd": (_i, [_p, _i, ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32, _u64,
+                                          ctypes.POINTER(RtUpdate), ctypes.c_uint32, ctypes.c_float, ctypes.c_float]),
     "polar_b200_rt_barrier": (_i, [_p, _i]),
     "polar_b200_rt_device_ptr": (_p, [_p, _i, _u64, _u64]),
     "polar_b200_rt_stream": (_p, [_p, _i]),
@@ -114,6 +121,13 @@ class Runtime:
         self._check(self.cdll.polar_b200_rt_allocate(self.h, device, t.virt_addr, t.bytes))
         return t
 
+    def adopt(self, shape, device_ptr, device=0):
+        """A record whose device copy is memory the caller owns (never freed by the runtime)."""
+        t = Tensor(self._next_va, shape)
+        self._next_va += t.bytes
+        self._check(self.cdll.polar_b200_rt_adopt(self.h, device, t.virt_addr, t.bytes, device_ptr))
+        return t
+
     def free(self, t):
         self._check(self.cdll.polar_b200_rt_deallocate(self.h, t.virt_addr, t.bytes))
 
@@ -126,11 +140,43 @@ class Runtime:
     def write_ptr(self, t, host_ptr):
         self._check(self.cdll.polar_b200_rt_write(self.h, t.virt_addr, t.bytes, host_ptr))
 
+    def host_buffer(self, t):
+        """Begins an in-place write: returns the record's pinned host buffer as a numpy array to
+        fill (the old contents are not preserved); publish() ends the write and starts the upload."""
+        h = _p()
+        self._check(self.cdll.polar_b200_rt_host_begin_write(self.h, t.virt_addr, t.bytes, ctypes.byref(h)))
+        return np.ctypeslib.as_array(ctypes.cast(h, ctypes.POINTER(ctypes.c_float)), (t.numel,)).reshape(t.shape)
+
+    def publish(self, t):
+        self._check(self.cdll.polar_b200_rt_host_end_write(self.h, t.virt_addr, t.bytes))
+
     def read(self, t, out=None):
         if out is None:
             out = np.empty(t.shape, np.float32)
         self._check(self.cdll.polar_b200_rt_read(self.h, t.virt_addr, t.bytes, out.ctypes.data))
         return out
+
+    def command(self, native_name, args, kernel_name=None):
+        """A LaunchCommand built once and launched many times (launch_command): the structs a
+        compiled graph would keep on its stack.  Returns (command, objects to keep alive)."""
+        n = len(args)
+        descs = (ArgDesc * max(1, n))()
+        keep = [descs]
+        for i, a in enumerate(args):
+            if isinstance(a, Tensor):
+                keep.append(a)
+                descs[i] = ArgDesc(0, ctypes.cast(ctypes.pointer(a.info), _p), ArgDesc.TENSOR)
+            else:
+                f = ctypes.c_float(float(a))
+                keep.append(f)
+                descs[i] = ArgDesc(4, ctypes.cast(ctypes.pointer(f), _p), ArgDesc.DATA)
+        cmd = LaunchCommand((kernel_name or ("node_" + native_name)).encode(), n, descs, native_name.encode())
+        return cmd, keep
+
+    def launch_command(self, cmd, device=0):
+        rc = self.cdll.polar_b200_rt_launch(self.h, device, ctypes.byref(cmd))
+        if rc != 0:
+            self._check(rc)
 
     def launch(self, native_name, args, device=0, kernel_name=None):
         """args: Tensor objects and Python floats, in LaunchCommand order."""
@@ -233,27 +279,62 @@ class RuntimeBuiltins:
 class RuntimeProgramExecutor:
     """Runs a builtin Program (program.py) through the device-runtime plugin, the way a PolarAI
     executor drives a runtime: one record per tensor, inputs written from host buffers
-    (ath_load's role: host copy, uploaded when a launch first locks the record on the
-    device), one Device::launch per builtin by native name, outputs read back to the host.
-    Single device; ALLREDUCE steps of a program are no-ops here."""
+    (ath_load's role: host copy into the record's pinned memory, upload started at once on the
+    device's upload stream), one Device::launch per builtin by native name, outputs read back to
+    the host.  The launch commands are built once.
 
-    def __init__(self, program, rt=None, device=0):
+    A program with an ALLREDUCE_FADD op (program.fuse_gradient_exchange) needs `peers`, a
+    PeerGradients built for program.exchanged(): those gradients are adopted as records whose
+    device memory is the rank's NVLink peer buffer, and the op becomes
+    polar_b200_rt_allreduce_fadd.  Plain ALLREDUCE ops are no-ops here (single rank)."""
+
+    def __init__(self, program, rt=None, device=0, peers=None):
         self.program = program
         self.rt = rt or Runtime()
         self.device = device
-        self.t = {name: self.rt.tensor(shape, device) for name, shape in program.tensors.items()}
+        exchanged = program.exchanged()
+        if exchanged and (peers is None or sorted(peers.tensors) != sorted(exchanged)):
+            raise ValueError(f"the program exchanges gradients over peer memory: pass `peers` built for {exchanged}")
+        self.peers = peers if exchanged else None
+        self.t = {}
+        for name, shape in program.tensors.items():
+            if name in exchanged:
+                self.t[name] = self.rt.adopt(shape, peers.tensors[name].data_ptr(), device)
+            else:
+                self.t[name] = self.rt.tensor(shape, device)
         for name, value in program.constants.items():
             self.rt.launch("ffill", [float(value), self.t[name]], device)
+        self._steps = []
+        self._keep = []
+        for kernel, args in program.ops:
+            if kernel == "ALLREDUCE":
+                continue
+            if kernel == "ALLREDUCE_FADD":
+                pairs = [(args[i], args[i + 1]) for i in range(2, len(args), 2)]
+                upd = (RtUpdate * len(pairs))()
+                for u, (w, g) in zip(upd, pairs):
+                    off, count = peers.offsets[g]
+                    u.weight_va, u.grad_offset, u.count = self.t[w].virt_addr, off, count
+                self._steps.append(("exchange", (upd, len(pairs), float(args[0]), float(args[1]))))
+                continue
+            cmd, keep = self.rt.command(kernel, [self.t[a] if isinstance(a, str) else a for a in args])
+            self._keep.append(keep)
+            self._steps.append(("launch", cmd))
 
     def set_inputs(self, **arrays):
         for name, a in arrays.items():
             self.rt.write(self.t[name], a)
 
     def run(self):
-        for kernel, args in self.program.ops:
-            if kernel == "ALLREDUCE":
-                continue
-            self.rt.launch(kernel, [self.t[a] if isinstance(a, str) else a for a in args], self.device)
+        rt, dev = self.rt, self.device
+        for kind, what in self._steps:
+            if kind == "launch":
+                rt.launch_command(what, dev)
+            else:
+                upd, n, sw, sg = what
+                p = self.peers
+                rt._check(rt.cdll.polar_b200_rt_allreduce_fadd(rt.h, dev, p.buffers, p.rank, p.world, p.n, upd, n,
+                                                               sw, sg))
 
     def output(self, name, out=None):
         return self.rt.read(self.t[name], out)

@@ -85,3 +85,48 @@ def test_shard_rows_rejects_uneven_batches():
     assert shard_rows(65536, 3, 8) == (24576, 32768)
     with pytest.raises(ValueError):
         shard_rows(10, 0, 3)
+
+
+def _late_worker(rank, world, port, out_dir):
+    # Two steps.  Rank 1 takes part in the first exchange and then stays away from the second
+    # (it waits, alive, then leaves between steps with nothing in flight).  Rank 0's second
+    # exchange has a one-second limit: it must come back with POLAR_B200_ERR_TIMEOUT, not block.
+    sys.path.insert(0, ROOT)
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import time
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    ge.load_package()
+    from polarai_framework_b200.capi import PolarB200Error
+    from polarai_framework_b200.data_parallel import ERR_TIMEOUT, init_from_env, make_allreduce
+    r, w, _ = init_from_env("gloo", timeout_s=30)
+    allreduce = make_allreduce(w, timeout_s=1.0)
+    g = torch.full((1024,), float(r + 1))
+    allreduce(g)                                           # step 1: both ranks
+    ok_first = bool(torch.all(g == 3.0))
+    result = "no error"
+    if r == 0:
+        t0 = time.perf_counter()
+        try:
+            allreduce(torch.ones(1024))                    # step 2: the peer never joins
+        except PolarB200Error as exc:
+            result = f"status {exc.status} after {time.perf_counter() - t0:.2f}s"
+            assert exc.status == ERR_TIMEOUT
+    else:
+        time.sleep(3.0)                                    # alive, not participating
+    with open(os.path.join(out_dir, f"late{r}.txt"), "w") as fh:
+        fh.write(f"{ok_first} {result}")
+    # no further collective: the group is broken by design; leave without the usual barrier
+    os._exit(0)
+
+
+def test_a_rank_that_stays_away_is_a_timeout_status_on_the_host(tmp_path):
+    port = 29900 + os.getpid() % 90
+    mp.spawn(_late_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = open(tmp_path / "late0.txt").read()
+    r1 = open(tmp_path / "late1.txt").read()
+    assert r0.startswith("True status 4 after"), r0
+    assert float(r0.split("after ")[1][:-1]) < 2.9                 # the limit, not the peer's sleep
+    assert r1 == "True no error"

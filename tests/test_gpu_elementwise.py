@@ -81,6 +81,38 @@ def test_sizes_against_oracle(gpu, oracle, n):
         assert max_rel(gpu.flogloss(p, y), oracle.flogloss(p, y)) <= 1e-5
 
 
+def test_logloss_edge_cases_match_the_oracle_class_by_class(gpu, oracle):
+    # Labels that are exactly 0 or 1 take a one-logarithm path whose result must be the bits of
+    # the two-logarithm formula; everything around the places where that could differ is checked
+    # against the oracle: p at and around 0, 1, 1 - eps (p + eps == 1: log == +0), eps
+    # (1 - p + eps == 1), arguments <= 0 (log = -inf / NaN: 0 * log must stay NaN), inf and NaN
+    # inputs, labels -0.0, 0.5 and 2 (general form).
+    eps = np.float32(1e-5)
+    one = np.float32(1.0)
+    ps = [0.0, 1.0, 1e-5, 1.0 - 1e-5, float(one - eps), float(np.nextafter(one - eps, 0)), float(np.nextafter(one - eps, 2)),
+          float(eps), float(np.nextafter(eps, 0)), float(np.nextafter(eps, 1)), 0.5, 0.25, 0.999, 1e-3,
+          -1e-5, float(-eps), -0.5, 1.00001, 1.5, 2.0, -0.0, np.inf, -np.inf, np.nan, 1e-30, 0.6, 0.2, 0.8, 0.3]
+    ys = [0.0, 1.0, -0.0, 0.5, 2.0, 1e-3, np.nan]
+    P, Y = np.meshgrid(np.array(ps, np.float32), np.array(ys, np.float32))
+    P, Y = np.ascontiguousarray(P.ravel()), np.ascontiguousarray(Y.ravel())
+    # pad so that vector and tail paths are both exercised
+    P, Y = np.tile(P, 41)[:8003], np.tile(Y, 41)[:8003]
+    with np.errstate(all="ignore"):
+        got, want = gpu.flogloss(P, Y), oracle.flogloss(P, Y)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    inf = np.isinf(want)
+    assert np.array_equal(np.isinf(got), inf) and np.array_equal(got[inf], want[inf])
+    zero = want == 0
+    assert np.array_equal(got == 0, zero) and np.array_equal(np.signbit(got[zero]), np.signbit(want[zero]))
+    rest = ~(np.isnan(want) | inf | zero)
+    assert np.max(np.abs(got[rest].astype(np.float64) - want[rest]) / np.abs(want[rest])) <= 1e-5
+    # binary labels at scale: the same tolerance on two million elements
+    rng = np.random.default_rng(77)
+    p = rng.uniform(0, 1, 1 << 21).astype(np.float32)
+    y = (rng.random(1 << 21) < 0.5).astype(np.float32)
+    assert max_rel(gpu.flogloss(p, y), oracle.flogloss(p, y)) <= 1e-5
+
+
 def test_fill_and_copy_special_bit_patterns(gpu):
     # bit-exact means NaN payloads, -0.0, denormals and infinities survive
     pats = np.array([0x7FC00001, 0xFFC12345, 0x80000000, 0x00000001, 0x7F800000, 0xFF800000, 0x3F9DF3B6],
@@ -132,6 +164,36 @@ def test_fsum(gpu):
     gpu.d.fsum(x[1:], acc)                                # misaligned view, adds on top
     torch.cuda.synchronize()
     assert abs(float(acc) - (want + float(x[1:].double().sum()))) <= 1e-9 * want
+
+
+def test_fsum_as_a_builtin_with_a_tensor_result(gpu):
+    # "fsum" by name: the float of a double-accumulated sum, the same bits run to run, with the
+    # library's own scratch and with a caller workspace of exactly the size it asks for
+    import ctypes
+    import torch
+    from polarai_framework_b200.capi import Arg
+    lib = gpu.d.lib
+    st = torch.cuda.current_stream().cuda_stream
+    for n in (1, 3, 4, 1_000_003, 65536 * 10):
+        x = torch.rand(n + 1, device="cuda")[1:] if n == 1_000_003 else torch.rand(n, device="cuda")   # one unaligned case
+        out = torch.full((1,), float("nan"), device="cuda")
+        args = (Arg * 2)()
+        shapes = [(ctypes.c_uint64 * 1)(n), (ctypes.c_uint64 * 1)(1)]
+        for a, t, shp in zip(args, (x, out), shapes):
+            a.is_tensor, a.tensor.data, a.tensor.dims, a.tensor.shape = 1, t.data_ptr(), 1, shp
+        lib.call("polar_b200_launch_by_name", b"fsum", args, 2, None, 0, st)
+        torch.cuda.synchronize()
+        want = float(x.double().sum())
+        first = float(out)
+        assert abs(first - want) <= 1e-6 * max(want, 1.0), n
+        need = int(lib.cdll.polar_b200_launch_workspace_bytes(b"fsum", args, 2))
+        assert need == int(lib.cdll.polar_b200_fsum_f32_workspace_bytes(n)) and need % 8 == 0 and need > 0
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        out.fill_(float("nan"))
+        lib.call("polar_b200_launch_by_name", b"fsum", args, 2, ws.data_ptr(), need, st)
+        torch.cuda.synchronize()
+        assert float(out) == first, n                                  # deterministic
+        assert lib.cdll.polar_b200_launch_by_name(b"fsum", args, 2, ws.data_ptr(), need - 8, st) == 5   # too small
 
 
 def test_large_stream_properties(gpu):
