@@ -670,16 +670,17 @@ def sm_count_of(torch, index):
 
 
 def tc_traffic(program, tc_ops, rows):
-    """DRAM bytes per launch of the tensor-core matmuls from the ncu captures summarised under
-    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 8192), scaled by
-    rows - traffic of these two launches grows in proportion with the batch - next to the
-    algorithmic bytes 4(mk + kn + mn)."""
+    """DRAM bytes per launch of the tensor-core matmuls from the ncu capture summarised in
+    profiles/fmatmul_tc_256row_tiles_mlp_batch16384_full.md (dram__bytes_read.sum +
+    dram__bytes_write.sum of the step's two launches at batch 16384: 305.7 MB and 409.3 MB),
+    scaled by rows - X, H and dZ1 grow with the batch, the 12.8 MB weight-shaped operands do
+    not - next to the algorithmic bytes 4(mk + kn + mn)."""
     alg = [4.0 * (m * k + k * n + m * n) for m, n, k in (mm_dims(program, k_, a) for _, k_, a in tc_ops)]
-    measured_at_8192 = (118.4e6 + 174.3e6) / 2.0
-    return {"traffic": rows * measured_at_8192 / 8192.0,
+    measured_at_16384 = (305.7e6 + 409.3e6) / 2.0
+    return {"traffic": rows * measured_at_16384 / 16384.0,
             "algorithmic_bytes": sum(alg) / max(1, len(alg)),
-            "traffic_note": "average of the step's tensor-core launches; ncu capture at batch 8192 scaled by rows "
-                            "(profiles/fmatmul_tc_mlp_batch8192_full.md)"}
+            "traffic_note": "average of the step's two tensor-core launches; ncu capture of the same kernel "
+                            "configuration at batch 16384, scaled by rows"}
 
 
 def shutdown(torch, dist, world, dp, code=0):
@@ -884,7 +885,11 @@ def run_single_kernel_workload(args):
         res = gemm_numbers(torch, lib, n, reps=max(1, args.steps))
         ms = res["fmatmul_f_f"]["ms"]
         tf = res["fmatmul_f_f"]["tflops"]
-        tf32 = measure_tf32_peak(torch, "cuda:0")
+        if args.no_extras:    # profiling runs: no library GEMM loop around the kernel of interest
+            tf32 = {"burst": peaks["bf16_tflops"] / 2.0, "sustained": peaks["bf16_tflops_sustained"] / 2.0,
+                    "how": f"not measured (--no-extras): MEASURED_PEAKS.json bf16 / 2 ({peaks['source']})"}
+        else:
+            tf32 = measure_tf32_peak(torch, "cuda:0")
         peak = tf32["burst"]
         line = {"metric": "fp32_matmul_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "dtype": "f32",
                 "config": {"workload": f"fmatmul_f_f_{n}x{n}x{n}",

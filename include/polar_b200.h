@@ -187,8 +187,12 @@ uint64_t polar_b200_fmatmul_workspace_bytes(int transLeft, int transRight,
  *    (12 MiB for m=4096, n=10).  A product that needs more returns
  *    POLAR_B200_ERR_WORKSPACE; other shapes return POLAR_B200_ERR_UNSUPPORTED.
  *  - The first call on each device looks the array's device address up
- *    (cudaGetSymbolAddress, with that device current); make that first call
- *    outside any stream capture.
+ *    (cudaGetSymbolAddress, with the stream's device current); make that first call
+ *    outside any stream capture.  With CUDA's default lazy module loading the 16 MiB
+ *    are reserved on a GPU when the library's module is first used there, not when the
+ *    library is loaded: a host that is about to hand ALL remaining device memory to its
+ *    own allocator should make one call per device first (or run with
+ *    CUDA_MODULE_LOADING=EAGER), or that first call can fail for lack of memory.
  *  - All calls share the one array per device and it keeps the last call's
  *    contents.  Nothing in it has to start at zero (each call overwrites every
  *    value it later reads).  Two calls whose kernels overlap on the GPU - different

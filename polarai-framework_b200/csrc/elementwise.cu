@@ -52,34 +52,39 @@ struct SigmoidOp {
   }
 };
 struct LogLossOp {
-  // out = fl(fl(-y * log(p + eps)) - fl((1 - y) * log(1 - p + eps))), eps = 1e-5.
-  // Two full-precision logf per element make the kernel issue-bound rather than HBM-bound.
-  // For a label that is exactly 0 or 1 - what LogLoss is fed - one of the two products is a
-  // signed zero whatever its logarithm is (as long as that logarithm is finite), so only the
-  // other logarithm is computed; the zero gets the sign the product would have had
-  // (log x < 0 for x < 1, +0 at x = 1).  Same bits as the two-logarithm form, half the
-  // arithmetic.  Any other label, or an argument whose logarithm is not finite (<= 0, inf,
-  // NaN, where 0 * log is NaN), takes the general form.
+  // out = fl(fl(-y * log(p + eps)) - fl((1 - y) * log(1 - p + eps))), eps = 1e-5: the general
+  // form, two full-precision logarithms (scalar fallback kernel, and soft labels in the
+  // vector kernel below).
   __device__ __forceinline__ float operator()(float p, float y) const {
     const float eps = 1e-5f;
-    const float a0 = __fadd_rn(p, eps);
-    const float a1 = __fadd_rn(__fadd_rn(1.0f, -p), eps);
-    const float w0 = -y, w1 = __fadd_rn(1.0f, -y);       // the two weights
-    const bool one = (y == 1.0f), zero = (y == 0.0f);
-    const float other = one ? a1 : a0;                     // the argument whose product is a zero
-    if ((one || zero) && other > 0.0f && other < __int_as_float(0x7f800000)) {
-      const float l = logf(one ? a0 : a1);
-      // stand-in with the sign of log(other): the product with a zero weight is the same signed zero
-      const float s = other < 1.0f ? -1.0f : (other > 1.0f ? 1.0f : 0.0f);
-      const float t0 = __fmul_rn(w0, one ? l : s);
-      const float t1 = __fmul_rn(w1, one ? s : l);
-      return __fadd_rn(t0, -t1);
-    }
-    float t0 = __fmul_rn(w0, logf(a0));
-    float t1 = __fmul_rn(w1, logf(a1));
+    float t0 = __fmul_rn(-y, logf(__fadd_rn(p, eps)));
+    float t1 = __fmul_rn(__fadd_rn(1.0f, -y), logf(__fadd_rn(__fadd_rn(1.0f, -p), eps)));
     return __fadd_rn(t0, -t1);
   }
 };
+// flogloss for labels that are exactly 0 or 1 (what LogLoss is fed): one of the two weights
+// -y and 1-y is then an exact zero, and its product with a logarithm is a signed zero, NaN
+// or NaN - whatever the logarithm's low bits are.  So only the OTHER logarithm needs full
+// precision; the one under the zero weight comes from the special-function unit
+// (lg2.approx), which returns the same NaN / -inf / +inf classes and the same sign.  (The
+// sign of that zero is only visible when the full-precision term is itself zero, i.e. its
+// argument is exactly 1; the two arguments sum to 1 + 2 eps, so the other one is then about
+// 2e-5, far from where an approximate logarithm could have the wrong sign.)  Same bits as
+// the two-logarithm form at roughly 60 % of its instructions - two full logf per element make
+// the builtin issue-bound instead of HBM-bound.  Branch-free, so the unrolled elements
+// interleave.
+__device__ __forceinline__ float logloss_binary(float p, float y) {
+  const float eps = 1e-5f;
+  const float a0 = __fadd_rn(p, eps);
+  const float a1 = __fadd_rn(__fadd_rn(1.0f, -p), eps);
+  const float w0 = -y, w1 = __fadd_rn(1.0f, -y);
+  const bool first = (w1 == 0.0f);                       // y == 1: log(a0) carries the result
+  const float fine = logf(first ? a0 : a1);
+  const float coarse = __logf(first ? a1 : a0);
+  const float t0 = __fmul_rn(w0, first ? fine : coarse);
+  const float t1 = __fmul_rn(w1, first ? coarse : fine);
+  return __fadd_rn(t0, -t1);
+}
 // Extended builtin: the three launches the reference's Sigmoid derivative compiles to
 // (SigmoidOperationInternal.cpp:107-135: fadd(ones,1,s,-1) -> fmul(.,s) -> fmul(grad,.))
 // in one pass, with the same three roundings, so the result is bit-identical.
@@ -110,11 +115,9 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p);
 __device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
 
 // Per-op tile shape: vectors in flight per input per thread, and CTAs per SM the
-// register budget must allow.  flogloss carries two logf per element: measured at
-// 2^28 elements it streams fastest with less per thread and twice the CTAs
-// (6.4 vs 5.8 TB/s); the others are flat between 2 and 8 vectors per thread.
+// register budget must allow (flat between 2 and 8 vectors per thread for every builtin
+// served by this template; flogloss has its own kernel below).
 template <class Op> struct Shape { static constexpr int kUnroll = 4, kMinCtas = kCtasPerSm; };
-template <> struct Shape<LogLossOp> { static constexpr int kUnroll = 2, kMinCtas = 8; };
 
 // NIN = number of input streams (0, 1 or 2).
 template <int NIN, class Op>
@@ -152,6 +155,60 @@ ew_vec_kernel(Op op, const float* in0, const float* in1, float* out, uint64_t n)
   if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
     uint64_t i = (nvec << 2) + threadIdx.x;
     out[i] = op(NIN >= 1 ? in0[i] : 0.f, NIN >= 2 ? in1[i] : 0.f);
+  }
+}
+
+// flogloss, vector form: one tile per CTA like ew_vec_kernel.  A thread whose labels are all
+// exactly 0 or 1 takes the one-logarithm arithmetic for its whole tile (one branch per
+// thread, uniform for hard labels); any other label sends the thread to the general form.
+constexpr int kLogLossUnroll = 4;
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+logloss_vec_kernel(const float* predicted, const float* truth, float* out, uint64_t n) {
+  const uint64_t nvec = n >> 2;
+  const float4* vp = reinterpret_cast<const float4*>(predicted);
+  const float4* vy = reinterpret_cast<const float4*>(truth);
+  float4* vo = reinterpret_cast<float4*>(out);
+  const uint64_t base = (uint64_t)blockIdx.x * kThreads * kLogLossUnroll;
+  float4 p[kLogLossUnroll], y[kLogLossUnroll];
+  bool binary = true;
+#pragma unroll
+  for (int u = 0; u < kLogLossUnroll; ++u) {
+    const uint64_t i = base + (uint64_t)u * kThreads + threadIdx.x;
+    if (i < nvec) {
+      p[u] = ld_stream(vp + i);
+      y[u] = ld_stream(vy + i);
+    } else {
+      p[u] = make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+      y[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kLogLossUnroll; ++u) {
+    const float w[4] = {y[u].x, y[u].y, y[u].z, y[u].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) binary = binary && (w[j] == 0.0f || w[j] == 1.0f);
+  }
+  LogLossOp general;
+#pragma unroll
+  for (int u = 0; u < kLogLossUnroll; ++u) {
+    const uint64_t i = base + (uint64_t)u * kThreads + threadIdx.x;
+    float4 r;
+    if (binary) {
+      r.x = logloss_binary(p[u].x, y[u].x);
+      r.y = logloss_binary(p[u].y, y[u].y);
+      r.z = logloss_binary(p[u].z, y[u].z);
+      r.w = logloss_binary(p[u].w, y[u].w);
+    } else {
+      r.x = general(p[u].x, y[u].x);
+      r.y = general(p[u].y, y[u].y);
+      r.z = general(p[u].z, y[u].z);
+      r.w = general(p[u].w, y[u].w);
+    }
+    if (i < nvec) st_stream(vo + i, r);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    const uint64_t i = (nvec << 2) + threadIdx.x;
+    out[i] = general(predicted[i], truth[i]);
   }
 }
 
@@ -337,7 +394,15 @@ int polar_b200_fsigmoid_unclamped(const float* in, float* out, uint64_t n, void*
 }
 int polar_b200_flogloss(const float* predicted, const float* groundTruth, float* out, uint64_t n,
                         void* stream) {
-  return launch_ew<2>("flogloss", LogLossOp{}, predicted, groundTruth, out, n, stream);
+  if (n >= 4 && predicted && groundTruth && out && n <= (1ull << 40) && aligned16(predicted) &&
+      aligned16(groundTruth) && aligned16(out)) {
+    clear_error();
+    LaunchDeviceScope on(stream, out);
+    logloss_vec_kernel<<<tiles_for(n >> 2, kLogLossUnroll), kThreads, 0, as_stream(stream)>>>(predicted, groundTruth,
+                                                                                            out, n);
+    return check_launch("flogloss");
+  }
+  return launch_ew<2>("flogloss", LogLossOp{}, predicted, groundTruth, out, n, stream);   // null, empty, unaligned
 }
 
 int polar_b200_fsigmoid_grad(const float* gradient, const float* sigmoidOut, float* out, uint64_t n,

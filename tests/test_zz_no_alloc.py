@@ -6,7 +6,8 @@ cannot afford cudaMalloc's device-wide synchronisation): its scratch is an array
 inside the library image.  Here it is called through the C ABI twice in a row -
 the second product smaller than the first, so values left in the shared scratch by
 the first call would show if the kernel depended on a clean array - and each
-result is compared with polar_b200_fmatmul on the same operands.
+result is compared with polar_b200_fmatmul on the same operands and, since that entry
+point runs the same kernel, also with the CPU oracle's double-accumulated product.
 
 The file name sorts last so that a run that stops at the first failure has
 already run every other test."""
@@ -40,7 +41,13 @@ def both(torch, lib, m, n, k, tr, seed):
     torch.cuda.synchronize()
     mag = (left.T.double().abs() @ (right.T if tr else right).double().abs())
     err = float(((got.double() - ref.double()).abs() / mag).max())
-    return err, bool(torch.isfinite(got).all())
+    # against the oracle: sum over k in double on the CPU, error relative to sum_k |a||b|
+    from oracle import oracle as orc
+    cpu = orc.Oracle()
+    cpu.set_threads(cpu.max_threads())
+    exact, omag = cpu.fmatmul_f64(1, tr, left.cpu().numpy(), right.cpu().numpy())
+    oerr = float(np.max(np.abs(got.cpu().numpy().astype(np.float64) - exact) / omag))
+    return max(err, oerr), bool(torch.isfinite(got).all())
 
 
 def test_two_calls_in_a_row_match_the_regular_entry_point(env):
