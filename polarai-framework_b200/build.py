@@ -125,7 +125,8 @@ def build_reference_host(force=False):
     ref = reference_root()
     if ref is None:
         return [p for p in (frontend, executor, tests_bin, os.path.join(out_dir, "autograd_parity"),
-                            os.path.join(out_dir, "lspolar")) if os.path.exists(p)]
+                            os.path.join(out_dir, "data_parallel_executor"), os.path.join(out_dir, "lspolar"))
+                if os.path.exists(p)]
     os.makedirs(out_dir, exist_ok=True)
     obj_dir = os.path.join(OBJ, "ref")
     gen = os.path.join(obj_dir, "gen")
@@ -166,7 +167,7 @@ def build_reference_host(force=False):
             list(ex.map(_run, jobs))
         _run([gxx, "-shared", "-o", frontend] + objs + ["-ldl", "-lpthread", "-Wl,-rpath,$ORIGIN/.."])
     ex_src = os.path.join(CSRC, "executor", "direct_executor.cpp")
-    if force or _newer(ex_src, executor, (frontend,)):
+    if force or _newer(ex_src, executor, (frontend, os.path.join(CSRC, "executor", "data_parallel_plan.hpp"))):
         _run([gxx] + flags + ["-shared", "-o", executor, ex_src, "-L", out_dir, "-lpolar_frontend",
                               "-Wl,-rpath,$ORIGIN/ref:$ORIGIN"])
     shim = os.path.join(ROOT, "tests", "ref_integration")
@@ -189,6 +190,17 @@ def build_reference_host(force=False):
         _run([gxx] + tflags + ["-I", shim, "-fopenmp", "-o", parity_bin, parity_src, oracle_o,
                                "-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl",
                                "-lpthread", "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
+    # the Executor's batch-sharded evaluation on several (fake, or real) devices
+    dp_bin = os.path.join(out_dir, "data_parallel_executor")
+    dp_src = os.path.join(shim, "data_parallel_executor.cpp")
+    if force or _newer(dp_src, dp_bin, (executor, os.path.join(shim, "oracle_device.hpp"), oracle_c)):
+        oracle_o = os.path.join(obj_dir, "builtins_oracle.o")
+        if not os.path.exists(oracle_o) or _newer(oracle_c, oracle_o):
+            _run(["/usr/bin/gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-c", oracle_c, "-o", oracle_o])
+        tflags = [f for f in flags if f != "-fno-exceptions"]
+        _run([gxx] + tflags + ["-I", shim, "-I", os.path.join(ROOT, "include"), "-fopenmp", "-o", dp_bin, dp_src,
+                               oracle_o, "-L", LIB, "-lpolar_b200_executor", "-L", out_dir, "-lpolar_frontend", "-ldl",
+                               "-lpthread", "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
     # host-side unit tests of the pool-based BackendAllocator with fake devices
     alloc_bin = os.path.join(out_dir, "pool_allocator_test")
     alloc_src = os.path.join(shim, "pool_allocator_test.cpp")
@@ -209,7 +221,7 @@ def build_reference_host(force=False):
     if os.path.exists(lspolar_src) and (force or _newer(lspolar_src, lspolar_bin, (frontend,))):
         _run([gxx] + flags + ["-I", os.path.join(g, "runtime", "driver"), "-o", lspolar_bin, lspolar_src, "-L", out_dir, "-lpolar_frontend", "-ldl", "-lpthread",
                               "-Wl,-rpath,$ORIGIN/..:$ORIGIN"])
-    return [frontend, executor, tests_bin, parity_bin, alloc_bin, lspolar_bin]
+    return [frontend, executor, tests_bin, parity_bin, dp_bin, alloc_bin, lspolar_bin]
 
 
 def build_all(force=False, verbose=False):

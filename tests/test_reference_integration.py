@@ -156,3 +156,30 @@ def test_recorded_program_has_the_call_sequence_the_reference_lowering_pins():
     # fadd's argument order: tensor, scale, tensor, scale, result (kernel_materialize.mlir:36,73)
     fadd = next(l.split()[2:] for l in grad.splitlines() if l.strip().startswith("launch fadd"))
     assert [t[0] for t in fadd] == ["T", "f", "T", "f", "T"], fadd
+
+
+DP_EXEC = os.path.join(ROOT, "polarai-framework_b200", "lib", "ref", "data_parallel_executor")
+
+
+@pytest.mark.skipif(not os.path.exists(DP_EXEC), reason="data-parallel executor test is not built")
+def test_executor_splits_the_batch_over_fake_devices():
+    # The Executor given 2 and 4 (fake, oracle-computing) devices and told which inputs are
+    # batch-shaped: every device receives the whole program on its rows, the batch contraction is
+    # summed over the devices, results equal the one-device run; undeclared, only the first
+    # device works (the reference's behaviour).
+    out = subprocess.run([DP_EXEC], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "DATA PARALLEL OK" in out.stdout
+    assert "2 devices 5 5 | 4 devices 5 5 5 5" in out.stdout
+    assert "undeclared: second device got 0 launches" in out.stdout
+
+
+@pytest.mark.gpu
+def test_executor_splits_the_batch_over_the_b200_devices():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    assert os.path.exists(DP_EXEC), "build the package where the reference tree is present"
+    out = subprocess.run([DP_EXEC], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "B200 devices vs the oracle on one device" in out.stdout and "DATA PARALLEL OK" in out.stdout
