@@ -306,6 +306,21 @@ int polar_b200_fmatmul_sigmoid_grad(int transLeft, int transRight, uint64_t m,
                                     float* out, void* workspace,
                                     uint64_t workspace_bytes, void* stream);
 
+/* fdense_grad: the two products of a dense layer's backward pass that read the layer's input
+ * activations H (a Sigmoid output), in ONE pass over H:
+ *   dW[kh,n]    = H^T . dZ                      what fmatmul_t_f(H, dZ) gives
+ *   dIn[rows,kh] = (dZ . W^T) * ((1 - H) * H)   what fmatmul_f_t_sigmoid_grad(dZ, W, H) gives
+ * with dZ [rows,n] the gradient at the layer's n <= 16 outputs and W [kh,n] its weights.  Run
+ * separately the two builtins stream H through HBM twice; this one once.  Same arithmetic,
+ * same order of every sum as those two launches: both results carry their bits.  Larger n, or
+ * pointers that are not 16-byte aligned, run the two builtins in sequence.  As a builtin,
+ * "fdense_grad": T dZ, T W, T H, T dW, T dIn - the one native name with TWO result tensors
+ * (the last two arguments).  Scratch as for fmatmul (polar_b200_fdense_grad_workspace_bytes). */
+int polar_b200_fdense_grad(uint64_t rows, uint64_t kh, uint64_t n, const float* dZ, const float* W,
+                           const float* H, float* dW, float* dIn, void* workspace,
+                           uint64_t workspace_bytes, void* stream);
+uint64_t polar_b200_fdense_grad_workspace_bytes(uint64_t rows, uint64_t kh, uint64_t n);
+
 /* Sum of n floats into *sum (a device double, ADDED to: clear it first), with
  * warp-shuffle + one atomic per block.  Used to report the scalar mean of an
  * elementwise flogloss output; the reference has no reduction builtin. */
@@ -341,7 +356,7 @@ typedef struct polar_b200_arg {
  * Transpose all "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own
  * here), and
  * the extended "fsigmoid_grad", "fsigmoid_logloss_grad", "fmatmul_x_y_sigmoid",
- * "fmatmul_x_y_sigmoid_grad", "fsum".
+ * "fmatmul_x_y_sigmoid_grad", "fdense_grad", "fsum".
  *
  * Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
  * on arguments in LaunchCommand order; this is what Device::launch forwards to
@@ -397,6 +412,11 @@ typedef struct polar_b200_update_segment {
 int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
                               const polar_b200_update_segment* segments, uint32_t n_segments,
                               float scale_w, float scale_g, void* stream);
+
+/* How many of the builtin's trailing tensor arguments it WRITES: 1 for every native name (the
+ * reference's convention: the last tensor is the result, e.g. AddOperationInternal.cpp:61-66)
+ * except "fdense_grad", which has two.  A runtime takes write locks accordingly. */
+int polar_b200_result_count(const char* nativeKernelName);
 
 /* Scratch bytes the launch `nativeKernelName(args)` would take from the stream-ordered pool
  * if polar_b200_launch_by_name were given no workspace (0 for every builtin but some

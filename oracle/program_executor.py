@@ -34,6 +34,16 @@ class OracleExecutor:
                     t[w] = np.asarray(o.fadd(t[w].ravel(), args[0], t[gname].ravel(), args[1]),
                                       np.float32).reshape(self.program.tensors[w])
                 continue
+            if kernel == "fdense_grad":
+                # the two builtins it stands for: fmatmul_t_f(H, dZ) and fmatmul_f_t(dZ, W) followed by
+                # the Sigmoid derivative chain with H
+                d, w, h, dw, din = args
+                t[dw] = np.asarray(o.fmatmul(True, False, t[h], t[d]), np.float32).reshape(self.program.tensors[dw])
+                r = o.fmatmul(False, True, t[d], t[w])
+                one = o.ffill(1.0, t[h].size)
+                r = o.fmul(r.ravel(), o.fmul(o.fadd(one, 1.0, t[h].ravel(), -1.0), t[h].ravel()))
+                t[din] = np.asarray(r, np.float32).reshape(self.program.tensors[din])
+                continue
             out = args[-1]
             shape = self.program.tensors[out]
             if kernel == "fadd":

@@ -53,6 +53,8 @@ SIGNATURES = {
     "polar_b200_fmatmul": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid_grad": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
+    "polar_b200_fdense_grad": (_i, [_u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _u64, _p]),
+    "polar_b200_fdense_grad_workspace_bytes": (_u64, [_u64, _u64, _u64]),
     "polar_b200_fmatmul_workspace_bytes": (_u64, [_i, _i, _u64, _u64, _u64]),
     "polar_b200_fmatmul_ffma": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p]),
     "polar_b200_fmatmul_tc": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
@@ -78,6 +80,7 @@ SIGNATURES = {
     "polar_b200_launch_by_name": (_i, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64, _p, _u64, _p]),
     "polar_b200_launch_workspace_bytes": (_u64, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64]),
     "polar_b200_launch_count": (_u64, []),
+    "polar_b200_result_count": (_i, [ctypes.c_char_p]),
 }
 
 

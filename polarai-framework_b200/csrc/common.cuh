@@ -100,10 +100,15 @@ private:
 // clamp to [1e-5, 1-1e-5] (opencl/kernels.h:141-156 of the reference).
 __device__ __forceinline__ float sigmoid_clamped(float x) {
   const float eps = 1e-5f;
-  // 1/d as the correctly rounded reciprocal: the same bits as IEEE division of 1 by d,
-  // without the division's slow-path branch (which keeps independent elements from
-  // being interleaved in the matmul epilogue).
-  float r = __frcp_rn(__fadd_rn(1.0f, expf(-x)));
+  // exp through the special-function unit (ex2.approx of -x * log2 e): two instructions
+  // instead of a dozen.  In the tensor-core epilogue, which cannot overlap the next tile's k
+  // loop with 256-row tiles, the sigmoid is a large part of the drain.  Error: ex2.approx is
+  // good to 2 ulp and the product -x * log2 e adds |x| * 6e-8 relative to the exponential - at
+  // most 8e-7 where it still matters (|x| < 11.6, beyond which the clamp takes over): within
+  // the 1e-5 the builtin is held to, by a factor 10.  The reciprocal stays correctly rounded
+  // (the same bits as IEEE division of 1 by d, without the division's slow-path branch, which
+  // keeps independent elements from being interleaved in the epilogue).
+  float r = __frcp_rn(__fadd_rn(1.0f, __expf(-x)));
   const float hi = __fadd_rn(1.0f, -eps);
   r = (fabsf(__fadd_rn(r, -1.0f)) < eps) ? hi : ((fabsf(r) < eps) ? eps : r);
   return r;

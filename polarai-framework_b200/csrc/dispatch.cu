@@ -1,5 +1,6 @@
 // fmatmul entry points and dispatch by native kernel name.
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -18,6 +19,10 @@ int skinny_kind(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
 uint64_t skinny_workspace_bytes(int kind, uint64_t m, uint64_t n, uint64_t k);
 int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                   const float* right, float* out, float* ws, cudaStream_t st, const float* sig, int sigmoid_out = 0);
+bool dense_grad_ok(uint64_t rows, uint64_t kh, uint64_t n, const float* H, const float* din);
+uint64_t dense_grad_workspace_bytes(uint64_t rows, uint64_t kh, uint64_t n);
+int launch_dense_grad(const float* H, const float* dz, const float* W, float* din, float* dw, float* ws,
+                      uint64_t rows, uint64_t kh, uint64_t n, cudaStream_t st);
 uint64_t ragged_rows_workspace_bytes(uint64_t rem, uint64_t n, uint64_t k);
 int launch_ragged_rows(const float* left_tail, uint64_t left_pitch, const float* right, float* out_tail,
                        float* ws, uint64_t rem, uint64_t n, uint64_t k, cudaStream_t st);
@@ -71,15 +76,45 @@ int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left
 // A t_f product whose row count is a few rows past a multiple of the 128-row tile would
 // spend a whole tile row of tensor-core work on them (784 rows: 7 tile rows for 6.1 of
 // work).  Those rows go to the bandwidth-bound kernel instead, which reads `right` once
-// more.  That pays only for long sums: at k = 65536 the tile row costs 0.33 ms and the extra
-// pass 0.2-0.3 ms, at k = 8192 the extra pass (80 us, launch- and ramp-dominated) costs more
-// than the tile row (43 us).  Returns the number of such rows (0: not applicable).
+// more - on a second stream of the library's own, forked from and joined back into the
+// caller's stream, so that the pass runs WHILE the tensor-core kernel computes the whole
+// tile rows (the two write disjoint rows of the result and use disjoint halves of the
+// scratch).  Run one after the other the extra pass only paid for long sums; overlapped it
+// pays whenever the tensor-core part lasts longer than the pass, i.e. from a few thousand k.
+// Returns the number of such rows (0: not applicable).
 uint64_t ragged_rows(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* right, int fused) {
   const uint64_t rem = m & 127;
   if (!tl || tr || fused != 0 || m <= 128 || rem == 0 || rem > 16) return 0;
-  if ((n & 3) != 0 || !aligned16(right) || k < 16384) return 0;
+  if ((n & 3) != 0 || !aligned16(right) || k < 4096) return 0;
   return rem;
 }
+
+// The library's side stream of the current device, with the two events of a fork/join.
+// Created on first use (make that use outside stream capture: the warm-up call does).
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+SideStream* side_stream() {
+  static SideStream per_device[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> g(mu);
+  SideStream& s = per_device[dev];
+  if (!s.stream) {
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      s = SideStream{};
+      return nullptr;
+    }
+  }
+  return &s;
+}
+
+inline uint64_t align256(uint64_t b) { return (b + 255) & ~255ull; }
 
 // Row sub-tiles per CTA tile for the tensor-core path: 256 x 256 tiles (2) fetch a third fewer
 // operand bytes per flop than 128 x 256 (1) and are 12-50 % faster on long sums (8192^3: 285
@@ -136,10 +171,8 @@ static uint64_t workspace_need(int tl, int tr, uint64_t m, uint64_t n, uint64_t 
     const uint64_t mm = m - rem;
     const int mt = tc_tile_rows(mm, n, k);
     uint64_t need = tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt);
-    if (rem) {
-      const uint64_t r = ragged_rows_workspace_bytes(rem, n, k);
-      if (r > need) need = r;
-    }
+    // the two parts run at the same time: the ragged rows' scratch follows the tiles' scratch
+    if (rem) need = align256(need) + ragged_rows_workspace_bytes(rem, n, k);
     return need;
   }
   return 0;
@@ -149,7 +182,12 @@ uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t
   return workspace_need(tl, tr, m, n, k, 0);
 }
 
+int polar_b200_result_count(const char* name) { return name && !std::strcmp(name, "fdense_grad") ? 2 : 1; }
+
 uint64_t polar_b200_launch_workspace_bytes(const char* name, const polar_b200_arg* a, uint64_t argc) {
+  if (name && a && !std::strcmp(name, "fdense_grad") && argc == 5 && a[0].is_tensor && a[1].is_tensor &&
+      a[0].tensor.dims == 2 && a[1].tensor.dims == 2 && a[0].tensor.shape && a[1].tensor.shape)
+    return polar_b200_fdense_grad_workspace_bytes(a[0].tensor.shape[0], a[1].tensor.shape[0], a[0].tensor.shape[1]);
   if (name && a && !std::strcmp(name, "fsum") && argc == 2 && a[0].is_tensor && (!a[0].tensor.dims || a[0].tensor.shape)) {
     uint64_t n = 1;
     for (uint64_t d = 0; d < a[0].tensor.dims; ++d) n *= a[0].tensor.shape[d];
@@ -206,26 +244,52 @@ static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, cons
                       workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0, 0, mt);
       }
       // whole tile rows on the tensor cores (left is stored [k, m]: the first m - rem columns
-      // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel
+      // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel, concurrently
       const uint64_t mm = m - rem;
       const int mt = tc_tile_rows(mm, n, k);
-      rc = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k, mt), workspace,
-                  workspace_bytes, as_stream(stream), 0, m, mt);
-      if (rc) return rc;
-      const uint64_t need = ragged_rows_workspace_bytes(rem, n, k);
-      if (workspace) {
-        if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      const uint64_t tc_need = align256(tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt));
+      const uint64_t rag_need = ragged_rows_workspace_bytes(rem, n, k);
+      cudaStream_t main_stream = as_stream(stream);
+      void* own = nullptr;
+      char* ws = static_cast<char*>(workspace);
+      if (ws) {
+        if (workspace_bytes < tc_need + rag_need || (reinterpret_cast<uintptr_t>(workspace) & 15))
           return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
-        return launch_ragged_rows(left + mm, m, right, out + mm * n, static_cast<float*>(workspace), rem, n, k,
-                                  as_stream(stream));
+      } else {
+        cudaError_t e = cudaMallocAsync(&own, tc_need + rag_need, main_stream);
+        if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+        ws = static_cast<char*>(own);
       }
-      void* ws = nullptr;
-      cudaError_t e = cudaMallocAsync(&ws, need, as_stream(stream));
-      if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
-      rc = launch_ragged_rows(left + mm, m, right, out + mm * n, static_cast<float*>(ws), rem, n, k, as_stream(stream));
-      e = cudaFreeAsync(ws, as_stream(stream));
-      if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
-      return rc;
+      // fork: the side stream starts where the caller's stream is now (one fork/join at a time
+      // per process: the side stream's two events are shared)
+      static std::mutex fork_mutex;
+      std::lock_guard<std::mutex> fork_guard(fork_mutex);
+      SideStream* side = side_stream();
+      cudaStream_t rag_stream = main_stream;
+      if (side && cudaEventRecord(side->fork, main_stream) == cudaSuccess &&
+          cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess) {
+        rag_stream = side->stream;
+      } else {
+        cudaGetLastError();   // no side stream: one after the other on the caller's stream
+      }
+      rc = launch_ragged_rows(left + mm, m, right, out + mm * n, reinterpret_cast<float*>(ws + tc_need), rem, n, k,
+                              rag_stream);
+      int rc2 = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k, mt),
+                       tc_need ? ws : nullptr, tc_need, main_stream, 0, m, mt);
+      // join: whatever follows on the caller's stream waits for the side stream too (also when a
+      // launch failed: a fork must never be left open, least of all under stream capture)
+      if (rag_stream != main_stream) {
+        if (cudaEventRecord(side->join, rag_stream) != cudaSuccess ||
+            cudaStreamWaitEvent(main_stream, side->join, 0) != cudaSuccess) {
+          cudaError_t e = cudaGetLastError();
+          if (!rc && !rc2) rc = fail(POLAR_B200_ERR_CUDA, "joining the side stream", e);
+        }
+      }
+      if (own) {
+        cudaError_t e = cudaFreeAsync(own, main_stream);
+        if (!rc && !rc2 && e != cudaSuccess) rc = fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+      }
+      return rc ? rc : rc2;
     }
     case kPathSkinny: {
       const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
@@ -278,6 +342,45 @@ int polar_b200_fmatmul_sigmoid_grad(int tl, int tr, uint64_t m, uint64_t n, uint
   LaunchDeviceScope on(stream, out);
   return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 2, sigmoidOut);
 }
+}
+
+uint64_t polar_b200_fdense_grad_workspace_bytes(uint64_t rows, uint64_t kh, uint64_t n) {
+  const float* al = reinterpret_cast<const float*>(256);
+  if (dense_grad_ok(rows, kh, n, al, al)) return dense_grad_workspace_bytes(rows, kh, n);
+  // the two builtins in sequence
+  const uint64_t a = workspace_need(1, 0, kh, n, rows, 0), b = workspace_need(0, 1, rows, kh, n, 2);
+  return a > b ? a : b;
+}
+
+int polar_b200_fdense_grad(uint64_t rows, uint64_t kh, uint64_t n, const float* dz, const float* w,
+                           const float* h, float* dw, float* din, void* workspace, uint64_t workspace_bytes,
+                           void* stream) {
+  clear_error();
+  if (rows == 0 || kh == 0 || n == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "fdense_grad: empty operand");
+  if (!dz || !w || !h || !dw || !din) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  if (rows > (1ull << 31) || kh > (1ull << 31)) return fail(POLAR_B200_ERR_INVALID, "matrix dimension too large");
+  LaunchDeviceScope on(stream, din);
+  if (!dense_grad_ok(rows, kh, n, h, din)) {
+    // shapes the one-pass kernel does not serve: the two builtins it stands for, one after the other
+    int rc = polar_b200_fmatmul(1, 0, kh, n, rows, h, dz, dw, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return polar_b200_fmatmul_sigmoid_grad(0, 1, rows, kh, n, dz, w, h, din, workspace, workspace_bytes, stream);
+  }
+  const uint64_t need = dense_grad_workspace_bytes(rows, kh, n);
+  cudaStream_t st = as_stream(stream);
+  if (need == 0) return launch_dense_grad(h, dz, w, din, dw, nullptr, rows, kh, n, st);
+  if (workspace) {
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
+    return launch_dense_grad(h, dz, w, din, dw, static_cast<float*>(workspace), rows, kh, n, st);
+  }
+  void* ws = nullptr;
+  cudaError_t e = cudaMallocAsync(&ws, need, st);
+  if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+  int rc = launch_dense_grad(h, dz, w, din, dw, static_cast<float*>(ws), rows, kh, n, st);
+  e = cudaFreeAsync(ws, st);
+  if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+  return rc;
 }
 
 int polar_b200_fmatmul_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -390,6 +493,17 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     if (kh > h || kw > w || a[2].tensor.shape[0] != h - kh + 1 || a[2].tensor.shape[1] != w - kw + 1)
       return fail(bad_args, "fconv2d: shapes do not agree");
     return polar_b200_fconv2d(a[0].tensor.data, h, w, a[1].tensor.data, kh, kw, a[2].tensor.data, stream);
+  }
+  if (!std::strcmp(name, "fdense_grad")) {
+    // (T dZ [rows,n], T W [kh,n], T H [rows,kh], T dW [kh,n], T dIn [rows,kh]): TWO results
+    if (!pattern("TTTTT") || a[0].tensor.dims != 2 || a[1].tensor.dims != 2 || a[2].tensor.dims != 2)
+      return fail(bad_args, "fdense_grad expects (T dZ[rows,n], T W[kh,n], T H[rows,kh], T dW[kh,n], T dIn[rows,kh])");
+    const uint64_t rows = a[0].tensor.shape[0], n = a[0].tensor.shape[1], kh = a[1].tensor.shape[0];
+    if (a[1].tensor.shape[1] != n || a[2].tensor.shape[0] != rows || a[2].tensor.shape[1] != kh ||
+        numel(a[3].tensor) != kh * n || numel(a[4].tensor) != rows * kh)
+      return fail(bad_args, "fdense_grad: shapes do not agree");
+    return polar_b200_fdense_grad(rows, kh, n, a[0].tensor.data, a[1].tensor.data, a[2].tensor.data, a[3].tensor.data,
+                                  a[4].tensor.data, workspace, workspace_bytes, stream);
   }
   if (!std::strcmp(name, "fsum")) {
     if (!pattern("TT") || numel(a[1].tensor) < 1) return fail(bad_args, "fsum expects (T in, T out[1])");

@@ -414,6 +414,94 @@ small_k_kernel(const float* __restrict__ left, const float* __restrict__ right, 
   }   // row ranges
 }
 
+// ---------------------------------------------------------------- dense layer backward, one pass
+//
+// The two products of a dense layer's backward pass that read the layer's INPUT activations
+//   dW[kh, n]  = H^T . dZ                      (small n, left M-contiguous: the kernel above)
+//   dIn[B, kh] = (dZ . W^T) * ((1 - H) * H)    (small k with the Sigmoid derivative fused)
+// share everything: both stream H [B, kh] row by row, both want the dZ rows staged in shared
+// memory, and in both a thread owns four consecutive hidden columns.  Done separately H
+// crosses HBM twice; here once.  Per row a thread loads its four H values (one 128-bit load),
+// reads the dZ row from shared memory, accumulates dW for its columns and stores its four
+// dIn values.  The arithmetic, its order and the division of the batch rows into splits are
+// those of the two kernels above (same fma per term, rows ascending, splits added in
+// ascending order), so both results carry the bits of the separate launches.
+template <int NP>
+__global__ void __launch_bounds__(kThreads, NP > 10 ? 1 : 2)
+dense_grad_kernel(const float* __restrict__ H, const float* __restrict__ dz, const float* __restrict__ W,
+                  float* __restrict__ din, float* __restrict__ partial, uint64_t rows, uint64_t kh, uint64_t n,
+                  uint64_t rows_per_split) {
+  __shared__ __align__(8) float2 bs[KS][NP];   // dZ rows, every value twice: one 64-bit load yields the pair
+  const uint64_t m0 = ((uint64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
+  const uint64_t rbeg = (uint64_t)blockIdx.y * rows_per_split;
+  const uint64_t rend = (rbeg + rows_per_split < rows) ? rbeg + rows_per_split : rows;
+  const bool live = m0 < kh;   // kh is a multiple of 4
+  // W rows of the thread's four columns, packed as (column 0, column 1) and (column 2, column 3)
+  unsigned long long w01[NP], w23[NP], acc01[NP], acc23[NP];
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    float v[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) v[c] = (live && (uint64_t)j < n) ? W[(m0 + c) * n + j] : 0.f;
+    w01[j] = pack2(v[0], v[1]);
+    w23[j] = pack2(v[2], v[3]);
+    acc01[j] = acc23[j] = 0ull;
+  }
+  for (uint64_t r0 = rbeg; r0 < rend; r0 += KS) {
+    const int rs = (int)((rend - r0 < KS) ? (rend - r0) : KS);
+    __syncthreads();
+    for (int e = threadIdx.x; e < KS * NP; e += kThreads) {
+      int j = e % NP, rr = e / NP;
+      float v = 0.f;
+      if (rr < rs && (uint64_t)j < n) v = dz[(r0 + rr) * n + j];
+      bs[rr][j] = make_float2(v, v);
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int rr = 0; rr < rs; rr += 4) {
+      float4 h[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (rr + u < rs) h[u] = __ldcs(reinterpret_cast<const float4*>(H + (r0 + rr + u) * kh + m0));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (rr + u >= rs) continue;
+        const unsigned long long h01 = pack2(h[u].x, h[u].y), h23 = pack2(h[u].z, h[u].w);
+        unsigned long long c01 = 0ull, c23 = 0ull;   // (dZ . W^T) for the four columns
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+          const unsigned long long dd = *reinterpret_cast<const unsigned long long*>(&bs[rr + u][j]);
+          ffma2(c01, dd, w01[j]);
+          ffma2(c23, dd, w23[j]);
+          ffma2(acc01[j], h01, dd);
+          ffma2(acc23[j], h23, dd);
+        }
+        float c0, c1, c2, c3;
+        unpack2(c01, c0, c1);
+        unpack2(c23, c2, c3);
+        const float4 o = make_float4(sigmoid_grad_chain(c0, h[u].x), sigmoid_grad_chain(c1, h[u].y),
+                                     sigmoid_grad_chain(c2, h[u].z), sigmoid_grad_chain(c3, h[u].w));
+        __stcs(reinterpret_cast<float4*>(din + (r0 + rr + u) * kh + m0), o);
+      }
+    }
+  }
+  if (live) {
+    float* dst = partial + ((uint64_t)blockIdx.y * kh + m0) * n;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      float r0, r1, r2, r3;
+      unpack2(acc01[j], r0, r1);
+      unpack2(acc23[j], r2, r3);
+      if ((uint64_t)j < n) {
+        dst[j] = r0;
+        dst[n + j] = r1;
+        dst[2 * n + j] = r2;
+        dst[3 * n + j] = r3;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- host side
 
 inline int round_np(uint64_t n) { return n <= 1 ? 1 : n <= 2 ? 2 : n <= 4 ? 4 : n <= 8 ? 8 : n <= 10 ? 10 : 16; }
@@ -480,6 +568,25 @@ int launch_small_n_mn(const float* l, const float* r, float* out, float* ws, uin
   uint64_t cap = (uint64_t)sm_count() * 4;
   reduce_splits_kernel<<<(unsigned)(g < cap ? g : cap), kThreads, 0, st>>>(ws, out, elems, splits);
   return check_launch("fmatmul_reduce_splits");
+}
+
+template <int NP>
+int launch_dense_grad_np(const float* H, const float* dz, const float* W, float* din, float* dw, float* ws,
+                         uint32_t splits, uint64_t rows, uint64_t kh, uint64_t n, cudaStream_t st) {
+  // the same division of the rows as launch_small_n_mn makes for dW = H^T . dZ
+  uint64_t m_blocks = (kh / 4 + kThreads - 1) / kThreads;
+  uint64_t rows_per_split = (rows + splits - 1) / splits;
+  rows_per_split = (rows_per_split + 3) & ~3ull;
+  dim3 grid((unsigned)m_blocks, splits);
+  float* dst = splits > 1 ? ws : dw;
+  dense_grad_kernel<NP><<<grid, kThreads, 0, st>>>(H, dz, W, din, dst, rows, kh, n, rows_per_split);
+  int rc = check_launch("fdense_grad");
+  if (rc || splits == 1) return rc;
+  uint64_t elems = kh * n;
+  uint64_t g = (elems + kThreads - 1) / kThreads;
+  uint64_t cap = (uint64_t)sm_count() * 4;
+  reduce_splits_kernel<<<(unsigned)(g < cap ? g : cap), kThreads, 0, st>>>(ws, dw, elems, splits);
+  return check_launch("fdense_grad_reduce");
 }
 
 }  // namespace skinny
@@ -579,6 +686,27 @@ int launch_skinny(int kind, int tl, int tr, uint64_t m, uint64_t n, uint64_t k, 
   return check_launch("fmatmul_small_k");
 }
 
+
+// Whether the one-pass dense-layer backward serves these sizes, i.e. whether the two separate
+// products would run on the small-n (left M-contiguous) and small-k kernels whose arithmetic it
+// reproduces: dZ [rows, n], W [kh, n], H and dIn [rows, kh].
+bool dense_grad_ok(uint64_t rows, uint64_t kh, uint64_t n, const float* H, const float* din) {
+  return n >= 1 && n <= 16 && rows >= 32 && kh >= 32 && (kh & 3) == 0 && aligned16(H) && aligned16(din);
+}
+uint64_t dense_grad_workspace_bytes(uint64_t rows, uint64_t kh, uint64_t n) {
+  return skinny_workspace_bytes(2, kh, n, rows);
+}
+int launch_dense_grad(const float* H, const float* dz, const float* W, float* din, float* dw, float* ws,
+                      uint64_t rows, uint64_t kh, uint64_t n, cudaStream_t st) {
+  using namespace skinny;
+  const uint32_t splits = splits_for(kh, rows);
+  switch (round_np(n)) {
+#define POLAR_DENSE(NP) case NP: return launch_dense_grad_np<NP>(H, dz, W, din, dw, ws, splits, rows, kh, n, st);
+    POLAR_DENSE(1) POLAR_DENSE(2) POLAR_DENSE(4) POLAR_DENSE(8) POLAR_DENSE(10) POLAR_DENSE(16)
+#undef POLAR_DENSE
+  }
+  return fail(POLAR_B200_ERR_UNSUPPORTED, "fdense_grad: unsupported n");
+}
 
 // ---------------------------------------------------------------- entry point that allocates nothing
 

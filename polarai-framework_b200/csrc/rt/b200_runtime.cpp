@@ -455,8 +455,10 @@ auto B200Device::launch(BackendAllocator& allocator, LaunchCommand& cmd, Event* 
     status = POLAR_B200_ERR_UNSUPPORTED;
     mLastError = "launch: bad argument list";
   }
-  MemoryRecord out_record{0, 0};
-  bool have_out = false;
+  // the builtin writes its LAST tensor argument (its last two, for the one builtin with two results)
+  MemoryRecord results[2] = {{0, 0}, {0, 0}};
+  int n_seen = 0;
+  const int n_results = polar_b200_result_count(name) > 1 ? 2 : 1;
   for (uint64_t i = 0; status == POLAR_B200_OK && i < cmd.argsCount; ++i) {
     const ArgDesc& a = cmd.args[i];
     if (a.type == ArgDesc::TENSOR) {
@@ -480,8 +482,9 @@ auto B200Device::launch(BackendAllocator& allocator, LaunchCommand& cmd, Event* 
         status = POLAR_B200_ERR_INVALID;
         mLastError = "launch: tensor is not allocated on this device";
       }
-      out_record = rec;   // every builtin writes its LAST tensor argument
-      have_out = true;
+      results[0] = results[1];
+      results[1] = rec;
+      ++n_seen;
     } else {
       args[i].is_tensor = 0;
       args[i].tensor = polar_b200_tensor{nullptr, 0, nullptr};
@@ -522,7 +525,7 @@ auto B200Device::launch(BackendAllocator& allocator, LaunchCommand& cmd, Event* 
                  cmd.kernelName ? cmd.kernelName : "", mLastError.c_str());
     mLastStatus = status;
   } else {
-    if (have_out) mAllocator->markWritten(out_record);
+    for (int r = 0; r < n_results && r < n_seen; ++r) mAllocator->markWritten(results[1 - r]);
     if (verbose()) std::fprintf(stderr, "[polar_rt_cuda] %s: launched %s\n", mName.c_str(), name);
   }
   cudaEvent_t evt = CudaApi::takeEvent(mOrdinal);

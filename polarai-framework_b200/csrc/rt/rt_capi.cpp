@@ -172,11 +172,17 @@ int polar_b200_rt_read(polar_b200_rt* rt, uint64_t va, uint64_t bytes, void* dst
 int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cmd) {
   B200Device* d = dev(rt, device);
   if (!d || !cmd) return fail(rt, POLAR_B200_ERR_INVALID, "no such device or null command");
-  // Locks as the operations' gen() methods take them: the output (last tensor
-  // argument) READ_WRITE, every other tensor READ.
-  int64_t out_idx = -1;
+  // Locks as the operations' gen() methods take them: the result (last tensor argument; the
+  // last two for the one builtin with two results) READ_WRITE, every other tensor READ.
+  std::vector<uint64_t> tensors;
   for (uint64_t i = 0; i < cmd->argsCount; ++i)
-    if (cmd->args[i].type == ArgDesc::TENSOR) out_idx = (int64_t)i;
+    if (cmd->args[i].type == ArgDesc::TENSOR) tensors.push_back(i);
+  const size_t n_results = std::min<size_t>(tensors.size(), (size_t)polar_b200_result_count(cmd->nativeKernelName));
+  auto is_result = [&](uint64_t i) {
+    for (size_t r = 0; r < n_results; ++r)
+      if (tensors[tensors.size() - 1 - r] == i) return true;
+    return false;
+  };
   auto record_of = [](TensorInfo* t) {
     MemoryRecord r{t->virtAddr, 4};
     for (uint64_t k = 0; k < t->dims; ++k) r.allocationSize *= t->shape[k];
@@ -188,14 +194,16 @@ int polar_b200_rt_launch(polar_b200_rt* rt, int device, struct LaunchCommand* cm
     for (auto& l : locked) if (l == r) return true;
     return false;
   };
-  if (out_idx >= 0) {
-    MemoryRecord r = record_of(static_cast<TensorInfo*>(cmd->args[out_idx].arg));
+  for (uint64_t i : tensors) {
+    if (!is_result(i)) continue;
+    MemoryRecord r = record_of(static_cast<TensorInfo*>(cmd->args[i].arg));
+    if (is_locked(r)) continue;
     rt->allocator->lock(r, *d, LockType::READ_WRITE);
-    if (int s = allocator_status(rt)) return s;
+    if (int s = allocator_status(rt)) { unlock_all(); return s; }
     locked.push_back(r);
   }
-  for (uint64_t i = 0; i < cmd->argsCount; ++i) {
-    if (cmd->args[i].type != ArgDesc::TENSOR || (int64_t)i == out_idx) continue;
+  for (uint64_t i : tensors) {
+    if (is_result(i)) continue;
     MemoryRecord r = record_of(static_cast<TensorInfo*>(cmd->args[i].arg));
     if (is_locked(r)) continue;   // an in-place update reads what it writes
     rt->allocator->lock(r, *d, LockType::READ);

@@ -147,6 +147,9 @@ def fuse_program(program):
                                                              ->  fsigmoid_logloss_grad(P, Y, out)
       fmatmul_x_y(L,R,Z); fsigmoid(Z,H)                      ->  fmatmul_x_y_sigmoid(L, R, H)
       fmatmul_x_y(L,R,G); fsigmoid_grad(G,S,out)             ->  fmatmul_x_y_sigmoid_grad(L, R, S, out)
+      fmatmul_t_f(H,D,dW); fmatmul_f_t_sigmoid_grad(D,W,H,dIn) ->  fdense_grad(D, W, H, dW, dIn)
+                                                                 (one pass over H instead of two; an
+                                                                 ALLREDUCE(dW) between them moves behind)
 
     A rewrite applies only when the intermediates (t1, t2, Z, G) are read by nothing else
     and are not outputs of the program; they are then never written.  `ones` must be a
@@ -214,6 +217,20 @@ def fuse_program(program):
                         break
                 if changed:
                     break
+            # the two products of a dense layer's backward pass that read its input activations
+            if k == "fmatmul_t_f" and i + 1 < len(ops):
+                h, d, dw = a
+                j = i + 1
+                moved = []
+                while j < len(ops) and ops[j][0] == "ALLREDUCE" and ops[j][1][0] == dw:
+                    moved.append(ops[j])
+                    j += 1
+                if j < len(ops) and ops[j][0] == "fmatmul_f_t_sigmoid_grad":
+                    d2, w, h2, din = ops[j][1]
+                    if d2 == d and h2 == h and len({h, d, dw, w, din}) == 5:
+                        ops[i:j + 1] = [("fdense_grad", [d, w, h, dw, din])] + moved
+                        changed = True
+                        break
     fused = Program(program.name + "_fused", dict(program.tensors), ops, list(program.inputs),
                     dict(program.constants), list(program.outputs))
     return fused

@@ -47,18 +47,26 @@ def test_whole_waves_need_no_scratch(lib):
 
 def test_weight_gradient_of_the_full_batch(lib):
     # 784 = 3 * 256 + 16 rows, k = 65536: 768 rows on the tensor cores in 256-row tiles (48 tiles,
-    # three work units each fill 144 of 148 SMs), 16 rows on the split-k small-n kernel
+    # three work units each fill 144 of 148 SMs), 16 rows on the split-k small-n kernel AT THE
+    # SAME TIME on the library's side stream: the two scratch areas follow one another
     tc = 3 * 768 * 4096 * 4
     splits_ragged = min((2 * SMS + 3) // 4, 65536 // 128)          # two CTAs per SM over 4 column blocks
     ragged = splits_ragged * 4096 * 16 * 4
-    assert ws(lib, 1, 0, 784, 4096, 65536) == max(tc, ragged) == tc
+    assert tc % 256 == 0
+    assert ws(lib, 1, 0, 784, 4096, 65536) == tc + ragged
 
 
 def test_weight_gradient_of_an_eighth_of_the_batch(lib):
-    # k = 8192: no ragged path, 128-row tiles (7 row tiles), stream mode: 21 teams of 7 CTAs,
-    # slots [row][team + column] of 128 x 256 floats
-    teams = SMS // 7
-    assert ws(lib, 1, 0, 784, 4096, 8192) == 7 * (teams + 16) * 128 * 256 * 4
+    # k = 8192 (the per-GPU shape of the 8-GPU run): the same division - 768 rows in 256-row tiles,
+    # stream mode (49 teams of 3 CTAs, slots [row tile][team + column] of 256 x 256 floats), the
+    # 16 rows beside it
+    teams = SMS // 3
+    tc = 3 * (teams + 16) * 256 * 256 * 4
+    ragged = min((2 * SMS + 3) // 4, 8192 // 128) * 4096 * 16 * 4
+    assert ws(lib, 1, 0, 784, 4096, 8192) == tc + ragged
+    # below 4096 the extra pass over the right operand would outlast the tiles: no division
+    assert ws(lib, 1, 0, 784, 4096, 2048) != 0
+    assert ws(lib, 1, 0, 784, 4096, 2048) % (128 * 256 * 4) == 0
 
 
 def test_long_k_and_few_tiles_use_fixed_cuts(lib):

@@ -96,6 +96,46 @@ def test_fused_matmuls_equal_two_launches(env, tl, tr, m, n, k):
     assert d.device_status() == 0
 
 
+@pytest.mark.parametrize("rows,kh,n", [
+    (8192, 4096, 10),      # the MLP's output layer on one GPU of eight
+    (1000, 260, 10),       # rows not a multiple of the staging depth, ragged last split
+    (640, 1024, 16), (300, 64, 1), (4096, 512, 3),
+    (100, 36, 17),         # more outputs than the one-pass kernel takes: the two builtins in sequence
+    (16, 64, 4),           # too few rows: likewise
+])
+def test_fdense_grad_equals_its_two_builtins(env, rows, kh, n):
+    # dW = H^T.dZ and dIn = (dZ.W^T)*((1-H)*H) from one pass over H: the bits of fmatmul_t_f and
+    # fmatmul_f_t_sigmoid_grad, with the library's own scratch and with a caller workspace
+    torch, lib, d = env
+    torch.manual_seed(rows + kh + n)
+    H = torch.empty((rows, kh), device="cuda").uniform_(1e-5, 1 - 1e-5)
+    dZ = torch.empty((rows, n), device="cuda").uniform_(-1, 1)
+    W = torch.empty((kh, n), device="cuda").uniform_(-0.5, 0.5)
+    want_dw, got_dw = torch.empty((kh, n), device="cuda"), torch.full((kh, n), float("nan"), device="cuda")
+    want_in, got_in = torch.empty((rows, kh), device="cuda"), torch.full((rows, kh), float("nan"), device="cuda")
+    d.fmatmul(1, 0, H, dZ, want_dw)
+    lib.call("polar_b200_fmatmul_sigmoid_grad", 0, 1, rows, kh, n, dZ.data_ptr(), W.data_ptr(), H.data_ptr(),
+             want_in.data_ptr(), None, 0, st(torch))
+    lib.call("polar_b200_fdense_grad", rows, kh, n, dZ.data_ptr(), W.data_ptr(), H.data_ptr(), got_dw.data_ptr(),
+             got_in.data_ptr(), None, 0, st(torch))
+    torch.cuda.synchronize()
+    assert torch.equal(got_dw.view(torch.int32), want_dw.view(torch.int32))
+    assert torch.equal(got_in.view(torch.int32), want_in.view(torch.int32))
+    need = int(lib.cdll.polar_b200_fdense_grad_workspace_bytes(rows, kh, n))
+    if need:
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        got_dw.fill_(float("nan")), got_in.fill_(float("nan"))
+        lib.call("polar_b200_fdense_grad", rows, kh, n, dZ.data_ptr(), W.data_ptr(), H.data_ptr(), got_dw.data_ptr(),
+                 got_in.data_ptr(), ws.data_ptr(), need, st(torch))
+        torch.cuda.synchronize()
+        assert torch.equal(got_dw.view(torch.int32), want_dw.view(torch.int32))
+        assert torch.equal(got_in.view(torch.int32), want_in.view(torch.int32))
+        assert lib.cdll.polar_b200_fdense_grad(rows, kh, n, dZ.data_ptr(), W.data_ptr(), H.data_ptr(),
+                                               got_dw.data_ptr(), got_in.data_ptr(), ws.data_ptr(), need - 16,
+                                               st(torch)) == 5
+    assert d.device_status() == 0
+
+
 @pytest.mark.parametrize("batch,hidden", [(1024, 4096), (200, 256)])
 def test_fused_mlp_program_is_bit_identical(env, batch, hidden):
     from polarai_framework_b200.program import DeviceExecutor, fuse_program, mlp_program
@@ -107,7 +147,7 @@ def test_fused_mlp_program_is_bit_identical(env, batch, hidden):
     W2 = rng.uniform(-a2, a2, (hidden, 10)).astype(np.float32)
     plain = mlp_program(batch, 784, hidden, 10, 0.1)
     fused = fuse_program(plain)
-    assert fused.launches() == plain.launches() - 11      # 20 launches become 9
+    assert fused.launches() == plain.launches() - 12      # 20 launches become 8
     outs = []
     for prog in (plain, fused):
         ex = DeviceExecutor(prog)
