@@ -217,6 +217,9 @@ def per_op_times(torch, ex, reps):
                     ex.allreduce(ex.t[arr])
             elif kernel == "peers":
                 ex.peers.launch(arr[0], arr[1], arr[2], s)
+            elif kernel == "peers_part":     # timed in order here; in the step the first part overlaps a matmul
+                seg, first, count, channel, _, sw, sg = arr
+                ex.peers.launch_range(channel, first, count, seg, sw, sg, s)
             else:
                 ex.lib.check(ex._fn(kernel, arr, n, ex._ws_ptr, ex._ws_bytes, s))
             b.record()
@@ -565,8 +568,12 @@ def run_mlp(args):
     times = per_op_times(torch, ex, reps=min(5, args.steps))
     total_ops_ms = sum(times)
     by_kernel = {}
+    seen_part = 0
     for (kernel, a), t in zip(program.ops, times):
         key = kernel if not kernel.startswith("fmatmul") else f"{kernel}:{a[-1]}"
+        if kernel == "ALLREDUCE_FADD_PART":
+            seen_part += 1
+            key = f"ALLREDUCE_FADD_PART:{seen_part}" + (" (overlapped in the step)" if a[3] else "")
         d = by_kernel.setdefault(key, {"launches": 0, "ms": 0.0})
         d["launches"] += 1
         d["ms"] += t
@@ -631,6 +638,8 @@ def run_mlp(args):
         line["parity"] = parity
     if peers is not None:
         line["exchange_phases_us"] = {k: round(v, 1) for k, v in peers.phase_times_us().items()}
+        if any(k == "ALLREDUCE_FADD_PART" for k, _ in program.ops):
+            line["exchange_phases_us_overlapped_part"] = {k: round(v, 1) for k, v in peers.phase_times_us(1).items()}
     line["device_status"] = dp.device_status()             # 0: no bounded device-side wait gave up
     if fused and not args.no_extras:
         # The same step as the reference's own builtin chain, one launch per builtin (20 launches
@@ -714,6 +723,8 @@ def mm_dims(program, kernel, args):
     m = ls[1] if tl else ls[0]
     k = ls[0] if tl else ls[1]
     n = rs[0] if tr else rs[1]
+    if kernel == "fmatmul_t_f_rows":
+        m = int(args[3])                                    # a block of rows of the product
     return int(m), int(n), int(k)
 
 

@@ -169,6 +169,19 @@ int polar_b200_fmatmul(int transLeft, int transRight, uint64_t m, uint64_t n,
 uint64_t polar_b200_fmatmul_workspace_bytes(int transLeft, int transRight,
                                             uint64_t m, uint64_t n, uint64_t k);
 
+/* A block of rows of fmatmul_t_f: out[row0 .. row0+rows, :] of out[m,n] = left^T . right with
+ * left stored [k,m], right [k,n]; the other rows of `out` are not touched.  Bit for bit the
+ * rows the product of the column block of `left` gives.  For a step that exchanges a weight
+ * gradient between GPUs while the rest of it is still being computed (see
+ * polar_b200_allreduce_fadd_range).  row0 and m multiples of 4; the block must be one the
+ * tensor-core path serves (rows >= 64, n >= 32, k >= 32, TMA-describable), else
+ * POLAR_B200_ERR_UNSUPPORTED.  Native name "fmatmul_t_f_rows": T left, T right, f32 row0,
+ * f32 rows (whole numbers), T out. */
+int polar_b200_fmatmul_t_f_rows(uint64_t m, uint64_t row0, uint64_t rows, uint64_t n, uint64_t k,
+                                const float* left, const float* right, float* out,
+                                void* workspace, uint64_t workspace_bytes, void* stream);
+uint64_t polar_b200_fmatmul_t_f_rows_workspace_bytes(uint64_t rows, uint64_t n, uint64_t k);
+
 /* fmatmul_t_f / fmatmul_t_t for a narrow result, without any allocation.
  * No counterpart in the reference: it exists for hosts that cannot call
  * cudaMalloc while they run - an application that has already handed all device
@@ -356,7 +369,7 @@ typedef struct polar_b200_arg {
  * Transpose all "ftranspose" - PolarGraphOps.td:461-523 - so each gets a name of its own
  * here), and
  * the extended "fsigmoid_grad", "fsigmoid_logloss_grad", "fmatmul_x_y_sigmoid",
- * "fmatmul_x_y_sigmoid_grad", "fdense_grad", "fsum".
+ * "fmatmul_x_y_sigmoid_grad", "fmatmul_t_f_rows", "fdense_grad", "fsum".
  *
  * Launches the builtin called `nativeKernelName` ("fadd", "fmatmul_t_f", ...)
  * on arguments in LaunchCommand order; this is what Device::launch forwards to
@@ -376,14 +389,17 @@ int polar_b200_launch_by_name(const char* nativeKernelName,
  * fadd's, so a replica ends with the bits the two-step form gives for the same sum.
  *
  * A peer buffer = POLAR_B200_PEER_CONTROL_BYTES of control words (zeroed by
- * polar_b200_peer_alloc, then owned by the kernels; 64-bit words 20..24 hold the last
+ * polar_b200_peer_alloc, then owned by the kernels; one block of
+ * POLAR_B200_PEER_CHANNEL_BYTES per channel, whose 64-bit words 20..24 hold the last
  * launch's phase timestamps in ns for profiling) followed by the payload (the
  * gradient vector, padded with zeros to 16 bytes).  Each rank allocates one, exports
  * it as a CUDA IPC handle, and opens every other rank's handle; ranks must be
  * distinct processes on GPUs with peer access (NVLink). */
 #define POLAR_B200_MAX_PEERS 16
 #define POLAR_B200_MAX_UPDATE_SEGMENTS 8
-#define POLAR_B200_PEER_CONTROL_BYTES 256
+#define POLAR_B200_PEER_CHANNELS 4
+#define POLAR_B200_PEER_CHANNEL_BYTES 256
+#define POLAR_B200_PEER_CONTROL_BYTES 1024
 #define POLAR_B200_PEER_HANDLE_BYTES 64
 
 int polar_b200_peer_alloc(uint64_t payload_bytes, void** buffer);
@@ -417,6 +433,20 @@ int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t worl
  * reference's convention: the last tensor is the result, e.g. AddOperationInternal.cpp:61-66)
  * except "fdense_grad", which has two.  A runtime takes write locks accordingly. */
 int polar_b200_result_count(const char* nativeKernelName);
+
+/* The same exchange for a PART of the payload, floats [first, first + count) (first a multiple
+ * of 4; every segment inside the range), on its own `channel` of control words
+ * (0 .. POLAR_B200_PEER_CHANNELS-1).  Exchanges on different channels may be in flight at the
+ * same time - on two streams of one GPU, in the same order on every rank - which is how a step
+ * hides most of its exchange: the first rows of a weight gradient travel while the
+ * tensor-core matmul is still computing the remaining rows.  Channel 0 is what
+ * polar_b200_allreduce_fadd uses; the other channels launch small CTAs that fit on an SM
+ * beside a running tensor-core matmul.  Per element the sum is still taken in ascending
+ * rank order: the bits do not depend on how the payload is cut. */
+int polar_b200_allreduce_fadd_range(void* const* buffers, uint32_t rank, uint32_t world, uint32_t channel,
+                                    uint64_t first, uint64_t count,
+                                    const polar_b200_update_segment* segments, uint32_t n_segments,
+                                    float scale_w, float scale_g, void* stream);
 
 /* Scratch bytes the launch `nativeKernelName(args)` would take from the stream-ordered pool
  * if polar_b200_launch_by_name were given no workspace (0 for every builtin but some

@@ -85,13 +85,18 @@ int polar_b200_rt_adopt(polar_b200_rt* rt, int device, uint64_t virtAddr, uint64
  * READ_WRITE for the launch like a builtin's output, so other copies of it become stale.
  * No counterpart in the reference (one device, no collective: ExecutorImpl.cpp:71-75). */
 typedef struct polar_b200_rt_update {
-  uint64_t weight_va;    /* record of one weight tensor (count floats) */
-  uint64_t grad_offset;  /* where its gradient starts in the peer payload, in floats */
-  uint64_t count;
+  uint64_t weight_va;      /* record of one weight tensor */
+  uint64_t weight_bytes;   /* its size */
+  uint64_t weight_offset;  /* first element of the record this update touches (floats) */
+  uint64_t grad_offset;    /* where the matching gradient elements start in the peer payload (floats) */
+  uint64_t count;          /* elements */
 } polar_b200_rt_update;
+/* channel, first, count: the part of the payload this call exchanges and the channel of control
+ * words it uses, as in polar_b200_allreduce_fadd_range (channel 0, first 0, count n = everything). */
 int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, uint32_t rank,
-                                 uint32_t world, uint64_t n, const polar_b200_rt_update* updates,
-                                 uint32_t n_updates, float scale_w, float scale_g);
+                                 uint32_t world, uint32_t channel, uint64_t first, uint64_t count,
+                                 const polar_b200_rt_update* updates, uint32_t n_updates, float scale_w,
+                                 float scale_g);
 
 /* One builtin: READ_WRITE lock on the last tensor argument, READ locks on the
  * others (as the operations' gen() methods emit), Device::launch, release.

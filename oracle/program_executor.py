@@ -34,6 +34,23 @@ class OracleExecutor:
                     t[w] = np.asarray(o.fadd(t[w].ravel(), args[0], t[gname].ravel(), args[1]),
                                       np.float32).reshape(self.program.tensors[w])
                 continue
+            if kernel == "ALLREDUCE_FADD_PART":
+                # the same sum and update for a block of rows of each listed pair
+                for i in range(4, len(args), 4):
+                    w, gname, r0, rows = args[i], args[i + 1], int(args[i + 2]), int(args[i + 3])
+                    sl = slice(r0, r0 + rows) if rows >= 0 else slice(None)
+                    piece = np.ascontiguousarray(t[gname][sl])
+                    if self.allreduce is not None:
+                        piece = self.allreduce(piece)
+                    t[gname][sl] = piece
+                    t[w][sl] = np.asarray(o.fadd(np.ascontiguousarray(t[w][sl]).ravel(), args[0], piece.ravel(), args[1]),
+                                          np.float32).reshape(t[w][sl].shape)
+                continue
+            if kernel == "fmatmul_t_f_rows":
+                # rows [r0, r0 + rows) of left^T . right: the product of that column block of left
+                left, right, r0, rows, outn = args[0], args[1], int(args[2]), int(args[3]), args[4]
+                t[outn][r0:r0 + rows] = o.fmatmul(True, False, np.ascontiguousarray(t[left][:, r0:r0 + rows]), t[right])
+                continue
             if kernel == "fdense_grad":
                 # the two builtins it stands for: fmatmul_t_f(H, dZ) and fmatmul_f_t(dZ, W) followed by
                 # the Sigmoid derivative chain with H

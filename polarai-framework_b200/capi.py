@@ -53,6 +53,8 @@ SIGNATURES = {
     "polar_b200_fmatmul": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fmatmul_sigmoid_grad": (_i, [_i, _i, _u64, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
+    "polar_b200_fmatmul_t_f_rows": (_i, [_u64, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _u64, _p]),
+    "polar_b200_fmatmul_t_f_rows_workspace_bytes": (_u64, [_u64, _u64, _u64]),
     "polar_b200_fdense_grad": (_i, [_u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _u64, _p]),
     "polar_b200_fdense_grad_workspace_bytes": (_u64, [_u64, _u64, _u64]),
     "polar_b200_fmatmul_workspace_bytes": (_u64, [_i, _i, _u64, _u64, _u64]),
@@ -77,6 +79,8 @@ SIGNATURES = {
     "polar_b200_peer_close": (_i, [_p]),
     "polar_b200_allreduce_fadd": (_i, [ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32, _u64, _p,
                                        ctypes.c_uint32, _f, _f, _p]),
+    "polar_b200_allreduce_fadd_range": (_i, [ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
+                                             _u64, _u64, _p, ctypes.c_uint32, _f, _f, _p]),
     "polar_b200_launch_by_name": (_i, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64, _p, _u64, _p]),
     "polar_b200_launch_workspace_bytes": (_u64, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64]),
     "polar_b200_launch_count": (_u64, []),

@@ -185,6 +185,9 @@ uint64_t polar_b200_fmatmul_workspace_bytes(int tl, int tr, uint64_t m, uint64_t
 int polar_b200_result_count(const char* name) { return name && !std::strcmp(name, "fdense_grad") ? 2 : 1; }
 
 uint64_t polar_b200_launch_workspace_bytes(const char* name, const polar_b200_arg* a, uint64_t argc) {
+  if (name && a && !std::strcmp(name, "fmatmul_t_f_rows") && argc == 5 && a[0].is_tensor && a[1].is_tensor &&
+      a[0].tensor.dims == 2 && a[1].tensor.dims == 2 && a[0].tensor.shape && a[1].tensor.shape && !a[3].is_tensor)
+    return polar_b200_fmatmul_t_f_rows_workspace_bytes((uint64_t)a[3].scalar, a[1].tensor.shape[1], a[0].tensor.shape[0]);
   if (name && a && !std::strcmp(name, "fdense_grad") && argc == 5 && a[0].is_tensor && a[1].is_tensor &&
       a[0].tensor.dims == 2 && a[1].tensor.dims == 2 && a[0].tensor.shape && a[1].tensor.shape)
     return polar_b200_fdense_grad_workspace_bytes(a[0].tensor.shape[0], a[1].tensor.shape[0], a[0].tensor.shape[1]);
@@ -208,6 +211,70 @@ int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) 
   // Alignment of the operands is assumed (allocator buffers are 256-byte aligned).
   const float* al = reinterpret_cast<const float*>(256);
   return choose_path(tl, tr, m, n, k, al, al, al);
+}
+
+// The tensor-core path of one product: whole tiles on the tcgen05 kernel, rows just past a tile
+// boundary of a t_f product beside it on the bandwidth-bound kernel.  `pitch` (t_f only; 0 = m)
+// is the number of floats between consecutive k rows of the stored left operand: a value above
+// m makes the product one over COLUMNS [0, m) of a wider stored matrix, i.e. over a block of
+// rows of the full result.
+static int tc_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
+                   float* out, void* workspace, uint64_t workspace_bytes, void* stream, int fused, uint64_t pitch) {
+  int rc = POLAR_B200_OK;
+  const uint64_t lp = pitch ? pitch : m;
+  const uint64_t rem = ragged_rows(tl, tr, m, n, k, right, fused);
+  if (rem == 0) {
+    const int mt = tc_tile_rows(m, n, k);
+    return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k, mt), workspace,
+                  workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0, pitch, mt);
+  }
+  // whole tile rows on the tensor cores (left is stored [k, m]: the first m - rem columns
+  // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel, concurrently
+  const uint64_t mm = m - rem;
+  const int mt = tc_tile_rows(mm, n, k);
+  const uint64_t tc_need = align256(tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt));
+  const uint64_t rag_need = ragged_rows_workspace_bytes(rem, n, k);
+  cudaStream_t main_stream = as_stream(stream);
+  void* own = nullptr;
+  char* ws = static_cast<char*>(workspace);
+  if (ws) {
+    if (workspace_bytes < tc_need + rag_need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
+  } else {
+    cudaError_t e = cudaMallocAsync(&own, tc_need + rag_need, main_stream);
+    if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
+    ws = static_cast<char*>(own);
+  }
+  // fork: the side stream starts where the caller's stream is now (one fork/join at a time
+  // per process: the side stream's two events are shared)
+  static std::mutex fork_mutex;
+  std::lock_guard<std::mutex> fork_guard(fork_mutex);
+  SideStream* side = side_stream();
+  cudaStream_t rag_stream = main_stream;
+  if (side && cudaEventRecord(side->fork, main_stream) == cudaSuccess &&
+      cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess) {
+    rag_stream = side->stream;
+  } else {
+    cudaGetLastError();   // no side stream: one after the other on the caller's stream
+  }
+  rc = launch_ragged_rows(left + mm, lp, right, out + mm * n, reinterpret_cast<float*>(ws + tc_need), rem, n, k,
+                          rag_stream);
+  int rc2 = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k, mt),
+                   tc_need ? ws : nullptr, tc_need, main_stream, 0, lp, mt);
+  // join: whatever follows on the caller's stream waits for the side stream too (also when a
+  // launch failed: a fork must never be left open, least of all under stream capture)
+  if (rag_stream != main_stream) {
+    if (cudaEventRecord(side->join, rag_stream) != cudaSuccess ||
+        cudaStreamWaitEvent(main_stream, side->join, 0) != cudaSuccess) {
+      cudaError_t e = cudaGetLastError();
+      if (!rc && !rc2) rc = fail(POLAR_B200_ERR_CUDA, "joining the side stream", e);
+    }
+  }
+  if (own) {
+    cudaError_t e = cudaFreeAsync(own, main_stream);
+    if (!rc && !rc2 && e != cudaSuccess) rc = fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
+  }
+  return rc ? rc : rc2;
 }
 
 // fused == 0: out = L.R;  1: out = fsigmoid(L.R);  2: out = (L.R) * ((1 - sig) * sig).
@@ -236,61 +303,8 @@ static int fmatmul_impl(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, cons
                       : polar_b200_fsigmoid_grad(out, sig, out, m * n, stream);
   }
   switch (path) {
-    case kPathTc: {
-      const uint64_t rem = ragged_rows(tl, tr, m, n, k, right, fused);
-      if (rem == 0) {
-        const int mt = tc_tile_rows(m, n, k);
-        return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k, mt), workspace,
-                      workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0, 0, mt);
-      }
-      // whole tile rows on the tensor cores (left is stored [k, m]: the first m - rem columns
-      // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel, concurrently
-      const uint64_t mm = m - rem;
-      const int mt = tc_tile_rows(mm, n, k);
-      const uint64_t tc_need = align256(tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt));
-      const uint64_t rag_need = ragged_rows_workspace_bytes(rem, n, k);
-      cudaStream_t main_stream = as_stream(stream);
-      void* own = nullptr;
-      char* ws = static_cast<char*>(workspace);
-      if (ws) {
-        if (workspace_bytes < tc_need + rag_need || (reinterpret_cast<uintptr_t>(workspace) & 15))
-          return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
-      } else {
-        cudaError_t e = cudaMallocAsync(&own, tc_need + rag_need, main_stream);
-        if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
-        ws = static_cast<char*>(own);
-      }
-      // fork: the side stream starts where the caller's stream is now (one fork/join at a time
-      // per process: the side stream's two events are shared)
-      static std::mutex fork_mutex;
-      std::lock_guard<std::mutex> fork_guard(fork_mutex);
-      SideStream* side = side_stream();
-      cudaStream_t rag_stream = main_stream;
-      if (side && cudaEventRecord(side->fork, main_stream) == cudaSuccess &&
-          cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess) {
-        rag_stream = side->stream;
-      } else {
-        cudaGetLastError();   // no side stream: one after the other on the caller's stream
-      }
-      rc = launch_ragged_rows(left + mm, m, right, out + mm * n, reinterpret_cast<float*>(ws + tc_need), rem, n, k,
-                              rag_stream);
-      int rc2 = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k, mt),
-                       tc_need ? ws : nullptr, tc_need, main_stream, 0, m, mt);
-      // join: whatever follows on the caller's stream waits for the side stream too (also when a
-      // launch failed: a fork must never be left open, least of all under stream capture)
-      if (rag_stream != main_stream) {
-        if (cudaEventRecord(side->join, rag_stream) != cudaSuccess ||
-            cudaStreamWaitEvent(main_stream, side->join, 0) != cudaSuccess) {
-          cudaError_t e = cudaGetLastError();
-          if (!rc && !rc2) rc = fail(POLAR_B200_ERR_CUDA, "joining the side stream", e);
-        }
-      }
-      if (own) {
-        cudaError_t e = cudaFreeAsync(own, main_stream);
-        if (!rc && !rc2 && e != cudaSuccess) rc = fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
-      }
-      return rc ? rc : rc2;
-    }
+    case kPathTc:
+      return tc_path(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, fused, 0);
     case kPathSkinny: {
       const int kind = skinny_kind(tl, tr, m, n, k, left, right, out);
       const uint64_t need = skinny_workspace_bytes(kind, m, n, k);
@@ -323,6 +337,28 @@ int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const
                        void* stream) {
   LaunchDeviceScope on(stream, out);
   return fmatmul_impl(tl, tr, m, n, k, left, right, out, workspace, workspace_bytes, stream, 0, nullptr);
+}
+
+uint64_t polar_b200_fmatmul_t_f_rows_workspace_bytes(uint64_t rows, uint64_t n, uint64_t k) {
+  return workspace_need(1, 0, rows, n, k, 0);
+}
+
+int polar_b200_fmatmul_t_f_rows(uint64_t m, uint64_t row0, uint64_t rows, uint64_t n, uint64_t k, const float* left,
+                                const float* right, float* out, void* workspace, uint64_t workspace_bytes,
+                                void* stream) {
+  clear_error();
+  if (rows == 0) return POLAR_B200_OK;
+  if (!left || !right || !out) return fail(POLAR_B200_ERR_INVALID, "null device pointer");
+  if (row0 + rows > m || (row0 & 3) || m > (1ull << 31) || n > (1ull << 31) || k > (1ull << 31))
+    return fail(POLAR_B200_ERR_INVALID, "fmatmul_t_f_rows: rows outside the result, or row0 not a multiple of 4");
+  if (row0 == 0 && rows == m) return polar_b200_fmatmul(1, 0, m, n, k, left, right, out, workspace, workspace_bytes, stream);
+  const float* l = left + row0;
+  float* o = out + row0 * n;
+  if ((m & 3) || !tc_shape_ok(1, 0, rows, n, k, l, right) || rows < 64 || n < 32 || k < 32 ||
+      skinny_kind(1, 0, rows, n, k, l, right, o))
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "fmatmul_t_f_rows serves blocks of rows that run on the tensor-core path");
+  LaunchDeviceScope on(stream, out);
+  return tc_path(1, 0, rows, n, k, l, right, o, workspace, workspace_bytes, stream, 0, m);
 }
 
 int polar_b200_fmatmul_sigmoid(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -493,6 +529,18 @@ int polar_b200_launch_by_name(const char* name, const polar_b200_arg* a, uint64_
     if (kh > h || kw > w || a[2].tensor.shape[0] != h - kh + 1 || a[2].tensor.shape[1] != w - kw + 1)
       return fail(bad_args, "fconv2d: shapes do not agree");
     return polar_b200_fconv2d(a[0].tensor.data, h, w, a[1].tensor.data, kh, kw, a[2].tensor.data, stream);
+  }
+  if (!std::strcmp(name, "fmatmul_t_f_rows")) {
+    // (T left[k,m], T right[k,n], f32 row0, f32 rows, T out[m,n]): rows [row0, row0+rows) of fmatmul_t_f
+    if (!pattern("TTffT") || a[0].tensor.dims != 2 || a[1].tensor.dims != 2 || a[4].tensor.dims != 2)
+      return fail(bad_args, "fmatmul_t_f_rows expects (T left, T right, f32 row0, f32 rows, T out)");
+    const uint64_t k = a[0].tensor.shape[0], m = a[0].tensor.shape[1], n = a[1].tensor.shape[1];
+    const float r0 = a[2].scalar, rr = a[3].scalar;
+    if (a[1].tensor.shape[0] != k || a[4].tensor.shape[0] != m || a[4].tensor.shape[1] != n || r0 < 0 || rr < 0 ||
+        r0 != (float)(uint64_t)r0 || rr != (float)(uint64_t)rr)
+      return fail(bad_args, "fmatmul_t_f_rows: shapes do not agree, or a row count that is not a whole number");
+    return polar_b200_fmatmul_t_f_rows(m, (uint64_t)r0, (uint64_t)rr, n, k, a[0].tensor.data, a[1].tensor.data,
+                                       a[4].tensor.data, workspace, workspace_bytes, stream);
   }
   if (!std::strcmp(name, "fdense_grad")) {
     // (T dZ [rows,n], T W [kh,n], T H [rows,kh], T dW [kh,n], T dIn [rows,kh]): TWO results

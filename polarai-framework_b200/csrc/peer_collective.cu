@@ -40,7 +40,9 @@ constexpr int kMaxSegments = POLAR_B200_MAX_UPDATE_SEGMENTS;
 constexpr int kThreads = 512;
 constexpr unsigned long long kDefaultWaitNs = 4000000000ull;   // 4 s
 
-// Control words at the head of every rank's buffer (uint32 each).
+// Control words at the head of every rank's buffer (uint32 each), one block of
+// POLAR_B200_PEER_CHANNEL_BYTES per channel: exchanges on different channels (different parts
+// of the payload, possibly in flight at the same time on two streams) do not share a word.
 constexpr int kReady = 0;                 // [kMaxWorld] written by peer p at index p
 constexpr int kDone = kMaxWorld;          // [kMaxWorld]
 constexpr int kStep = 2 * kMaxWorld;      // local: last completed step
@@ -50,7 +52,9 @@ constexpr int kAborted = kStep + 3;       // local: the step in which a CTA of t
 // %globaltimer (ns) of CTA 0 in the last launch: start, gradients of all ranks ready, slice
 // summed and stored, all slices in place, update done.  Five 64-bit words, for profiling.
 constexpr int kStamps = 40;
-static_assert((kStamps + 10) * 4 <= POLAR_B200_PEER_CONTROL_BYTES, "control block too small");
+static_assert((kStamps + 10) * 4 <= POLAR_B200_PEER_CHANNEL_BYTES, "control block too small");
+static_assert(POLAR_B200_PEER_CHANNEL_BYTES * POLAR_B200_PEER_CHANNELS == POLAR_B200_PEER_CONTROL_BYTES,
+              "channels fill the control area");
 
 struct Segment {
   float* w;
@@ -61,7 +65,8 @@ struct Segment {
 struct Params {
   unsigned char* base[kMaxWorld];   // every rank's buffer (own one included), control block first
   Segment seg[kMaxSegments];
-  uint64_t n4;                      // length of G in float4
+  uint64_t first4, n4;              // the part of G this launch exchanges, in float4
+  uint32_t channel;                 // which control block
   uint32_t rank, world, n_seg;
   float scale_w, scale_g;
   int* status;
@@ -119,7 +124,9 @@ __device__ __forceinline__ bool wait_all(const uint32_t* words, uint32_t world, 
 template <int WORLD>   // 0 = any world size up to kMaxWorld
 __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p) {
   const uint32_t world = WORLD ? (uint32_t)WORLD : p.world;
-  uint32_t* ctl = reinterpret_cast<uint32_t*>(p.base[p.rank]);
+  const uint32_t kThreadsNow = blockDim.x;
+  const uint32_t ctl_off = p.channel * (POLAR_B200_PEER_CHANNEL_BYTES / 4);
+  uint32_t* ctl = reinterpret_cast<uint32_t*>(p.base[p.rank]) + ctl_off;
   const uint32_t step = *(volatile uint32_t*)(ctl + kStep) + 1u;
   unsigned long long* stamps = reinterpret_cast<unsigned long long*>(ctl + kStamps);
   const bool stamper = blockIdx.x == 0 && threadIdx.x == 0;
@@ -128,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
   // 1. my G is complete (the launches that wrote it precede this one in the stream)
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kReady + p.rank, step);
+    st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + ctl_off + kReady + p.rank, step);
   }
   const bool ready = wait_all(ctl + kReady, world, step, p.status, 301, p.wait_ns);
   if (!ready && threadIdx.x == 0) *(volatile uint32_t*)(ctl + kAborted) = step;
@@ -137,14 +144,15 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
   // 2. slice `rank`, summed in rank order, to everyone
   if (ready) {
     const uint64_t per = (p.n4 + world - 1) / world;
-    const uint64_t lo = (uint64_t)p.rank * per;
-    const uint64_t hi = lo + per < p.n4 ? lo + per : p.n4;
+    const uint64_t lo_rel = (uint64_t)p.rank * per < p.n4 ? (uint64_t)p.rank * per : p.n4;
+    const uint64_t lo = p.first4 + lo_rel;
+    const uint64_t hi = p.first4 + (lo_rel + per < p.n4 ? lo_rel + per : p.n4);
     // With few ranks a thread has many elements and one NVLink round trip per element would
     // be a chain of latencies: UNR elements' loads are issued together.
     constexpr int W = WORLD ? WORLD : kMaxWorld;
     constexpr int UNR = WORLD == 2 ? 4 : (WORLD == 4 ? 2 : 1);
-    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
-    for (uint64_t i0 = lo + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i0 < hi; i0 += stride * UNR) {
+    const uint64_t stride = (uint64_t)gridDim.x * kThreadsNow;
+    for (uint64_t i0 = lo + (uint64_t)blockIdx.x * kThreadsNow + threadIdx.x; i0 < hi; i0 += stride * UNR) {
       float4 v[UNR][W];
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
@@ -188,7 +196,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     __threadfence_system();
     // "slice in place" is only said when every CTA of this rank did its part of the sum
     if (*(volatile uint32_t*)(ctl + kAborted) != step)
-      st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + kDone + p.rank, step);
+      st_release_sys(reinterpret_cast<uint32_t*>(p.base[threadIdx.x]) + ctl_off + kDone + p.rank, step);
   }
   const bool done = wait_all(ctl + kDone, world, step, p.status, 302, p.wait_ns);
   if (stamper) stamps[3] = now_ns();
@@ -200,7 +208,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     const float4* g4 = reinterpret_cast<const float4*>(g + sg.offset);
     float4* w4 = reinterpret_cast<float4*>(sg.w);
     const uint64_t c4 = sg.count >> 2;
-    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < c4; i += (uint64_t)gridDim.x * kThreads) {
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreadsNow + threadIdx.x; i < c4; i += (uint64_t)gridDim.x * kThreadsNow) {
       const float4 gv = __ldcg(g4 + i);
       float4 wv = w4[i];
       wv.x = __fadd_rn(__fmul_rn(wv.x, p.scale_w), __fmul_rn(gv.x, p.scale_g));
@@ -289,14 +297,16 @@ int polar_b200_peer_close(void* buffer) {
   return e == cudaSuccess ? POLAR_B200_OK : fail(POLAR_B200_ERR_CUDA, "cudaIpcCloseMemHandle", e);
 }
 
-int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
-                              const polar_b200_update_segment* segments, uint32_t n_segments, float scale_w,
-                              float scale_g, void* stream) {
+static int allreduce_fadd_impl(void* const* buffers, uint32_t rank, uint32_t world, uint32_t channel, uint64_t first,
+                               uint64_t n, const polar_b200_update_segment* segments, uint32_t n_segments,
+                               float scale_w, float scale_g, void* stream) {
   clear_error();
   if (!buffers || world == 0 || world > (uint32_t)peer::kMaxWorld || rank >= world)
     return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: bad rank/world or null buffer list");
   if (n_segments > (uint32_t)peer::kMaxSegments || (n_segments && !segments))
     return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: too many update segments");
+  if (channel >= POLAR_B200_PEER_CHANNELS || (first & 3))
+    return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: bad channel, or a range that does not start on a 16-byte boundary");
   if (n == 0) return POLAR_B200_OK;
   peer::Params p{};
   for (uint32_t r = 0; r < world; ++r) {
@@ -305,8 +315,8 @@ int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t worl
   }
   for (uint32_t s = 0; s < n_segments; ++s) {
     const polar_b200_update_segment& g = segments[s];
-    if (!g.weights || !aligned16(g.weights) || (g.offset & 3) || g.offset + g.count > n)
-      return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: segment outside the vector, or not 16-byte aligned");
+    if (!g.weights || !aligned16(g.weights) || (g.offset & 3) || g.offset < first || g.offset + g.count > first + n)
+      return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: segment outside the exchanged range, or not 16-byte aligned");
     p.seg[s] = peer::Segment{g.weights, g.offset, g.count};
   }
   LaunchDeviceScope on(stream, buffers[rank]);
@@ -314,14 +324,19 @@ int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t worl
   p.status = device_status_word(&rc);
   if (!p.status) return rc;
   p.wait_ns = wait_limit_ns(peer::kDefaultWaitNs);
+  p.first4 = first / 4;
   p.n4 = (n + 3) / 4;   // the buffer is padded to 16 bytes by polar_b200_peer_alloc
+  p.channel = channel;
   p.rank = rank; p.world = world; p.n_seg = n_segments;
   p.scale_w = scale_w; p.scale_g = scale_g;
   // Every CTA waits on the other ranks, so all of them must be resident at once: at most one
   // per SM, launched cooperatively (the driver then starts the grid only as a whole, also
-  // when other kernels are holding SMs at that moment).
-  uint64_t most = p.n4;
-  uint64_t want = (most + peer::kThreads - 1) / peer::kThreads;
+  // when other kernels are holding SMs at that moment).  Channel 0 is the exchange that has
+  // the GPU to itself: 512 threads per CTA.  The other channels are meant to run BESIDE a
+  // tensor-core matmul that already holds 576 threads and most of the registers of every SM:
+  // 128 threads per CTA fit next to it.
+  const unsigned threads = channel == 0 ? peer::kThreads : 128;
+  uint64_t want = (p.n4 + threads - 1) / threads;
   unsigned grid = (unsigned)(want < (uint64_t)sm_count() ? (want ? want : 1) : (uint64_t)sm_count());
   cudaStream_t st = as_stream(stream);
   const void* fn = nullptr;
@@ -332,9 +347,21 @@ int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t worl
     default: fn = reinterpret_cast<const void*>(&peer::allreduce_fadd_kernel<0>); break;
   }
   void* kargs[] = {&p};
-  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(peer::kThreads), kargs, 0, st);
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(threads), kargs, 0, st);
   if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "allreduce_fadd cooperative launch", e);
   return check_launch("allreduce_fadd launch");
+}
+
+int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
+                              const polar_b200_update_segment* segments, uint32_t n_segments, float scale_w,
+                              float scale_g, void* stream) {
+  return allreduce_fadd_impl(buffers, rank, world, 0, 0, n, segments, n_segments, scale_w, scale_g, stream);
+}
+
+int polar_b200_allreduce_fadd_range(void* const* buffers, uint32_t rank, uint32_t world, uint32_t channel,
+                                    uint64_t first, uint64_t count, const polar_b200_update_segment* segments,
+                                    uint32_t n_segments, float scale_w, float scale_g, void* stream) {
+  return allreduce_fadd_impl(buffers, rank, world, channel, first, count, segments, n_segments, scale_w, scale_g, stream);
 }
 
 }  // extern "C"

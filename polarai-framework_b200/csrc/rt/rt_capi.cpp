@@ -230,8 +230,8 @@ int polar_b200_rt_adopt(polar_b200_rt* rt, int device, uint64_t va, uint64_t byt
 }
 
 int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, uint32_t rank, uint32_t world,
-                                 uint64_t n, const polar_b200_rt_update* updates, uint32_t n_updates, float scale_w,
-                                 float scale_g) {
+                                 uint32_t channel, uint64_t first, uint64_t count, const polar_b200_rt_update* updates,
+                                 uint32_t n_updates, float scale_w, float scale_g) {
   B200Device* d = dev(rt, device);
   if (!d || (n_updates && !updates) || n_updates > POLAR_B200_MAX_UPDATE_SEGMENTS)
     return fail(rt, POLAR_B200_ERR_INVALID, "no such device, or a bad update list");
@@ -241,15 +241,25 @@ int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buf
   polar_b200_update_segment seg[POLAR_B200_MAX_UPDATE_SEGMENTS];
   auto unlock_all = [&] { for (auto& r : locked) rt->allocator->release(r, *d); };
   for (uint32_t i = 0; i < n_updates; ++i) {
-    MemoryRecord r{updates[i].weight_va, updates[i].count * sizeof(float)};
-    rt->allocator->lock(r, *d, LockType::READ_WRITE);
-    if (int s = allocator_status(rt)) { unlock_all(); return s; }
-    locked.push_back(r);
-    seg[i].weights = static_cast<float*>(d->getAllocator()->getPtr(r));
-    seg[i].offset = updates[i].grad_offset;
-    seg[i].count = updates[i].count;
+    const polar_b200_rt_update& u = updates[i];
+    if ((u.weight_offset + u.count) * sizeof(float) > u.weight_bytes) {
+      unlock_all();
+      return fail(rt, POLAR_B200_ERR_INVALID, "update runs past its weight record");
+    }
+    MemoryRecord r{u.weight_va, u.weight_bytes};
+    bool have = false;
+    for (auto& l : locked) have = have || l == r;
+    if (!have) {
+      rt->allocator->lock(r, *d, LockType::READ_WRITE);
+      if (int s = allocator_status(rt)) { unlock_all(); return s; }
+      locked.push_back(r);
+    }
+    seg[i].weights = static_cast<float*>(d->getAllocator()->getPtr(r)) + u.weight_offset;
+    seg[i].offset = u.grad_offset;
+    seg[i].count = u.count;
   }
-  int status = polar_b200_allreduce_fadd(buffers, rank, world, n, seg, n_updates, scale_w, scale_g, d->stream());
+  int status = polar_b200_allreduce_fadd_range(buffers, rank, world, channel, first, count, seg, n_updates, scale_w,
+                                               scale_g, d->stream());
   if (status) rt->error = polar_b200_last_error();
   else for (auto& r : locked) d->pool().markWritten(r);
   unlock_all();

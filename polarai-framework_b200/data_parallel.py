@@ -99,13 +99,16 @@ class DataParallelExecutor:
     make_program(rows) builds the builtin program for `rows` rows (program.mlp_program,
     program.logreg_program); `sharded` names the inputs whose first dimension is the batch.
     builtins = "extended" applies program.fuse_program (outputs bit-identical to the chain);
-    collective = "peer" asks for the single-kernel exchange over NVLink peer memory.
+    collective = "peer" asks for the single-kernel exchange over NVLink peer memory; with
+    overlap (the default) the last weight gradient is computed in two blocks of rows and the first
+    block's exchange runs on a second stream while the second block is computed
+    (program.overlap_gradient_exchange).
     """
 
     def __init__(self, make_program, global_batch, sharded=("X", "Y"), rank=0, world=1, device="cuda:0",
-                 builtins="extended", collective="peer", timeout_s=None):
+                 builtins="extended", collective="peer", timeout_s=None, overlap=True):
         from .peer_gradients import PeerGradients
-        from .program import DeviceExecutor, fuse_gradient_exchange, fuse_program
+        from .program import DeviceExecutor, fuse_gradient_exchange, fuse_program, overlap_gradient_exchange
         self.rank, self.world = rank, world
         self.device = torch.device(device)
         self.global_batch = global_batch
@@ -121,6 +124,8 @@ class DataParallelExecutor:
             self.collective = "nccl all-reduce, then fadd updates"
             if fused and collective == "peer":
                 xprog = fuse_gradient_exchange(program)
+                if overlap:
+                    xprog = overlap_gradient_exchange(xprog)
                 why = ""
                 peers = None
                 if xprog.exchanged():
@@ -136,6 +141,9 @@ class DataParallelExecutor:
                     program, self.peers = xprog, peers
                     self.collective = ("peer memory over NVLink: sum over ranks and weight update in one kernel "
                                        "per rank")
+                    if any(k == "ALLREDUCE_FADD_PART" for k, _ in xprog.ops):
+                        self.collective += ("; the last weight gradient in two blocks of rows, the first block's "
+                                            "exchange overlapping the second block's matmul")
                 else:
                     if peers is not None:
                         peers.close()

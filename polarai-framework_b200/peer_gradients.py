@@ -14,7 +14,7 @@ import torch
 from .capi import lib
 
 HANDLE_BYTES = 64
-CONTROL_BYTES = 256
+CONTROL_BYTES = 1024     # POLAR_B200_PEER_CONTROL_BYTES: four channels of 256 bytes
 
 
 class UpdateSegment(ctypes.Structure):
@@ -105,19 +105,49 @@ class PeerGradients:
             seg[i].weights, seg[i].offset, seg[i].count = w.data_ptr(), off, count
         return seg
 
+    def piece_segments(self, pieces):
+        """Segment table and payload range [first, first + count) for (weight tensor, gradient name,
+        first row, rows) pieces - rows < 0 = the whole tensor - which must be adjacent in the payload."""
+        seg = (UpdateSegment * len(pieces))()
+        spans = []
+        for i, (w, g, r0, rows) in enumerate(pieces):
+            off, count = self.offsets[g]
+            if w.numel() != count or not w.is_contiguous():
+                raise ValueError(f"weight of {g}: {tuple(w.shape)} does not match the gradient")
+            if rows >= 0:
+                cols = count // w.shape[0]
+                off, count = off + r0 * cols, rows * cols
+                ptr = w.data_ptr() + 4 * r0 * cols
+            else:
+                ptr = w.data_ptr()
+            seg[i].weights, seg[i].offset, seg[i].count = ptr, off, count
+            spans.append((off, off + (count + 3) // 4 * 4))
+        spans.sort()
+        for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+            if a1 != b0:
+                raise ValueError("the pieces of one exchange must be adjacent in the payload")
+        return seg, spans[0][0], spans[-1][1] - spans[0][0]
+
+    def launch_range(self, channel, first, count, seg, scale_w, scale_g, stream):
+        rc = self.lib.cdll.polar_b200_allreduce_fadd_range(self.buffers, self.rank, self.world, channel, first, count,
+                                                           seg, len(seg), scale_w, scale_g, stream)
+        if rc != 0:
+            self.lib.check(rc)
+
     def launch(self, seg, scale_w, scale_g, stream):
         rc = self.lib.cdll.polar_b200_allreduce_fadd(self.buffers, self.rank, self.world, self.n, seg, len(seg),
                                                      scale_w, scale_g, stream)
         if rc != 0:
             self.lib.check(rc)
 
-    def phase_times_us(self):
-        """Durations of the last launch's phases on this rank, from the control block's
-        timestamps (CTA 0): wait for all ranks' gradients, sum + distribute the slice, wait
-        for all slices, update."""
+    def phase_times_us(self, channel=0):
+        """Durations of the last launch's phases on this rank and channel, from the control
+        block's timestamps (CTA 0): wait for all ranks' gradients, sum + distribute the slice,
+        wait for all slices, update."""
         torch.cuda.synchronize(self.device)
         ctl = torch.as_tensor(_DeviceSpan(self.own, CONTROL_BYTES // 4), device=self.device)
-        t = ctl[40:50].view(torch.int64).cpu().tolist()
+        base = channel * 64
+        t = ctl[base + 40:base + 50].view(torch.int64).cpu().tolist()
         return {"ready_wait": (t[1] - t[0]) / 1e3, "sum_slice": (t[2] - t[1]) / 1e3,
                 "done_wait": (t[3] - t[2]) / 1e3, "update": (t[4] - t[3]) / 1e3}
 

@@ -43,11 +43,20 @@ class Program:
         return sum(1 for k, _ in self.ops if k != "ALLREDUCE")
 
     def exchanged(self):
-        """Names of the gradients an ALLREDUCE_FADD op sums, in payload order."""
+        """Names of the gradients the program sums over peer memory, in payload order."""
+        names = []
         for k, a in self.ops:
             if k == "ALLREDUCE_FADD":
-                return [a[i] for i in range(3, len(a), 2)]
-        return []
+                names += [a[i] for i in range(3, len(a), 2) if a[i] not in names]
+            elif k == "ALLREDUCE_FADD_PART":
+                names += [g for _, g, _, _ in exchange_pieces(a) if g not in names]
+        return names
+
+
+def exchange_pieces(args):
+    """(weight, gradient, first row, rows) of every piece an ALLREDUCE_FADD_PART op exchanges;
+    rows < 0 = the whole tensor.  args = [scale_w, scale_g, channel, overlapped, W, g, row0, rows, ...]."""
+    return [(args[i], args[i + 1], int(args[i + 2]), int(args[i + 3])) for i in range(4, len(args), 4)]
 
 
 def elementwise_chain_program(n):
@@ -284,6 +293,49 @@ def fuse_gradient_exchange(program):
                    dict(program.constants), list(program.outputs))
 
 
+def overlap_gradient_exchange(program, tile_rows=256):
+    """Rewrites the tail  fmatmul_t_f(X, D, g); ALLREDUCE_FADD(sw, sg, ..., W, g, ...)  so that most of
+    the exchange runs WHILE the last gradient is still being computed:
+
+        fmatmul_t_f_rows(X, D, 0, r, g)                    rows [0, r) of g
+        ALLREDUCE_FADD_PART(sw, sg, channel 1, overlapped, W, g, 0, r)       on a second stream
+        fmatmul_t_f_rows(X, D, r, m - r, g)                the remaining rows, meanwhile
+        ALLREDUCE_FADD_PART(sw, sg, channel 0, in order,  W, g, r, m - r, <every other pair, whole>)
+
+    r = two thirds of the rows, rounded down to whole tiles.  The payload is laid out with g first,
+    so the second exchange's pieces are contiguous.  Per element the sum over the ranks and the
+    update are unchanged; each block of rows is the fmatmul_t_f product of a column block of X, whose
+    sum over k the tensor-core kernel may cut into work units differently than for the whole matrix -
+    so g agrees with the one-launch form within the fmatmul tolerance (on the CPU oracle, which sums
+    sequentially, bit for bit), and the replicas stay bit-identical to each other.
+    Returned unchanged when the program has no such tail or g has too few rows to cut."""
+    ops = [(k, list(a)) for k, a in program.ops]
+    if len(ops) < 2 or ops[-1][0] != "ALLREDUCE_FADD" or ops[-2][0] != "fmatmul_t_f":
+        return program
+    sw, sg = ops[-1][1][:2]
+    pairs = [(ops[-1][1][i], ops[-1][1][i + 1]) for i in range(2, len(ops[-1][1]), 2)]
+    x, d, g = ops[-2][1]
+    if g not in [gr for _, gr in pairs]:
+        return program
+    m = program.tensors[g][0]
+    r = (2 * m // 3) // tile_rows * tile_rows
+    if r < tile_rows or m - r < 64 or r % 4:
+        return program
+    w = next(wt for wt, gr in pairs if gr == g)
+    rest = [(wt, gr) for wt, gr in pairs if gr != g]
+    last = [float(sw), float(sg), 0.0, 0.0, w, g, float(r), float(m - r)]
+    for wt, gr in rest:
+        last += [wt, gr, 0.0, -1.0]
+    new_ops = ops[:-2] + [
+        ("fmatmul_t_f_rows", [x, d, 0.0, float(r), g]),
+        ("ALLREDUCE_FADD_PART", [float(sw), float(sg), 1.0, 1.0, w, g, 0.0, float(r)]),
+        ("fmatmul_t_f_rows", [x, d, float(r), float(m - r), g]),
+        ("ALLREDUCE_FADD_PART", last),
+    ]
+    return Program(program.name + "_overlap", dict(program.tensors), new_ops, list(program.inputs),
+                   dict(program.constants), list(program.outputs))
+
+
 class DeviceExecutor:
     """Runs a Program on one GPU: one device tensor per program tensor, every op
     through polar_b200_launch_by_name on torch's current stream.  Argument
@@ -318,6 +370,12 @@ class DeviceExecutor:
                 pairs = [(self.t[args[i]], args[i + 1]) for i in range(2, len(args), 2)]
                 self._compiled.append(("peers", (peers.segments(pairs), float(args[0]), float(args[1])), 0))
                 continue
+            if kernel == "ALLREDUCE_FADD_PART":
+                pieces = [(self.t[w], g, r0, rows) for w, g, r0, rows in exchange_pieces(args)]
+                seg, first, count = peers.piece_segments(pieces)
+                self._compiled.append(("peers_part", (seg, first, count, int(args[2]), bool(args[3]), float(args[0]),
+                                                      float(args[1])), 0))
+                continue
             arr = (Arg * len(args))()
             for i, a in enumerate(args):
                 if isinstance(a, str):
@@ -334,6 +392,12 @@ class DeviceExecutor:
             self._keep.append(arr)
             self._compiled.append((kernel.encode(), arr, len(args)))
         self._fn = fn
+        # an exchange marked "overlapped" runs on a second stream, forked from the launch stream where
+        # the op stands and joined at the end of the program
+        self._side = None
+        if any(k == "peers_part" and a[4] for k, a, _ in self._compiled):
+            self._side = torch.cuda.Stream(self.device)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
         # one scratch buffer, sized for the most demanding launch of the program
         wsb = self.lib.cdll.polar_b200_launch_workspace_bytes
         need = max([0] + [int(wsb(k, arr, n)) for k, arr, n in self._compiled if isinstance(k, bytes)])
@@ -351,7 +415,9 @@ class DeviceExecutor:
             self.t[name].copy_(a if isinstance(a, torch.Tensor) else torch.from_numpy(a))
 
     def run(self):
-        s = torch.cuda.current_stream(self.device).cuda_stream
+        main = torch.cuda.current_stream(self.device)
+        s = main.cuda_stream
+        forked = False
         for kernel, arr, n in self._compiled:
             if kernel is None:
                 if self.allreduce is not None:
@@ -360,9 +426,22 @@ class DeviceExecutor:
             if kernel == "peers":
                 self.peers.launch(arr[0], arr[1], arr[2], s)
                 continue
+            if kernel == "peers_part":
+                seg, first, count, channel, overlapped, sw, sg = arr
+                if overlapped:
+                    self._fork.record(main)
+                    self._side.wait_event(self._fork)
+                    self.peers.launch_range(channel, first, count, seg, sw, sg, self._side.cuda_stream)
+                    forked = True
+                else:
+                    self.peers.launch_range(channel, first, count, seg, sw, sg, s)
+                continue
             rc = self._fn(kernel, arr, n, self._ws_ptr, self._ws_bytes, s)
             if rc != 0:
                 self.lib.check(rc)
+        if forked:
+            self._join.record(self._side)
+            main.wait_event(self._join)
 
     def output(self, name):
         torch.cuda.synchronize(self.device)

@@ -38,7 +38,8 @@ class LaunchCommand(ctypes.Structure):
 
 
 class RtUpdate(ctypes.Structure):
-    _fields_ = [("weight_va", _u64), ("grad_offset", _u64), ("count", _u64)]
+    _fields_ = [("weight_va", _u64), ("weight_bytes", _u64), ("weight_offset", _u64), ("grad_offset", _u64),
+                ("count", _u64)]
 
 
 RT_SIGNATURES = {
@@ -54,8 +55,9 @@ RT_SIGNATURES = {
     "polar_b200_rt_read": (_i, [_p, _u64, _u64, _p]),
     "polar_b200_rt_launch": (_i, [_p, _i, ctypes.POINTER(LaunchCommand)]),
     "polar_b200_rt_adopt": (_i, [_p, _i, _u64, _u64, _p]),
-    "polar_b200_rt_allreduce_fadd": (_i, [_p, _i, ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32, _u64,
-                                          ctypes.POINTER(RtUpdate), ctypes.c_uint32, ctypes.c_float, ctypes.c_float]),
+    "polar_b200_rt_allreduce_fadd": (_i, [_p, _i, ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32,
+                                          ctypes.c_uint32, _u64, _u64, ctypes.POINTER(RtUpdate), ctypes.c_uint32,
+                                          ctypes.c_float, ctypes.c_float]),
     "polar_b200_rt_barrier": (_i, [_p, _i]),
     "polar_b200_rt_device_ptr": (_p, [_p, _i, _u64, _u64]),
     "polar_b200_rt_stream": (_p, [_p, _i]),
@@ -286,7 +288,8 @@ class RuntimeProgramExecutor:
     A program with an ALLREDUCE_FADD op (program.fuse_gradient_exchange) needs `peers`, a
     PeerGradients built for program.exchanged(): those gradients are adopted as records whose
     device memory is the rank's NVLink peer buffer, and the op becomes
-    polar_b200_rt_allreduce_fadd.  Plain ALLREDUCE ops are no-ops here (single rank)."""
+    polar_b200_rt_allreduce_fadd (an exchange the program marks "overlapped" runs in order here:
+    the plugin drives one stream per device).  Plain ALLREDUCE ops are no-ops here (single rank)."""
 
     def __init__(self, program, rt=None, device=0, peers=None):
         self.program = program
@@ -309,13 +312,30 @@ class RuntimeProgramExecutor:
         for kernel, args in program.ops:
             if kernel == "ALLREDUCE":
                 continue
-            if kernel == "ALLREDUCE_FADD":
-                pairs = [(args[i], args[i + 1]) for i in range(2, len(args), 2)]
-                upd = (RtUpdate * len(pairs))()
-                for u, (w, g) in zip(upd, pairs):
+            if kernel in ("ALLREDUCE_FADD", "ALLREDUCE_FADD_PART"):
+                if kernel == "ALLREDUCE_FADD":
+                    pieces, channel = [(args[i], args[i + 1], 0, -1) for i in range(2, len(args), 2)], 0
+                else:
+                    from .program import exchange_pieces
+                    pieces, channel = exchange_pieces(args), int(args[2])
+                upd = (RtUpdate * len(pieces))()
+                spans = []
+                for u, (w, g, r0, rows) in zip(upd, pieces):
                     off, count = peers.offsets[g]
-                    u.weight_va, u.grad_offset, u.count = self.t[w].virt_addr, off, count
-                self._steps.append(("exchange", (upd, len(pairs), float(args[0]), float(args[1]))))
+                    wt = self.t[w]
+                    woff = 0
+                    if rows >= 0:
+                        cols = count // wt.shape[0]
+                        off, count, woff = off + r0 * cols, rows * cols, r0 * cols
+                    u.weight_va, u.weight_bytes, u.weight_offset = wt.virt_addr, wt.bytes, woff
+                    u.grad_offset, u.count = off, count
+                    spans.append((off, off + (count + 3) // 4 * 4))
+                spans.sort()
+                first, total = spans[0][0], spans[-1][1] - spans[0][0]
+                if kernel == "ALLREDUCE_FADD":
+                    first, total = 0, peers.n
+                self._steps.append(("exchange", (upd, len(pieces), float(args[0]), float(args[1]), channel, first,
+                                                 total)))
                 continue
             cmd, keep = self.rt.command(kernel, [self.t[a] if isinstance(a, str) else a for a in args])
             self._keep.append(keep)
@@ -331,10 +351,10 @@ class RuntimeProgramExecutor:
             if kind == "launch":
                 rt.launch_command(what, dev)
             else:
-                upd, n, sw, sg = what
+                upd, n, sw, sg, channel, first, total = what
                 p = self.peers
-                rt._check(rt.cdll.polar_b200_rt_allreduce_fadd(rt.h, dev, p.buffers, p.rank, p.world, p.n, upd, n,
-                                                               sw, sg))
+                rt._check(rt.cdll.polar_b200_rt_allreduce_fadd(rt.h, dev, p.buffers, p.rank, p.world, channel, first,
+                                                               total, upd, n, sw, sg))
 
     def output(self, name, out=None):
         return self.rt.read(self.t[name], out)

@@ -291,3 +291,41 @@ def test_result_that_is_only_4_byte_aligned(gpu, par_oracle):
         d.fmatmul(tl, tr, L, R, out)
         torch.cuda.synchronize()
         assert rel_err(out.cpu().numpy(), ref, mag) <= 5e-6
+
+
+@pytest.mark.parametrize("m,n,k,row0,rows", [(784, 4096, 8192, 0, 512), (784, 4096, 8192, 512, 272), (1024, 512, 2048, 256, 768),
+                                            (784, 512, 4096, 0, 784)])
+def test_block_of_rows_of_a_t_f_product(gpu, par_oracle, m, n, k, row0, rows):
+    # out[row0 : row0+rows] of left^T.right, the other rows untouched; through the entry point and by name
+    import ctypes
+    import torch
+    from polarai_framework_b200.capi import Arg
+    rng = np.random.default_rng(m + n + k + row0)
+    l, r = operands(rng, 1, 0, m, n, k)
+    ref, mag = par_oracle.fmatmul_f64(1, 0, np.ascontiguousarray(l[:, row0:row0 + rows]), r)
+    L, R = torch.from_numpy(l).cuda(), torch.from_numpy(r).cuda()
+    lib = gpu.d.lib
+    st = torch.cuda.current_stream().cuda_stream
+    out = torch.full((m, n), float("nan"), device="cuda")
+    lib.call("polar_b200_fmatmul_t_f_rows", m, row0, rows, n, k, L.data_ptr(), R.data_ptr(), out.data_ptr(), None, 0, st)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert rel_err(got[row0:row0 + rows], ref, mag) <= 5e-6
+    assert np.isnan(got[:row0]).all() and np.isnan(got[row0 + rows:]).all()
+    # by name, with a caller workspace of the size the library asks for
+    args = (Arg * 5)()
+    shapes = [(ctypes.c_uint64 * 2)(k, m), (ctypes.c_uint64 * 2)(k, n), None, None, (ctypes.c_uint64 * 2)(m, n)]
+    out2 = torch.full((m, n), float("nan"), device="cuda")
+    for a, t, shp in zip(args, (L, R, None, None, out2), shapes):
+        if t is not None:
+            a.is_tensor, a.tensor.data, a.tensor.dims, a.tensor.shape = 1, t.data_ptr(), 2, shp
+    args[2].scalar, args[3].scalar = float(row0), float(rows)
+    need = int(lib.cdll.polar_b200_launch_workspace_bytes(b"fmatmul_t_f_rows", args, 5))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    lib.call("polar_b200_launch_by_name", b"fmatmul_t_f_rows", args, 5, ws.data_ptr() if need else None, need, st)
+    torch.cuda.synchronize()
+    assert np.array_equal(out2.cpu().numpy()[row0:row0 + rows].view(np.uint32), got[row0:row0 + rows].view(np.uint32))
+    assert gpu.d.device_status() == 0
+    # a block that does not start on a multiple of 4, or runs past the result: statuses
+    assert lib.cdll.polar_b200_fmatmul_t_f_rows(m, 2, 64, n, k, L.data_ptr(), R.data_ptr(), out.data_ptr(), None, 0, st) == 1
+    assert lib.cdll.polar_b200_fmatmul_t_f_rows(m, 0, m + 4, n, k, L.data_ptr(), R.data_ptr(), out.data_ptr(), None, 0, st) == 1

@@ -36,17 +36,27 @@ def test_one_rank_equals_the_plain_program_over_several_steps():
     fused = fuse_program(mlp_program(batch, 784, hidden, 10, 0.1))
     xprog = fuse_gradient_exchange(fused)
     peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, 0, 1, "cuda:0")
+    from polarai_framework_b200.program import overlap_gradient_exchange
+    oprog = overlap_gradient_exchange(xprog)
+    opeers = PeerGradients({g: oprog.tensors[g] for g in oprog.exchanged()}, 0, 1, "cuda:0")
     a = DeviceExecutor(fused, "cuda:0")
     b = DeviceExecutor(xprog, "cuda:0", peers=peers)
-    for ex in (a, b):
+    c = DeviceExecutor(oprog, "cuda:0", peers=opeers)
+    for ex in (a, b, c):
         ex.set_inputs(X=X, Y=Y, W1=W1, W2=W2)
     for step in range(4):
-        a.run(), b.run()
+        a.run(), b.run(), c.run()
         for k in ("L", "W1", "W2", "dW1", "dW2"):
             assert np.array_equal(a.output(k).view(np.uint32), b.output(k).view(np.uint32)), (step, k)
+        # dW1 in two blocks of rows on two streams: the same sums up to how k is cut
+        for k in ("L", "dW2"):
+            assert np.array_equal(a.output(k).view(np.uint32), c.output(k).view(np.uint32)), (step, k)
+        for k in ("dW1", "W1", "W2"):
+            assert np.max(np.abs(a.output(k) - c.output(k))) <= 1e-5 * np.abs(a.output(k)).max(), (step, k)
     assert lib.cdll.polar_b200_device_status() == 0
-    del b
+    del b, c
     peers.close()
+    opeers.close()
 
 
 def test_bad_arguments_are_statuses():
@@ -140,7 +150,8 @@ def _rank_main(rank, world, port, out_dir):
     pkg = ge.load_package()
     from polarai_framework_b200.data_parallel import init_from_env, make_allreduce, shard_rows
     from polarai_framework_b200.peer_gradients import PeerGradients
-    from polarai_framework_b200.program import DeviceExecutor, fuse_gradient_exchange, fuse_program, mlp_program
+    from polarai_framework_b200.program import (DeviceExecutor, fuse_gradient_exchange, fuse_program, mlp_program,
+                                                overlap_gradient_exchange)
     r, w, local = init_from_env("nccl")
     dev = f"cuda:{local}"
     batch, hidden = 1024, 1024
@@ -149,22 +160,40 @@ def _rank_main(rank, world, port, out_dir):
     fused = fuse_program(mlp_program(hi - lo, 784, hidden, 10, 0.1))
     xprog = fuse_gradient_exchange(fused)
     peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, r, w, dev)
+    # the same exchange cut in two: the first block of dW1's rows travels on a second stream while
+    # the second block is computed
+    oprog = overlap_gradient_exchange(xprog)
+    assert oprog.ops[-1][0] == "ALLREDUCE_FADD_PART"
+    opeers = PeerGradients({g: oprog.tensors[g] for g in oprog.exchanged()}, r, w, dev)
     a = DeviceExecutor(fused, dev, make_allreduce(w))
     b = DeviceExecutor(xprog, dev, peers=peers)
-    for ex in (a, b):
+    c = DeviceExecutor(oprog, dev, peers=opeers)
+    for ex in (a, b, c):
         ex.set_inputs(X=X[lo:hi], Y=Y[lo:hi], W1=W1, W2=W2)
     res = {}
     for step in range(3):
-        a.run(), b.run()
+        a.run(), b.run(), c.run()
+    torch.cuda.synchronize()
+    # and once more as a CUDA graph (fork and join of the second stream are captured)
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            c.run()
+    torch.cuda.synchronize()
+    dist.barrier()
+    a.run(), b.run(), g.replay()
     torch.cuda.synchronize()
     for k in ("W1", "W2", "dW1", "dW2"):
-        res[f"nccl_{k}"], res[f"peer_{k}"] = a.output(k), b.output(k)
+        res[f"nccl_{k}"], res[f"peer_{k}"], res[f"over_{k}"] = a.output(k), b.output(k), c.output(k)
     res["status"] = np.array([pkg.lib().cdll.polar_b200_device_status()])
     np.savez(os.path.join(out_dir, f"rank{r}.npz"), **res)
     dist.barrier()
     torch.cuda.synchronize()
-    del b
+    del b, c, g
     peers.close()
+    opeers.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -181,3 +210,6 @@ def test_two_ranks_on_two_gpus(tmp_path):
     for k in ("W1", "W2", "dW1", "dW2"):
         assert np.array_equal(r0[f"peer_{k}"], r1[f"peer_{k}"]), k            # replicas identical
         assert np.array_equal(r0[f"peer_{k}"], r0[f"nccl_{k}"]), k            # a + b has one rounding
+        assert np.array_equal(r0[f"over_{k}"], r1[f"over_{k}"]), k            # overlapped form: replicas identical too
+        scale = np.abs(r0[f"peer_{k}"]).max()
+        assert np.max(np.abs(r0[f"over_{k}"] - r0[f"peer_{k}"])) <= 1e-5 * scale, k   # k cut differently, same sums

@@ -14,8 +14,8 @@ import __graft_entry__ as ge  # noqa: E402
 
 ge.load_package()
 from polarai_framework_b200.peer_gradients import payload_layout, slice_bounds  # noqa: E402
-from polarai_framework_b200.program import (Program, fuse_gradient_exchange, fuse_program, logreg_program,  # noqa: E402
-                                            mlp_program)
+from polarai_framework_b200.program import (Program, exchange_pieces, fuse_gradient_exchange, fuse_program,  # noqa: E402
+                                            logreg_program, mlp_program, overlap_gradient_exchange)
 
 
 def test_rewrite_of_the_mlp_tail():
@@ -92,6 +92,26 @@ def test_rewritten_program_equals_the_plain_one_on_the_oracle():
         assert np.array_equal(outs[0][k], outs[1][k]), k
 
 
+def test_overlap_rewrite_cuts_the_last_gradient_by_rows():
+    base = fuse_gradient_exchange(fuse_program(mlp_program(64, 784, 96, 10, 0.1)))
+    p = overlap_gradient_exchange(base)
+    kinds = [k for k, _ in p.ops]
+    assert kinds[-4:] == ["fmatmul_t_f_rows", "ALLREDUCE_FADD_PART", "fmatmul_t_f_rows", "ALLREDUCE_FADD_PART"]
+    (_, a1), (_, x1), (_, a2), (_, x2) = p.ops[-4:]
+    assert a1 == ["X", "dZ1", 0.0, 512.0, "dW1"] and a2 == ["X", "dZ1", 512.0, 272.0, "dW1"]   # 784 = 512 + 272
+    assert x1[2:4] == [1.0, 1.0] and exchange_pieces(x1) == [("W1", "dW1", 0, 512)]               # channel 1, overlapped
+    assert x2[2:4] == [0.0, 0.0] and exchange_pieces(x2) == [("W1", "dW1", 512, 272), ("W2", "dW2", 0, -1)]
+    assert p.exchanged() == ["dW1", "dW2"]          # payload order: the rest of dW1 and dW2 are adjacent
+    # the pieces of the second exchange are adjacent in the payload, the first one starts it
+    offsets, n = payload_layout({g: p.tensors[g] for g in p.exchanged()})
+    assert offsets["dW1"] == (0, 784 * 96) and offsets["dW2"][0] == 784 * 96
+    # too few rows to cut, or no exchange at the end: unchanged
+    small = fuse_gradient_exchange(fuse_program(mlp_program(64, 300, 96, 10, 0.1)))
+    assert overlap_gradient_exchange(small) is small
+    plain = mlp_program(64, 784, 96, 10, 0.1)
+    assert overlap_gradient_exchange(plain) is plain
+
+
 def _worker(rank, world, port, batch, hidden, out_dir):
     sys.path.insert(0, ROOT)
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
@@ -112,10 +132,13 @@ def _worker(rank, world, port, batch, hidden, out_dir):
         return t.numpy()
 
     res = {}
-    for tag, rewrite in (("plain", False), ("xchg", True)):
+    for tag, rewrite in (("plain", 0), ("xchg", 1), ("over", 2)):
         prog = mlp_program(hi - lo, 784, hidden, 10, 0.1)
         if rewrite:
             prog = fuse_gradient_exchange(fuse_program(prog))
+        if rewrite == 2:
+            prog = overlap_gradient_exchange(prog)
+            assert prog.ops[-1][0] == "ALLREDUCE_FADD_PART"
         ex = OracleExecutor(prog, orc.Oracle(2), allreduce)
         ex.set_inputs(X=X[lo:hi], Y=Y[lo:hi], W1=W1, W2=W2)
         ex.run()
@@ -133,3 +156,5 @@ def test_two_gloo_ranks_rewritten_equals_plain(tmp_path):
     for k in ("W1", "W2", "dW1", "dW2"):
         assert np.array_equal(r0[f"xchg_{k}"], r0[f"plain_{k}"]), k      # same sums, same update arithmetic
         assert np.array_equal(r0[f"xchg_{k}"], r1[f"xchg_{k}"]), k       # replicas identical
+        assert np.array_equal(r0[f"over_{k}"], r0[f"plain_{k}"]), k      # cut by rows and exchanged in two parts: same bits
+        assert np.array_equal(r0[f"over_{k}"], r1[f"over_{k}"]), k
