@@ -419,7 +419,8 @@ def run_mlp(args):
     W1, W2 = mlp_weights(rng)
     fused = args.builtins == "extended"
     dp = DataParallelExecutor(lambda rows: mlp_program(rows, N_IN, N_HIDDEN, N_OUT, LR), GLOBAL_BATCH, ("X", "Y"),
-                              rank, world, dev, builtins=args.builtins, collective=args.collective)
+                              rank, world, dev, builtins=args.builtins, collective=args.collective,
+                              overlap=args.overlap_exchange)
     ex, program, chain, peers, per = dp.ex, dp.program, dp.chain, dp.peers, dp.rows
     Xs, Ys = np.ascontiguousarray(X[dp.lo:dp.hi]), np.ascontiguousarray(Y[dp.lo:dp.hi])
     x_host = torch.from_numpy(Xs).pin_memory()
@@ -944,6 +945,9 @@ def main():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="mlp at N>1 with extended builtins: gradient sum + update as one peer-memory kernel, "
                          "or NCCL all-reduces followed by fadd")
+    ap.add_argument("--overlap-exchange", action="store_true",
+                    help="mlp at N>1: compute the last weight gradient in two blocks of rows and exchange the first "
+                         "block on a second stream meanwhile (measured slower at these shapes; off by default)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-parity", action="store_true",

@@ -100,13 +100,15 @@ class DataParallelExecutor:
     program.logreg_program); `sharded` names the inputs whose first dimension is the batch.
     builtins = "extended" applies program.fuse_program (outputs bit-identical to the chain);
     collective = "peer" asks for the single-kernel exchange over NVLink peer memory; with
-    overlap (the default) the last weight gradient is computed in two blocks of rows and the first
-    block's exchange runs on a second stream while the second block is computed
-    (program.overlap_gradient_exchange).
+    overlap=True the last weight gradient is computed in two blocks of rows and the first block's
+    exchange runs on a second stream while the second block is computed
+    (program.overlap_gradient_exchange).  Off by default: on B200 the two-block matmul costs
+    34-40 us more than the one-launch form at the per-GPU shapes of the 784-4096-10 step, which is
+    what the overlap hides of the exchange - measured 0.805 vs 0.779 ms per step at 8 GPUs.
     """
 
     def __init__(self, make_program, global_batch, sharded=("X", "Y"), rank=0, world=1, device="cuda:0",
-                 builtins="extended", collective="peer", timeout_s=None, overlap=True):
+                 builtins="extended", collective="peer", timeout_s=None, overlap=False):
         from .peer_gradients import PeerGradients
         from .program import DeviceExecutor, fuse_gradient_exchange, fuse_program, overlap_gradient_exchange
         self.rank, self.world = rank, world
