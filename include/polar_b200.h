@@ -227,7 +227,8 @@ int polar_b200_fmatmul_ffma(int transLeft, int transRight, uint64_t m,
 
 /* The tensor-core path alone, with its tuning knobs exposed for tests and
  * benchmarks: tile_n is 128 or 256 (128 x tile_n tiles), or 512 for 256 x 256 tiles
- * (slab_k 16 only); slab_k is 16 or 32 (floats of k staged per pipeline stage); passes is 3 (fp32-accurate three-product
+ * (slab_k 16 only), plus 1000 to make the operands exchange roles (see
+ * polar_b200_fmatmul_tc_plan; not with stream mode); slab_k is 16 or 32 (floats of k staged per pipeline stage); passes is 3 (fp32-accurate three-product
  * TF32 split) or 1 (plain TF32, about 1e-3 relative); write_hi == 1 makes the
  * split warps store the masked high parts explicitly instead of relying on the
  * tensor core ignoring the low 13 mantissa bits (2: diagnostic, the result is not
@@ -272,6 +273,17 @@ uint64_t polar_b200_wait_limit_ns(void);
  * 2 = FFMA tiles. */
 int polar_b200_fmatmul_path(int transLeft, int transRight, uint64_t m,
                             uint64_t n, uint64_t k);
+
+/* How the tensor-core path would run the product (meaningful when polar_b200_fmatmul_path
+ * answers 0): *tile_rows = 128 or 256 (rows of a CTA tile; columns are 256), *exchanged = 1
+ * when the operands exchange roles - the kernel computes the transposed product with `right`
+ * as its row operand and stores each tile transposed, so that a warp's store instruction
+ * writes one 128-byte line of a result row (taken for sums of a few hundred to a few thousand
+ * terms, where the epilogue is a visible share of a tile's time) - and *splits = work units per
+ * tile (1 = whole tiles, 0 = stream mode, >1 = fixed cuts of k).  For a t_f product with rows
+ * just past a tile boundary the answer describes the whole-tile part.  Any pointer may be NULL. */
+void polar_b200_fmatmul_tc_plan(int transLeft, int transRight, uint64_t m, uint64_t n, uint64_t k,
+                                int* tile_rows, int* exchanged, int* splits);
 
 /* ---- extended builtins (beside, never instead of, the ones above) -------- */
 

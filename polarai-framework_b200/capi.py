@@ -63,6 +63,7 @@ SIGNATURES = {
     "polar_b200_fmatmul_tn_small_n_static": (_i, [_i, _u64, _u64, _u64, _p, _p, _p, _p]),
     "polar_b200_static_scratch_bytes": (_u64, []),
     "polar_b200_fmatmul_path": (_i, [_i, _i, _u64, _u64, _u64]),
+    "polar_b200_fmatmul_tc_plan": (None, [_i, _i, _u64, _u64, _u64, _p, _p, _p]),
     "polar_b200_device_status": (_i, []),
     "polar_b200_device_status_clear": (None, []),
     "polar_b200_device_status_of": (_i, [_i]),

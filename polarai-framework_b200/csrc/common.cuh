@@ -99,18 +99,23 @@ private:
 // epilogue so that both give the same bits: r = 1/(1+exp(-x)), then the reference's
 // clamp to [1e-5, 1-1e-5] (opencl/kernels.h:141-156 of the reference).
 __device__ __forceinline__ float sigmoid_clamped(float x) {
+  // Six instructions, two of them on the special-function unit: ex2.approx of -x * log2 e, 1 + e,
+  // rcp.approx, and the clamp as one min and one max.  In the tensor-core epilogue, which cannot
+  // overlap the next tile's k loop with 256-row tiles, the sigmoid is a large part of the drain,
+  // and a dozen instructions per element (IEEE reciprocal, compare-and-select clamp) made the
+  // drain issue-bound.
+  //  - Error: ex2.approx is good to 2 ulp, the product -x * log2 e adds |x| * 6e-8 relative to the
+  //    exponential (at most 8e-7 where it still matters: |x| < 11.6, beyond which the clamp takes
+  //    over), rcp.approx 1 ulp: within the 1e-5 the builtin is held to, by a factor 10.
+  //  - The clamp: r lies in [0, 1], so the reference's "|r - 1| < eps -> 1 - eps, else |r| < eps
+  //    -> eps" is min(r, fl(1 - eps)) followed by max(., eps); the .NaN forms keep a NaN a NaN,
+  //    as the reference's comparisons (all false) do.
   const float eps = 1e-5f;
-  // exp through the special-function unit (ex2.approx of -x * log2 e): two instructions
-  // instead of a dozen.  In the tensor-core epilogue, which cannot overlap the next tile's k
-  // loop with 256-row tiles, the sigmoid is a large part of the drain.  Error: ex2.approx is
-  // good to 2 ulp and the product -x * log2 e adds |x| * 6e-8 relative to the exponential - at
-  // most 8e-7 where it still matters (|x| < 11.6, beyond which the clamp takes over): within
-  // the 1e-5 the builtin is held to, by a factor 10.  The reciprocal stays correctly rounded
-  // (the same bits as IEEE division of 1 by d, without the division's slow-path branch, which
-  // keeps independent elements from being interleaved in the epilogue).
-  float r = __frcp_rn(__fadd_rn(1.0f, __expf(-x)));
-  const float hi = __fadd_rn(1.0f, -eps);
-  r = (fabsf(__fadd_rn(r, -1.0f)) < eps) ? hi : ((fabsf(r) < eps) ? eps : r);
+  const float hi = 1.0f - eps;   // folded at compile time, the same float as fadd(1, -eps)
+  float d = __fadd_rn(1.0f, __expf(-x)), r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  asm("min.NaN.f32 %0, %0, %1;" : "+f"(r) : "f"(hi));
+  asm("max.NaN.f32 %0, %0, %1;" : "+f"(r) : "f"(eps));
   return r;
 }
 // The reference's Sigmoid derivative chain on one element, with its three roundings:

@@ -1,4 +1,5 @@
 // fmatmul entry points and dispatch by native kernel name.
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -9,7 +10,8 @@ int launch_ffma(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
                 const float* right, float* out, cudaStream_t stream);
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch = 0, int mt = 1);
+              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch = 0, int mt = 1,
+              int swap_ab = 0);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k, int mt = 1);
 uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits, int mt = 1);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -47,27 +49,27 @@ int choose_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float*
 int run_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left, const float* right,
            float* out, int bn, int bk, int passes, int write_hi, uint32_t splits, void* workspace,
            uint64_t workspace_bytes, cudaStream_t stream, int epilogue = 0, uint64_t left_pitch = 0,
-           int mt = 1) {
+           int mt = 1, int swap_ab = 0) {
   if (splits == 1)
     return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream,
-                     left_pitch, mt);
+                     left_pitch, mt, swap_ab);
   // splits == 0 is the stream mode of the 256-column tile configurations
   if (splits == 0 && bn != 256) splits = 1;
   const uint64_t need = splits == 0 ? tc_workspace_bytes(m, n, k, 0, mt) : (uint64_t)splits * m * n * sizeof(float);
   if (need == 0)   // stream mode asked for a shape it does not suit
     return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, nullptr, 1, epilogue, stream,
-                     left_pitch, mt);
+                     left_pitch, mt, swap_ab);
   if (workspace) {
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
       return fail(POLAR_B200_ERR_WORKSPACE, "workspace too small or not 16-byte aligned");
     return launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(workspace),
-                     splits, epilogue, stream, left_pitch, mt);
+                     splits, epilogue, stream, left_pitch, mt, swap_ab);
   }
   void* ws = nullptr;
   cudaError_t e = cudaMallocAsync(&ws, need, stream);
   if (e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaMallocAsync(workspace)", e);
   int rc = launch_tc(tl, tr, m, n, k, left, right, out, bn, bk, passes, write_hi, static_cast<float*>(ws), splits,
-                     epilogue, stream, left_pitch, mt);
+                     epilogue, stream, left_pitch, mt, swap_ab);
   e = cudaFreeAsync(ws, stream);
   if (rc == POLAR_B200_OK && e != cudaSuccess) return fail(POLAR_B200_ERR_CUDA, "cudaFreeAsync(workspace)", e);
   return rc;
@@ -116,29 +118,59 @@ SideStream* side_stream() {
 
 inline uint64_t align256(uint64_t b) { return (b + 255) & ~255ull; }
 
-// Row sub-tiles per CTA tile for the tensor-core path: 256 x 256 tiles (2) fetch a third fewer
-// operand bytes per flop than 128 x 256 (1) and are 12-50 % faster on long sums (8192^3: 285
-// vs 242 TFLOP/s, t_f 275 vs 180), but pad m to a multiple of 256, cannot overlap a tile's
-// epilogue with the next tile's k loop (both accumulators belong to one tile), and make half
-// as many tiles, which matters when those fill the last wave badly and k is too short to cut.
-// The choice compares padded rows x relative cost per row / wave efficiency of both.
-int tc_tile_rows(uint64_t m, uint64_t n, uint64_t k) {
-  if (m < 256 || k < 512) return 1;
+// How the tensor-core path runs one product.
+//  mt: row sub-tiles per CTA tile.  256 x 256 tiles (2) fetch a third fewer operand bytes per
+//    flop than 128 x 256 (1) and are 12-50 % faster on long sums (8192^3: 285 vs 242 TFLOP/s,
+//    t_f 275 vs 180), but pad the tile rows to a multiple of 256, cannot overlap a tile's epilogue
+//    with the next tile's k loop (both accumulators belong to one tile), and make half as many
+//    tiles, which matters when those fill the last wave badly and k is too short to cut.
+//  swap: the operands exchange roles (launch_tc), which turns the epilogue's stores into whole
+//    128-byte lines: 2-4 % on sums of a few hundred to a few thousand terms, where the epilogue
+//    is a visible share of a tile; needs whole tiles or fixed k cuts, and no row pitch.
+//  splits: as tc_default_splits, for the orientation chosen.
+// The choice compares padded tile area x relative cost / wave efficiency of the candidates.
+struct TcChoice {
+  int mt;
+  int swap;
+  uint32_t splits;
+};
+
+TcChoice tc_choose(uint64_t m, uint64_t n, uint64_t k, bool may_swap) {
   const double sms = (double)sm_count();
-  double est[3] = {0, 0, 0};
-  for (int mt = 1; mt <= 2; ++mt) {
-    const uint64_t rows = 128ull * mt;
-    const uint64_t tiles_m = (m + rows - 1) / rows, tiles = tiles_m * ((n + 255) / 256);
-    double eff = 1.0;
-    if (k < 2048 && (double)tiles < 8 * sms) {          // too short to cut: whole waves of tiles
-      const double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
-      eff = (double)tiles / (waves * sms);
-    }
-    // measured: 0.67-0.85 of the 128-row cost from k = 16384 up, 0.9-0.93 at k = 784 ... 8192
-    const double cost = mt == 1 ? 1.0 : (k < 16384 ? 0.9 : 0.75);
-    est[mt] = (double)(tiles_m * rows) * cost / eff;
+  if (const char* f = getenv("POLAR_B200_TC_FORCE")) {   // PROBE ONLY
+    int mt = f[0] - '0', swap = f[1] - '0';
+    if (!may_swap) swap = 0;
+    uint32_t sp = swap ? tc_default_splits(n, m, k, mt) : tc_default_splits(m, n, k, mt);
+    if (swap && sp == 0) sp = 1;
+    return TcChoice{mt, swap, sp};
   }
-  return est[2] < est[1] ? 2 : 1;
+  TcChoice best{1, 0, 1};
+  double best_est = 0.0;
+  for (int swap = 0; swap <= (may_swap && k >= 256 && k <= 2048 ? 1 : 0); ++swap) {
+    const uint64_t rows_dim = swap ? n : m, cols_dim = swap ? m : n;
+    for (int mt = 1; mt <= 2; ++mt) {
+      if (mt == 2 && (rows_dim < 256 || k < 512)) continue;
+      const uint64_t rows = 128ull * mt;
+      const uint64_t tiles_m = (rows_dim + rows - 1) / rows, tiles_n = (cols_dim + 255) / 256, tiles = tiles_m * tiles_n;
+      uint32_t splits = tc_default_splits(rows_dim, cols_dim, k, mt);
+      if (swap && splits == 0) splits = 1;             // stream mode stores through slots: whole tiles instead
+      double eff = 1.0;
+      if (splits == 1 && (double)tiles < 8 * sms) {    // whole waves of tiles
+        const double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
+        eff = (double)tiles / (waves * sms);
+      }
+      // measured against the 128-row tile: 0.67-0.85 of its cost from k = 16384 up, 0.83-0.88 at
+      // k = 784 ... 8192 (256-bit or line-wide stores in the epilogue)
+      double cost = mt == 1 ? 1.0 : (k < 16384 ? 0.85 : 0.75);
+      if (swap) cost *= 0.97;
+      const double est = (double)(tiles_m * rows) * (double)(tiles_n * 256) * cost / eff;
+      if (best_est == 0.0 || est < best_est) {
+        best_est = est;
+        best = TcChoice{mt, swap, splits};
+      }
+    }
+  }
+  return best;
 }
 
 int check_mm(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
@@ -162,15 +194,15 @@ extern "C" {
 // Scratch a matmul launch needs; `fused` as in fmatmul_impl below (only the sigmoid epilogue
 // of the tensor-core kernel changes the answer: it keeps rows past a tile boundary on the
 // tensor cores).
-static uint64_t workspace_need(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, int fused) {
+static uint64_t workspace_need(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, int fused, bool pitched = false) {
   const float* al = reinterpret_cast<const float*>(256);   // allocator buffers are 256-byte aligned
   int kind = skinny_kind(tl, tr, m, n, k, al, al, al);
   if (kind) return skinny_workspace_bytes(kind, m, n, k);
   if (choose_path(tl, tr, m, n, k, al, al, al) == kPathTc) {
     const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, fused == 1 ? 1 : 0);
     const uint64_t mm = m - rem;
-    const int mt = tc_tile_rows(mm, n, k);
-    uint64_t need = tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt);
+    const TcChoice c = tc_choose(mm, n, k, rem == 0 && !pitched);
+    uint64_t need = c.swap ? tc_workspace_bytes(n, mm, k, c.splits, c.mt) : tc_workspace_bytes(mm, n, k, c.splits, c.mt);
     // the two parts run at the same time: the ragged rows' scratch follows the tiles' scratch
     if (rem) need = align256(need) + ragged_rows_workspace_bytes(rem, n, k);
     return need;
@@ -213,6 +245,16 @@ int polar_b200_fmatmul_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k) 
   return choose_path(tl, tr, m, n, k, al, al, al);
 }
 
+void polar_b200_fmatmul_tc_plan(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, int* tile_rows, int* exchanged,
+                                int* splits) {
+  const float* al = reinterpret_cast<const float*>(256);
+  const uint64_t rem = ragged_rows(tl, tr, m, n, k, al, 0);
+  const TcChoice c = tc_choose(m - rem, n, k, rem == 0);
+  if (tile_rows) *tile_rows = 128 * c.mt;
+  if (exchanged) *exchanged = c.swap;
+  if (splits) *splits = (int)c.splits;
+}
+
 // The tensor-core path of one product: whole tiles on the tcgen05 kernel, rows just past a tile
 // boundary of a t_f product beside it on the bandwidth-bound kernel.  `pitch` (t_f only; 0 = m)
 // is the number of floats between consecutive k rows of the stored left operand: a value above
@@ -224,15 +266,16 @@ static int tc_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const flo
   const uint64_t lp = pitch ? pitch : m;
   const uint64_t rem = ragged_rows(tl, tr, m, n, k, right, fused);
   if (rem == 0) {
-    const int mt = tc_tile_rows(m, n, k);
-    return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(m, n, k, mt), workspace,
-                  workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0, pitch, mt);
+    const TcChoice c = tc_choose(m, n, k, pitch == 0);
+    return run_tc(tl, tr, m, n, k, left, right, out, 256, 16, 3, 0, c.splits, workspace,
+                  workspace_bytes, as_stream(stream), fused == 1 ? 1 : 0, pitch, c.mt, c.swap);
   }
   // whole tile rows on the tensor cores (left is stored [k, m]: the first m - rem columns
   // of rows of pitch m), the last `rem` rows on the bandwidth-bound kernel, concurrently
   const uint64_t mm = m - rem;
-  const int mt = tc_tile_rows(mm, n, k);
-  const uint64_t tc_need = align256(tc_workspace_bytes(mm, n, k, tc_default_splits(mm, n, k, mt), mt));
+  const TcChoice c = tc_choose(mm, n, k, false);
+  const int mt = c.mt;
+  const uint64_t tc_need = align256(tc_workspace_bytes(mm, n, k, c.splits, mt));
   const uint64_t rag_need = ragged_rows_workspace_bytes(rem, n, k);
   cudaStream_t main_stream = as_stream(stream);
   void* own = nullptr;
@@ -259,7 +302,7 @@ static int tc_path(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const flo
   }
   rc = launch_ragged_rows(left + mm, lp, right, out + mm * n, reinterpret_cast<float*>(ws + tc_need), rem, n, k,
                           rag_stream);
-  int rc2 = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, tc_default_splits(mm, n, k, mt),
+  int rc2 = run_tc(tl, tr, mm, n, k, left, right, out, 256, 16, 3, 0, c.splits,
                    tc_need ? ws : nullptr, tc_need, main_stream, 0, lp, mt);
   // join: whatever follows on the caller's stream waits for the side stream too (also when a
   // launch failed: a fork must never be left open, least of all under stream capture)
@@ -340,7 +383,9 @@ int polar_b200_fmatmul(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const
 }
 
 uint64_t polar_b200_fmatmul_t_f_rows_workspace_bytes(uint64_t rows, uint64_t n, uint64_t k) {
-  return workspace_need(1, 0, rows, n, k, 0);
+  // a block that is the whole result runs as the plain builtin, which may choose differently
+  const uint64_t a = workspace_need(1, 0, rows, n, k, 0, true), b = workspace_need(1, 0, rows, n, k, 0, false);
+  return a > b ? a : b;
 }
 
 int polar_b200_fmatmul_t_f_rows(uint64_t m, uint64_t row0, uint64_t rows, uint64_t n, uint64_t k, const float* left,
@@ -437,6 +482,10 @@ int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, co
   int rc = check_mm(tl, tr, m, n, k, left, right, out);
   if (rc) return rc;
   if (m == 0 || n == 0 || k == 0) return fail(POLAR_B200_ERR_UNSUPPORTED, "empty matrix");
+  // tile_n + 1000: the operands exchange roles (the transposed product is computed and stored
+  // transposed; whole tiles or fixed k cuts only)
+  const int swap_ab = tile_n >= 1000 ? 1 : 0;
+  if (swap_ab) tile_n -= 1000;
   // tile_n = 512 selects the 256 x 256 tile configuration (256 columns, two row sub-tiles)
   const int mt = tile_n == 512 ? 2 : 1;
   if (mt == 2) tile_n = 256;
@@ -447,14 +496,18 @@ int polar_b200_fmatmul_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, co
     return fail(POLAR_B200_ERR_INVALID, "passes must be 1 or 3 (13: issue-rate diagnostic)");
   if (!tc_shape_ok(tl, tr, m, n, k, left, right))
     return fail(POLAR_B200_ERR_UNSUPPORTED, "operands are not expressible as TMA tensor maps");
+  if (swap_ab && (splits == -1 || !tc_shape_ok(tr ? 0 : 1, tl ? 0 : 1, n, m, k, right, left)))
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "exchanged operands: not with stream mode, and both roles must suit TMA");
   if (splits < -1 || splits > 64 || (splits > 1 && ((m * n) & 3)))
     return fail(POLAR_B200_ERR_INVALID,
                 "splits must be -1 (stream), 0 (automatic) or 1..64, and m*n a multiple of 4 when > 1");
   if (splits == -1 && tile_n != 256) return fail(POLAR_B200_ERR_INVALID, "stream mode needs tile_n = 256");
   LaunchDeviceScope on(stream, out);
-  const uint32_t s = splits == -1 ? 0u : splits == 0 ? tc_default_splits(m, n, k, mt) : (uint32_t)splits;
+  uint32_t s = splits == -1 ? 0u : splits == 0 ? (swap_ab ? tc_default_splits(n, m, k, mt) : tc_default_splits(m, n, k, mt))
+                                               : (uint32_t)splits;
+  if (swap_ab && s == 0) s = 1;
   return run_tc(tl, tr, m, n, k, left, right, out, tile_n, slab_k, passes, write_hi, s, nullptr, 0, as_stream(stream),
-                0, 0, mt);
+                0, 0, mt, swap_ab);
 }
 
 static uint64_t numel(const polar_b200_tensor& t) {

@@ -47,6 +47,7 @@
 // tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -101,6 +102,10 @@ struct Params {
   uint32_t share;   // slabs per team
   uint32_t teams;
   float* slots;
+  int wide_store;   // 256-bit stores in the epilogue where alignment allows
+  // The kernel was given the operands in exchanged roles (it computes the transposed product):
+  // a tile's rows are columns of the result, whose row length is m.  See launch_tc.
+  int out_t;
 };
 
 // Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
@@ -174,6 +179,11 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   // the columns: to the result, to the piece's partial-product buffer, or to its slot.
   const bool vec_ok = ((p.n & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                       ((reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
+  // A thread owns a row of the tile, so a warp's store instruction touches 32 rows: with 256-bit
+  // stores each of them is a whole 32-byte sector instead of half of one.
+  const bool wide_ok = p.wide_store && ((p.n & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(p.partial) & 31) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(p.slots) & 31) == 0);
   auto drain = [&](const Piece& pc, uint32_t as, int h0, int h1, int q, int half) {
       int m0, n0;
       tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
@@ -200,15 +210,37 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         } else if (to_slot) {
           // a whole tile per slot, padding rows and columns included (they hold zeros)
           float* dst = p.slots + ((uint64_t)pc.slot * kTileM + tile_row) * BN + c;
+          if (wide_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) st_global_v8(dst + j, r + j);
+          } else
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
                         __uint_as_float(r[j + 3])};
             *reinterpret_cast<float4*>(dst + j) = v;
           }
+        } else if (p.out_t) {
+          // A tensor-memory lane is a COLUMN of the result here: the 32 lanes of a warp write 32
+          // consecutive floats of one result row with every store instruction (one 128-byte line),
+          // where the plain orientation has each lane writing into a row of its own.
+          if (row < p.m) {
+            float* dst = out_base + ((uint64_t)n0 + c) * p.m + row;
+            if ((uint64_t)n0 + c + 32 <= p.n) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j, dst += p.m) *dst = __uint_as_float(r[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j, dst += p.m)
+                if ((uint64_t)n0 + c + j < p.n) *dst = __uint_as_float(r[j]);
+            }
+          }
         } else if (row < p.m) {
           float* dst = out_base + row * p.n + n0 + c;
-          if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
+          if (wide_ok && (uint64_t)n0 + c + 32 <= p.n) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) st_global_v8(dst + j, r + j);
+          } else if (vec_ok && (uint64_t)n0 + c + 32 <= p.n) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               float4 v = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
@@ -580,10 +612,18 @@ uint32_t choose_splits(uint64_t tiles, uint64_t num_kb, uint64_t m, uint64_t n, 
   return best;
 }
 
+static bool wide_store_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("POLAR_B200_TC_STORE_BITS");
+    return !(e && atoi(e) == 128);
+  }();
+  return on;
+}
+
 template <int BN, int BK, int MT = 1>
 static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                       const float* right, float* out, int passes, int write_hi, float* ws, uint32_t splits,
-                      int epilogue, cudaStream_t stream, uint64_t left_pitch) {
+                      int epilogue, cudaStream_t stream, uint64_t left_pitch, int out_t) {
   using C = Cfg<BN, BK, MT>;
   static_assert(C::kStages >= 2 && C::kSmemBytes <= 227 * 1024, "stage ring must fit shared memory");
   int dev = 0;
@@ -612,6 +652,10 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   p.b_mn_major = tr ? 0 : 1;
   p.passes = passes; p.write_hi = write_hi; p.status = status_word;
   p.wait_ns = wait_limit_ns(2000000000ull);
+  p.wide_store = wide_store_enabled() ? 1 : 0;
+  p.out_t = out_t;
+  if (out_t && (splits == 0 || left_pitch))
+    return fail(POLAR_B200_ERR_UNSUPPORTED, "exchanged operands: whole tiles or fixed k cuts only, no row pitch");
   uint64_t tm = (m + BM * MT - 1) / (BM * MT), tn = (n + BN - 1) / BN;
   if (tm * tn > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   p.tiles_m = (uint32_t)tm; p.tiles_n = (uint32_t)tn;
@@ -651,18 +695,33 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
 
 }  // namespace tc
 
+// swap_ab: the operands exchange roles.  out[m,n] = L.R is computed as its transpose
+// R'.L' [n,m] - `right` becomes the operand whose rows are tensor-memory lanes - and the epilogue
+// stores tile element (lane i, column j) at out[j][i]: consecutive lanes then write consecutive
+// floats of a result row.  The products and the order of the sum over k are the same; only the
+// two cross terms of the split (lo.hi, hi.lo) are added in exchanged order.  Pays where the
+// epilogue is a visible part of a tile's time, i.e. for short sums.
 int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
               const float* right, float* out, int bn, int bk, int passes, int write_hi, float* ws,
-              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch, int mt) {
+              uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch, int mt, int swap_ab) {
+  if (swap_ab) {
+    // left' = right: stored [k,n] (tr = 0) is "stored [k,m']" (tl' = 1); right' = left: stored
+    // [m,k] (tl = 0) is "stored [n',k]" (tr' = 1)
+    const int tl2 = tr ? 0 : 1, tr2 = tl ? 0 : 1;
+    const float* l2 = right;
+    const float* r2 = left;
+    const uint64_t m2 = n, n2 = m;
+    tl = tl2; tr = tr2; left = l2; right = r2; m = m2; n = n2;
+  }
   if (mt == 2)   // 256 x 256 tiles, 16-float slabs
-    return tc::launch_cfg<256, 16, 2>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
+    return tc::launch_cfg<256, 16, 2>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
   if (bn == 128 && bk == 32)
-    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
+    return tc::launch_cfg<128, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
   if (bn == 128)
-    return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
+    return tc::launch_cfg<128, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
   if (bk == 32)
-    return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
-  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch);
+    return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
+  return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
 }
 
 // Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.

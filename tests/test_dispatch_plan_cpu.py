@@ -39,6 +39,29 @@ def test_paths(lib):
     assert path(0, 0, 512, 510, 512) == FFMA            # row pitch TMA cannot describe (n % 4 != 0, right stored [k, n])
 
 
+def tc_plan(lib, tl, tr, m, n, k):
+    rows, exchanged, splits = ctypes.c_int(-1), ctypes.c_int(-1), ctypes.c_int(-1)
+    lib.cdll.polar_b200_fmatmul_tc_plan(tl, tr, m, n, k, ctypes.byref(rows), ctypes.byref(exchanged),
+                                        ctypes.byref(splits))
+    return rows.value, exchanged.value, splits.value
+
+
+def test_tile_height_and_orientation(lib):
+    # MLP layer 1 (k = 784: the epilogue is a visible share of a tile): 256-row tiles, operands in
+    # exchanged roles so that the epilogue stores whole lines, whole tiles - at the full batch and
+    # at the per-GPU batch of the 8-GPU run (512 tiles in four waves still beat 1024 128-row tiles)
+    assert tc_plan(lib, 0, 0, 65536, 4096, 784) == (256, 1, 1)
+    assert tc_plan(lib, 0, 0, 8192, 4096, 784) == (256, 1, 1)
+    # long sums: the epilogue does not matter, the plain orientation stays
+    assert tc_plan(lib, 0, 0, 8192, 8192, 8192)[:2] == (256, 0)
+    # the weight gradient (stream mode or fixed cuts; rows past the tile boundary beside it)
+    assert tc_plan(lib, 1, 0, 784, 4096, 8192) == (256, 0, 0)
+    rows, exchanged, splits = tc_plan(lib, 1, 0, 784, 4096, 65536)
+    assert (rows, exchanged) == (256, 0) and splits == 3
+    # a short sum below the exchange's range, and one tile row only: 128-row tiles
+    assert tc_plan(lib, 0, 0, 128, 512, 64) == (128, 0, 1)
+
+
 def test_whole_waves_need_no_scratch(lib):
     assert ws(lib, 0, 0, 65536, 4096, 784) == 0
     assert ws(lib, 0, 0, 8192, 8192, 8192) == 0

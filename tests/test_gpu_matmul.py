@@ -77,8 +77,10 @@ def test_tensor_core_path(gpu, par_oracle, tl, tr, shape):
     rng = np.random.default_rng(m * 7 + n * 3 + k + tl * 2 + tr)
     l, r = operands(rng, tl, tr, m, n, k)
     ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
-    for tile_n in (256, 128, 512):          # 512: the 256 x 256 tile configuration
-        for slab_k in ((16,) if tile_n == 512 else (16, 32)):
+    # 512: the 256 x 256 tile configuration; + 1000: the operands exchange roles (the transposed
+    # product is computed and its tiles are stored transposed)
+    for tile_n in (256, 128, 512, 1256, 1128, 1512):
+        for slab_k in ((16,) if tile_n % 1000 == 512 else (16, 32)):
             got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k)
             err = rel_err(got, ref, mag)
             assert err <= TOL, (tile_n, slab_k, err)
@@ -104,7 +106,8 @@ def test_k_cut_into_work_units_and_stream_mode(gpu, par_oracle, tl, tr, shape):
     for splits in (-1, 2, 3, 8):
         if splits > 1 and ((m * n) & 3 or (k + 15) // 16 < splits):
             continue
-        for tile_n, slab_k in (((256, 16), (256, 32), (512, 16)) if splits == -1 else ((256, 16), (512, 16))):
+        for tile_n, slab_k in (((256, 16), (256, 32), (512, 16)) if splits == -1 else
+                               ((256, 16), (512, 16), (1256, 16), (1512, 16))):
             got = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k, splits=splits)
             assert rel_err(got, ref, mag) <= 5e-6, (splits, tile_n, slab_k)
             again = gpu.fmatmul(tl, tr, l, r, which="tc", tile_n=tile_n, slab_k=slab_k, splits=splits)
@@ -276,7 +279,7 @@ def test_result_that_is_only_4_byte_aligned(gpu, par_oracle):
         l, r = operands(rng, tl, tr, m, n, k)
         ref, mag = par_oracle.fmatmul_f64(tl, tr, l, r)
         L, R = torch.from_numpy(l).cuda(), torch.from_numpy(r).cuda()
-        for tile_n in (256, 512):
+        for tile_n in (256, 512) if splits == -1 else (256, 512, 1256, 1512):
             base = torch.full((m * n + 8,), float("nan"), device="cuda")
             out = base[1:1 + m * n].view(m, n)
             assert out.data_ptr() % 16 == 4

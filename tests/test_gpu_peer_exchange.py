@@ -48,10 +48,13 @@ def test_one_rank_equals_the_plain_program_over_several_steps():
         a.run(), b.run(), c.run()
         for k in ("L", "W1", "W2", "dW1", "dW2"):
             assert np.array_equal(a.output(k).view(np.uint32), b.output(k).view(np.uint32)), (step, k)
-        # dW1 in two blocks of rows on two streams: the same sums up to how k is cut
+        # dW1 in two blocks of rows on two streams: the same sums up to how the tensor-core path
+        # runs a block (tile orientation, cuts of k), so W1 agrees to rounding and, from the second
+        # step on, so does everything computed from it
         for k in ("L", "dW2"):
-            assert np.array_equal(a.output(k).view(np.uint32), c.output(k).view(np.uint32)), (step, k)
-        for k in ("dW1", "W1", "W2"):
+            if step == 0:
+                assert np.array_equal(a.output(k).view(np.uint32), c.output(k).view(np.uint32)), (step, k)
+        for k in ("L", "dW1", "dW2", "W1", "W2"):
             assert np.max(np.abs(a.output(k) - c.output(k))) <= 1e-5 * np.abs(a.output(k)).max(), (step, k)
     assert lib.cdll.polar_b200_device_status() == 0
     del b, c
