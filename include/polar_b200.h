@@ -460,6 +460,21 @@ int polar_b200_allreduce_fadd_range(void* const* buffers, uint32_t rank, uint32_
                                     const polar_b200_update_segment* segments, uint32_t n_segments,
                                     float scale_w, float scale_g, void* stream);
 
+/* The same exchange with the sum done inside the NVLink switch.  `multicast` is the multicast
+ * address of the SAME buffers (the address at which a store reaches every rank's copy and a
+ * multimem load returns the sum of all copies; control block first, like the buffers), as a
+ * host that owns a multicast object has it - torch's symmetric memory hands one out
+ * (`multicast_ptr`), or cuMulticastCreate / cuMulticastBindMem by hand.  `buffers` are still
+ * needed: the ranks' flags go through them.  Each rank then moves one slice in and one slice
+ * out over its links instead of (world - 1) of each.  The order of the sum is the switch's,
+ * not rank order: every rank receives the same bits, and they agree with the plain exchange to
+ * rounding.  multicast == NULL is polar_b200_allreduce_fadd_range.  Do not let a rank exit
+ * while its memory is bound to the multicast object and other ranks are still running. */
+int polar_b200_allreduce_fadd_multicast(void* const* buffers, void* multicast, uint32_t rank, uint32_t world,
+                                        uint32_t channel, uint64_t first, uint64_t count,
+                                        const polar_b200_update_segment* segments, uint32_t n_segments,
+                                        float scale_w, float scale_g, void* stream);
+
 /* Scratch bytes the launch `nativeKernelName(args)` would take from the stream-ordered pool
  * if polar_b200_launch_by_name were given no workspace (0 for every builtin but some
  * fmatmul shapes).  Only shapes are read, not the data pointers. */

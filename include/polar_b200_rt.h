@@ -92,8 +92,10 @@ typedef struct polar_b200_rt_update {
   uint64_t count;          /* elements */
 } polar_b200_rt_update;
 /* channel, first, count: the part of the payload this call exchanges and the channel of control
- * words it uses, as in polar_b200_allreduce_fadd_range (channel 0, first 0, count n = everything). */
-int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, uint32_t rank,
+ * words it uses, as in polar_b200_allreduce_fadd_range (channel 0, first 0, count n = everything).
+ * multicast: the buffers' NVLink multicast address for the sum inside the switch, or NULL
+ * (polar_b200_allreduce_fadd_multicast). */
+int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, void* multicast, uint32_t rank,
                                  uint32_t world, uint32_t channel, uint64_t first, uint64_t count,
                                  const polar_b200_rt_update* updates, uint32_t n_updates, float scale_w,
                                  float scale_g);

@@ -82,6 +82,8 @@ SIGNATURES = {
                                        ctypes.c_uint32, _f, _f, _p]),
     "polar_b200_allreduce_fadd_range": (_i, [ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
                                              _u64, _u64, _p, ctypes.c_uint32, _f, _f, _p]),
+    "polar_b200_allreduce_fadd_multicast": (_i, [ctypes.POINTER(_p), _p, ctypes.c_uint32, ctypes.c_uint32,
+                                                 ctypes.c_uint32, _u64, _u64, _p, ctypes.c_uint32, _f, _f, _p]),
     "polar_b200_launch_by_name": (_i, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64, _p, _u64, _p]),
     "polar_b200_launch_workspace_bytes": (_u64, [ctypes.c_char_p, ctypes.POINTER(Arg), _u64]),
     "polar_b200_launch_count": (_u64, []),

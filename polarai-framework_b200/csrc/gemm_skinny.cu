@@ -129,43 +129,54 @@ small_n_kmajor_resident_kernel(const float* __restrict__ left, const float* __re
                                uint64_t rsj, int act) {
   extern __shared__ float bs[];   // [NP][k + 4], k contiguous
   const uint32_t kpad = (uint32_t)k + 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t warps_total = (uint64_t)gridDim.x * (kResidentThreads / 32);
+  const uint64_t groups = (m + ROWS_PER_WARP - 1) / ROWS_PER_WARP;
+  uint64_t g = (uint64_t)blockIdx.x * (kResidentThreads / 32) + warp;
+  // The loads of a chunk (two 128-bit loads per row and lane) are issued one chunk ahead of its
+  // arithmetic, and the very first ones before the small operand is staged: with one group of
+  // rows per warp (8192 rows on 148 SMs) the kernel is otherwise a chain of memory latencies.
+  float4 a0[ROWS_PER_WARP], a1[ROWS_PER_WARP];
+  auto load_chunk = [&](uint64_t group, uint32_t kk) {
+#pragma unroll
+    for (int r = 0; r < ROWS_PER_WARP; ++r) {
+      const uint64_t row = group * ROWS_PER_WARP + r;
+      const float* src = left + (row < m ? row : m - 1) * k;   // clamped: results of padding rows are dropped
+      a0[r] = __ldcs(reinterpret_cast<const float4*>(src + kk));
+      a1[r] = (kk + 128 < (uint32_t)k) ? __ldcs(reinterpret_cast<const float4*>(src + kk + 128))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  if (g < groups && (uint32_t)lane * 4 < (uint32_t)k) load_chunk(g, lane * 4);
   for (uint64_t e = threadIdx.x; e < (uint64_t)NP * k; e += kResidentThreads) {
     uint32_t j = (uint32_t)(e % NP), kk = (uint32_t)(e / NP);
     bs[j * kpad + kk] = ((uint64_t)j < n) ? right[(uint64_t)kk * rsk + (uint64_t)j * rsj] : 0.f;
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint64_t warps_total = (uint64_t)gridDim.x * (kResidentThreads / 32);
-  const uint64_t groups = (m + ROWS_PER_WARP - 1) / ROWS_PER_WARP;
-  for (uint64_t g = (uint64_t)blockIdx.x * (kResidentThreads / 32) + warp; g < groups; g += warps_total) {
+  for (; g < groups; g += warps_total) {
     const uint64_t row0 = g * ROWS_PER_WARP;
     float acc[ROWS_PER_WARP][NP];
 #pragma unroll
     for (int r = 0; r < ROWS_PER_WARP; ++r)
 #pragma unroll
       for (int j = 0; j < NP; ++j) acc[r][j] = 0.f;
-    const float* rows[ROWS_PER_WARP];
-#pragma unroll
-    for (int r = 0; r < ROWS_PER_WARP; ++r)
-      rows[r] = left + ((row0 + r < m) ? (row0 + r) : (m - 1)) * k;   // clamped: results of padding rows are dropped
     for (uint32_t kk = lane * 4; kk < (uint32_t)k; kk += 256) {
-      float4 a0[ROWS_PER_WARP], a1[ROWS_PER_WARP];
-      const bool second = kk + 128 < (uint32_t)k;
+      float4 c0[ROWS_PER_WARP], c1[ROWS_PER_WARP];
 #pragma unroll
-      for (int r = 0; r < ROWS_PER_WARP; ++r) {
-        a0[r] = __ldcs(reinterpret_cast<const float4*>(rows[r] + kk));
-        a1[r] = second ? __ldcs(reinterpret_cast<const float4*>(rows[r] + kk + 128))
-                       : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      for (int r = 0; r < ROWS_PER_WARP; ++r) { c0[r] = a0[r]; c1[r] = a1[r]; }
+      const bool second = kk + 128 < (uint32_t)k;
+      // the next chunk of this group, or the first chunk of this warp's next group
+      if (kk + 256 < (uint32_t)k) load_chunk(g, kk + 256);
+      else if (g + warps_total < groups) load_chunk(g + warps_total, lane * 4);
 #pragma unroll
       for (int j = 0; j < NP; ++j) {
         const float4 b0 = *reinterpret_cast<const float4*>(&bs[j * kpad + kk]);
 #pragma unroll
         for (int r = 0; r < ROWS_PER_WARP; ++r) {
-          acc[r][j] = fmaf(a0[r].x, b0.x, acc[r][j]);
-          acc[r][j] = fmaf(a0[r].y, b0.y, acc[r][j]);
-          acc[r][j] = fmaf(a0[r].z, b0.z, acc[r][j]);
-          acc[r][j] = fmaf(a0[r].w, b0.w, acc[r][j]);
+          acc[r][j] = fmaf(c0[r].x, b0.x, acc[r][j]);
+          acc[r][j] = fmaf(c0[r].y, b0.y, acc[r][j]);
+          acc[r][j] = fmaf(c0[r].z, b0.z, acc[r][j]);
+          acc[r][j] = fmaf(c0[r].w, b0.w, acc[r][j]);
         }
       }
       if (second) {
@@ -174,10 +185,10 @@ small_n_kmajor_resident_kernel(const float* __restrict__ left, const float* __re
           const float4 b1 = *reinterpret_cast<const float4*>(&bs[j * kpad + kk + 128]);
 #pragma unroll
           for (int r = 0; r < ROWS_PER_WARP; ++r) {
-            acc[r][j] = fmaf(a1[r].x, b1.x, acc[r][j]);
-            acc[r][j] = fmaf(a1[r].y, b1.y, acc[r][j]);
-            acc[r][j] = fmaf(a1[r].z, b1.z, acc[r][j]);
-            acc[r][j] = fmaf(a1[r].w, b1.w, acc[r][j]);
+            acc[r][j] = fmaf(c1[r].x, b1.x, acc[r][j]);
+            acc[r][j] = fmaf(c1[r].y, b1.y, acc[r][j]);
+            acc[r][j] = fmaf(c1[r].z, b1.z, acc[r][j]);
+            acc[r][j] = fmaf(c1[r].w, b1.w, acc[r][j]);
           }
         }
       }
@@ -458,13 +469,16 @@ dense_grad_kernel(const float* __restrict__ H, const float* __restrict__ dz, con
     }
     __syncthreads();
     if (!live) continue;
-    for (int rr = 0; rr < rs; rr += 4) {
-      float4 h[4];
+    // six to eight 128-bit loads in flight per thread (two CTAs of 256 threads per SM then keep
+    // 48-64 KB outstanding, what HBM latency x bandwidth asks of one SM)
+    constexpr int kBatch = NP == 10 ? 6 : 8;   // at ten columns 128 registers hold six rows without spilling
+    for (int rr = 0; rr < rs; rr += kBatch) {
+      float4 h[kBatch];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < kBatch; ++u)
         if (rr + u < rs) h[u] = __ldcs(reinterpret_cast<const float4*>(H + (r0 + rr + u) * kh + m0));
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kBatch; ++u) {
         if (rr + u >= rs) continue;
         const unsigned long long h01 = pack2(h[u].x, h[u].y), h23 = pack2(h[u].z, h[u].w);
         unsigned long long c01 = 0ull, c23 = 0ull;   // (dZ . W^T) for the four columns

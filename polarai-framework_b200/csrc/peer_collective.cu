@@ -71,6 +71,11 @@ struct Params {
   float scale_w, scale_g;
   int* status;
   unsigned long long wait_ns;
+  // The same buffer's NVLink multicast address (control block first), or nullptr.  With it the
+  // slice is summed INSIDE the switch (multimem.ld_reduce) and sent to every rank with one store
+  // per element (multimem.st): a rank's links carry one slice in and one slice out instead of
+  // (world - 1) of each.
+  unsigned char* mc;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -93,6 +98,16 @@ __device__ __forceinline__ float4 ld_peer(const float4* p) {
 __device__ __forceinline__ void st_peer(float4* p, float4 v) {
   asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
                ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float4 multimem_sum(const float4* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_store(float4* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 __device__ __forceinline__ unsigned long long now_ns() {
   unsigned long long t;
@@ -147,39 +162,66 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     const uint64_t lo_rel = (uint64_t)p.rank * per < p.n4 ? (uint64_t)p.rank * per : p.n4;
     const uint64_t lo = p.first4 + lo_rel;
     const uint64_t hi = p.first4 + (lo_rel + per < p.n4 ? lo_rel + per : p.n4);
-    // With few ranks a thread has many elements and one NVLink round trip per element would
-    // be a chain of latencies: UNR elements' loads are issued together.
+    // The slice comes in over NVLink and goes out again to everyone: the two directions only run
+    // at the same time if some threads are storing while others are loading.  So a thread walks
+    // several elements (the host sizes the CTAs for about four each) and asks for the NEXT
+    // element's values before it sums and stores the current one.  Issued all at once - one
+    // element per thread, everything in flight - the kernel spends one slice's transfer time
+    // loading and then another one storing (46 us of a 16 us transfer at eight ranks).
     constexpr int W = WORLD ? WORLD : kMaxWorld;
-    constexpr int UNR = WORLD == 2 ? 4 : (WORLD == 4 ? 2 : 1);
     const uint64_t stride = (uint64_t)gridDim.x * kThreadsNow;
-    for (uint64_t i0 = lo + (uint64_t)blockIdx.x * kThreadsNow + threadIdx.x; i0 < hi; i0 += stride * UNR) {
-      float4 v[UNR][W];
+    auto load_all = [&](float4 (&v)[W], uint64_t i) {
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const uint64_t i = i0 + (uint64_t)u * stride;
-        if (i >= hi) continue;
+      for (int r = 0; r < W; ++r)
+        if (r < (int)world)
+          v[r] = ld_peer(reinterpret_cast<const float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i);
+    };
+    auto sum_and_store = [&](const float4 (&v)[W], uint64_t i) {
+      float4 s = v[0];
 #pragma unroll
-        for (int r = 0; r < W; ++r)
-          if (r < (int)world)
-            v[u][r] = ld_peer(reinterpret_cast<const float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i);
+      for (int r = 1; r < W; ++r)
+        if (r < (int)world) {
+          s.x = __fadd_rn(s.x, v[r].x);
+          s.y = __fadd_rn(s.y, v[r].y);
+          s.z = __fadd_rn(s.z, v[r].z);
+          s.w = __fadd_rn(s.w, v[r].w);
+        }
+#pragma unroll
+      for (int r = 0; r < W; ++r)
+        if (r < (int)world)
+          st_peer(reinterpret_cast<float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i, s);
+    };
+    uint64_t i = lo + (uint64_t)blockIdx.x * kThreadsNow + threadIdx.x;
+    if (p.mc) {
+      // In the switch: one load returns the sum over all ranks (in the switch's order, the same
+      // bits for every rank since only this rank asks for this slice), one store delivers it to
+      // all.  Two elements' loads are in flight per thread.
+      float4* mc4 = reinterpret_cast<float4*>(p.mc + POLAR_B200_PEER_CONTROL_BYTES);
+      for (; i < hi; i += 2 * stride) {
+        const bool two = i + stride < hi;
+        const float4 a = multimem_sum(mc4 + i);
+        float4 b = a;
+        if (two) b = multimem_sum(mc4 + i + stride);
+        multimem_store(mc4 + i, a);
+        if (two) multimem_store(mc4 + i + stride, b);
       }
+    } else if constexpr (WORLD != 0) {
+      float4 cur[W], nxt[W];
+      if (i < hi) load_all(cur, i);
+      while (i < hi) {
+        const uint64_t in = i + stride;
+        if (in < hi) load_all(nxt, in);
+        sum_and_store(cur, i);
 #pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const uint64_t i = i0 + (uint64_t)u * stride;
-        if (i >= hi) continue;
-        float4 s = v[u][0];
-#pragma unroll
-        for (int r = 1; r < W; ++r)
-          if (r < (int)world) {
-            s.x = __fadd_rn(s.x, v[u][r].x);
-            s.y = __fadd_rn(s.y, v[u][r].y);
-            s.z = __fadd_rn(s.z, v[u][r].z);
-            s.w = __fadd_rn(s.w, v[u][r].w);
-          }
-#pragma unroll
-        for (int r = 0; r < W; ++r)
-          if (r < (int)world)
-            st_peer(reinterpret_cast<float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i, s);
+        for (int r = 0; r < W; ++r) cur[r] = nxt[r];
+        i = in;
+      }
+    } else {
+      // any other number of ranks: sixteen values per element leave no registers for a second set
+      float4 v[W];
+      for (; i < hi; i += stride) {
+        load_all(v, i);
+        sum_and_store(v, i);
       }
     }
   }
@@ -208,6 +250,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     const float4* g4 = reinterpret_cast<const float4*>(g + sg.offset);
     float4* w4 = reinterpret_cast<float4*>(sg.w);
     const uint64_t c4 = sg.count >> 2;
+#pragma unroll 4
     for (uint64_t i = (uint64_t)blockIdx.x * kThreadsNow + threadIdx.x; i < c4; i += (uint64_t)gridDim.x * kThreadsNow) {
       const float4 gv = __ldcg(g4 + i);
       float4 wv = w4[i];
@@ -297,9 +340,9 @@ int polar_b200_peer_close(void* buffer) {
   return e == cudaSuccess ? POLAR_B200_OK : fail(POLAR_B200_ERR_CUDA, "cudaIpcCloseMemHandle", e);
 }
 
-static int allreduce_fadd_impl(void* const* buffers, uint32_t rank, uint32_t world, uint32_t channel, uint64_t first,
-                               uint64_t n, const polar_b200_update_segment* segments, uint32_t n_segments,
-                               float scale_w, float scale_g, void* stream) {
+static int allreduce_fadd_impl(void* const* buffers, void* multicast, uint32_t rank, uint32_t world, uint32_t channel,
+                               uint64_t first, uint64_t n, const polar_b200_update_segment* segments,
+                               uint32_t n_segments, float scale_w, float scale_g, void* stream) {
   clear_error();
   if (!buffers || world == 0 || world > (uint32_t)peer::kMaxWorld || rank >= world)
     return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: bad rank/world or null buffer list");
@@ -327,17 +370,25 @@ static int allreduce_fadd_impl(void* const* buffers, uint32_t rank, uint32_t wor
   p.first4 = first / 4;
   p.n4 = (n + 3) / 4;   // the buffer is padded to 16 bytes by polar_b200_peer_alloc
   p.channel = channel;
+  if (multicast && !aligned16(multicast)) return fail(POLAR_B200_ERR_INVALID, "allreduce_fadd: unaligned multicast address");
+  p.mc = world > 1 ? static_cast<unsigned char*>(multicast) : nullptr;
   p.rank = rank; p.world = world; p.n_seg = n_segments;
   p.scale_w = scale_w; p.scale_g = scale_g;
   // Every CTA waits on the other ranks, so all of them must be resident at once: at most one
   // per SM, launched cooperatively (the driver then starts the grid only as a whole, also
-  // when other kernels are holding SMs at that moment).  Channel 0 is the exchange that has
-  // the GPU to itself: 512 threads per CTA.  The other channels are meant to run BESIDE a
-  // tensor-core matmul that already holds 576 threads and most of the registers of every SM:
-  // 128 threads per CTA fit next to it.
-  const unsigned threads = channel == 0 ? peer::kThreads : 128;
-  uint64_t want = (p.n4 + threads - 1) / threads;
+  // when other kernels are holding SMs at that moment).  CTA size: about four elements of this
+  // rank's slice per thread (see the kernel), at most 512 threads on channel 0, the exchange
+  // that has the GPU to itself.  The other channels are meant to run BESIDE a tensor-core
+  // matmul that already holds 576 threads and most of the registers of every SM: at most 128
+  // threads per CTA fit next to it.
+  const unsigned max_threads = channel == 0 ? peer::kThreads : 128;
+  uint64_t want = (p.n4 + 63) / 64;
   unsigned grid = (unsigned)(want < (uint64_t)sm_count() ? (want ? want : 1) : (uint64_t)sm_count());
+  const uint64_t slice = (p.n4 + world - 1) / world;
+  uint64_t per_cta = ((slice + 3) / 4 + grid - 1) / grid;
+  unsigned threads = (unsigned)(((per_cta + 31) / 32) * 32);
+  if (threads < 64) threads = 64;
+  if (threads > max_threads) threads = max_threads;
   cudaStream_t st = as_stream(stream);
   const void* fn = nullptr;
   switch (world) {
@@ -355,13 +406,22 @@ static int allreduce_fadd_impl(void* const* buffers, uint32_t rank, uint32_t wor
 int polar_b200_allreduce_fadd(void* const* buffers, uint32_t rank, uint32_t world, uint64_t n,
                               const polar_b200_update_segment* segments, uint32_t n_segments, float scale_w,
                               float scale_g, void* stream) {
-  return allreduce_fadd_impl(buffers, rank, world, 0, 0, n, segments, n_segments, scale_w, scale_g, stream);
+  return allreduce_fadd_impl(buffers, nullptr, rank, world, 0, 0, n, segments, n_segments, scale_w, scale_g, stream);
 }
 
 int polar_b200_allreduce_fadd_range(void* const* buffers, uint32_t rank, uint32_t world, uint32_t channel,
                                     uint64_t first, uint64_t count, const polar_b200_update_segment* segments,
                                     uint32_t n_segments, float scale_w, float scale_g, void* stream) {
-  return allreduce_fadd_impl(buffers, rank, world, channel, first, count, segments, n_segments, scale_w, scale_g, stream);
+  return allreduce_fadd_impl(buffers, nullptr, rank, world, channel, first, count, segments, n_segments, scale_w, scale_g,
+                             stream);
+}
+
+int polar_b200_allreduce_fadd_multicast(void* const* buffers, void* multicast, uint32_t rank, uint32_t world,
+                                        uint32_t channel, uint64_t first, uint64_t count,
+                                        const polar_b200_update_segment* segments, uint32_t n_segments, float scale_w,
+                                        float scale_g, void* stream) {
+  return allreduce_fadd_impl(buffers, multicast, rank, world, channel, first, count, segments, n_segments, scale_w,
+                             scale_g, stream);
 }
 
 }  // extern "C"

@@ -229,8 +229,8 @@ int polar_b200_rt_adopt(polar_b200_rt* rt, int device, uint64_t va, uint64_t byt
   return allocator_status(rt);
 }
 
-int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, uint32_t rank, uint32_t world,
-                                 uint32_t channel, uint64_t first, uint64_t count, const polar_b200_rt_update* updates,
+int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buffers, void* multicast, uint32_t rank,
+                                 uint32_t world, uint32_t channel, uint64_t first, uint64_t count, const polar_b200_rt_update* updates,
                                  uint32_t n_updates, float scale_w, float scale_g) {
   B200Device* d = dev(rt, device);
   if (!d || (n_updates && !updates) || n_updates > POLAR_B200_MAX_UPDATE_SEGMENTS)
@@ -258,8 +258,8 @@ int polar_b200_rt_allreduce_fadd(polar_b200_rt* rt, int device, void* const* buf
     seg[i].offset = u.grad_offset;
     seg[i].count = u.count;
   }
-  int status = polar_b200_allreduce_fadd_range(buffers, rank, world, channel, first, count, seg, n_updates, scale_w,
-                                               scale_g, d->stream());
+  int status = polar_b200_allreduce_fadd_multicast(buffers, multicast, rank, world, channel, first, count, seg, n_updates,
+                                                   scale_w, scale_g, d->stream());
   if (status) rt->error = polar_b200_last_error();
   else for (auto& r : locked) d->pool().markWritten(r);
   unlock_all();

@@ -99,7 +99,9 @@ class DataParallelExecutor:
     make_program(rows) builds the builtin program for `rows` rows (program.mlp_program,
     program.logreg_program); `sharded` names the inputs whose first dimension is the batch.
     builtins = "extended" applies program.fuse_program (outputs bit-identical to the chain);
-    collective = "peer" asks for the single-kernel exchange over NVLink peer memory; with
+    collective = "peer" asks for the single-kernel exchange over NVLink peer memory - with the sum
+    done inside the switch where symmetric memory has a multicast address, "peer-ipc" for plain peer
+    loads and stores only (the form to use where a rank may leave in mid-run); with
     overlap=True the last weight gradient is computed in two blocks of rows and the first block's
     exchange runs on a second stream while the second block is computed
     (program.overlap_gradient_exchange).  Off by default: on B200 the two-block matmul costs
@@ -124,7 +126,7 @@ class DataParallelExecutor:
         self.collective = "none (one rank)"
         if world > 1:
             self.collective = "nccl all-reduce, then fadd updates"
-            if fused and collective == "peer":
+            if fused and collective in ("peer", "peer-ipc"):
                 xprog = fuse_gradient_exchange(program)
                 if overlap:
                     xprog = overlap_gradient_exchange(xprog)
@@ -133,7 +135,7 @@ class DataParallelExecutor:
                 if xprog.exchanged():
                     try:
                         peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, rank, world,
-                                              self.device)
+                                              self.device, transport="ipc" if collective == "peer-ipc" else "auto")
                     except Exception as exc:               # noqa: BLE001 - any failure means "not available here"
                         why = f"{type(exc).__name__}: {exc}"
                 # every rank must take the same form: a vote
@@ -142,7 +144,8 @@ class DataParallelExecutor:
                 if int(ok.item()) == 1:
                     program, self.peers = xprog, peers
                     self.collective = ("peer memory over NVLink: sum over ranks and weight update in one kernel "
-                                       "per rank")
+                                       "per rank" + (", the sum done inside the switch (multimem)"
+                                                     if peers.transport == "multicast" else ""))
                     if any(k == "ALLREDUCE_FADD_PART" for k, _ in xprog.ops):
                         self.collective += ("; the last weight gradient in two blocks of rows, the first block's "
                                             "exchange overlapping the second block's matmul")

@@ -55,7 +55,7 @@ RT_SIGNATURES = {
     "polar_b200_rt_read": (_i, [_p, _u64, _u64, _p]),
     "polar_b200_rt_launch": (_i, [_p, _i, ctypes.POINTER(LaunchCommand)]),
     "polar_b200_rt_adopt": (_i, [_p, _i, _u64, _u64, _p]),
-    "polar_b200_rt_allreduce_fadd": (_i, [_p, _i, ctypes.POINTER(_p), ctypes.c_uint32, ctypes.c_uint32,
+    "polar_b200_rt_allreduce_fadd": (_i, [_p, _i, ctypes.POINTER(_p), _p, ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.c_uint32, _u64, _u64, ctypes.POINTER(RtUpdate), ctypes.c_uint32,
                                           ctypes.c_float, ctypes.c_float]),
     "polar_b200_rt_barrier": (_i, [_p, _i]),
@@ -353,7 +353,7 @@ class RuntimeProgramExecutor:
             else:
                 upd, n, sw, sg, channel, first, total = what
                 p = self.peers
-                rt._check(rt.cdll.polar_b200_rt_allreduce_fadd(rt.h, dev, p.buffers, p.rank, p.world, channel, first,
+                rt._check(rt.cdll.polar_b200_rt_allreduce_fadd(rt.h, dev, p.buffers, p.multicast, p.rank, p.world, channel, first,
                                                                total, upd, n, sw, sg))
 
     def output(self, name, out=None):
