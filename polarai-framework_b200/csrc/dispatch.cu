@@ -1,5 +1,4 @@
 // fmatmul entry points and dispatch by native kernel name.
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -137,13 +136,6 @@ struct TcChoice {
 
 TcChoice tc_choose(uint64_t m, uint64_t n, uint64_t k, bool may_swap) {
   const double sms = (double)sm_count();
-  if (const char* f = getenv("POLAR_B200_TC_FORCE")) {   // PROBE ONLY
-    int mt = f[0] - '0', swap = f[1] - '0';
-    if (!may_swap) swap = 0;
-    uint32_t sp = swap ? tc_default_splits(n, m, k, mt) : tc_default_splits(m, n, k, mt);
-    if (swap && sp == 0) sp = 1;
-    return TcChoice{mt, swap, sp};
-  }
   TcChoice best{1, 0, 1};
   double best_est = 0.0;
   for (int swap = 0; swap <= (may_swap && k >= 256 && k <= 2048 ? 1 : 0); ++swap) {
