@@ -682,11 +682,11 @@ def sm_count_of(torch, index):
 def tc_traffic(program, tc_ops, rows):
     """DRAM bytes per launch of the tensor-core matmuls from the ncu capture summarised in
     profiles/fmatmul_tc_256row_tiles_mlp_batch16384_full.md (dram__bytes_read.sum +
-    dram__bytes_write.sum of the step's two launches at batch 16384: 305.7 MB and 409.3 MB),
+    dram__bytes_write.sum of the step's two launches at batch 16384: 280.8 MB and 425.6 MB),
     scaled by rows - X, H and dZ1 grow with the batch, the 12.8 MB weight-shaped operands do
     not - next to the algorithmic bytes 4(mk + kn + mn)."""
     alg = [4.0 * (m * k + k * n + m * n) for m, n, k in (mm_dims(program, k_, a) for _, k_, a in tc_ops)]
-    measured_at_16384 = (305.7e6 + 409.3e6) / 2.0
+    measured_at_16384 = (280.8e6 + 425.6e6) / 2.0
     return {"traffic": rows * measured_at_16384 / 16384.0,
             "algorithmic_bytes": sum(alg) / max(1, len(alg)),
             "traffic_note": "average of the step's two tensor-core launches; ncu capture of the same kernel "
