@@ -12,6 +12,7 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
               uint32_t splits, int epilogue, cudaStream_t stream, uint64_t left_pitch = 0, int mt = 1,
               int swap_ab = 0);
 uint32_t tc_default_splits(uint64_t m, uint64_t n, uint64_t k, int mt = 1);
+bool tc_tail_in_halves(uint64_t tiles, uint64_t grid);
 uint64_t tc_workspace_bytes(uint64_t m, uint64_t n, uint64_t k, uint32_t splits, int mt = 1);
 bool tc_shape_ok(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                  const float* right);
@@ -148,7 +149,9 @@ TcChoice tc_choose(uint64_t m, uint64_t n, uint64_t k, bool may_swap) {
       if (swap && splits == 0) splits = 1;             // stream mode stores through slots: whole tiles instead
       double eff = 1.0;
       if (splits == 1 && (double)tiles < 8 * sms) {    // whole waves of tiles
-        const double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
+        double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
+        // a tail of at most half a wave runs as column halves, which last about 0.6 of a tile
+        if (tc_tail_in_halves(tiles, (uint64_t)sms)) waves -= 0.4;
         eff = (double)tiles / (waves * sms);
       }
       // measured against the 128-row tile: 0.67-0.85 of its cost from k = 16384 up, 0.83-0.88 at

@@ -82,6 +82,7 @@ template <int BN, int BK, int MT = 1> struct Cfg {
   static constexpr uint32_t kSmemBytes = kTileBytes + 1024 + 256;
   static constexpr uint32_t kTmemCols = 2 * BN;            // two fp32 accumulators
   static constexpr uint32_t kBoxBytes = 32 * BK * 4;       // one MN-major TMA box {32 m/n, BK k}
+  static constexpr int kBBoxRows = BN < 128 ? BN : 128;    // a K-major B slab arrives in boxes of 128 rows
 };
 
 struct Params {
@@ -106,6 +107,9 @@ struct Params {
   // The kernel was given the operands in exchanged roles (it computes the transposed product):
   // a tile's rows are columns of the result, whose row length is m.  See launch_tc.
   int out_t;
+  // Whole-tile mode: tiles from this one on are computed as two column halves by two CTAs
+  // (halves_from in tc_plan.hpp; kNoHalves = none).  256-column tiles only.
+  uint32_t half_from;
 };
 
 // Tile raster: groups of kGroupM row tiles walk the column tiles together, so the
@@ -149,7 +153,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   // Work comes in pieces (PieceWalk): a (tile, split) unit with a fixed share of the k slabs,
   // or, in stream mode, whatever part of a tile falls into this CTA's share of all slabs.
   auto make_walk = [&]() {
-    return PieceWalk(p.tiles_m, p.tiles_n, p.splits, p.share, p.teams, num_kb, blockIdx.x, gridDim.x);
+    return PieceWalk(p.tiles_m, p.tiles_n, p.splits, p.share, p.teams, num_kb, blockIdx.x, gridDim.x, p.half_from);
   };
 
   if (threadIdx.x == 0) {
@@ -187,6 +191,9 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   auto drain = [&](const Piece& pc, uint32_t as, int h0, int h1, int q, int half) {
       int m0, n0;
       tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
+      // a column half of a tile: its 128 accumulator columns belong to tile columns [n0, n0 + 128)
+      const int width = pc.half ? BN / 2 : BN;
+      if (pc.half == 2) n0 += BN / 2;
       const bool to_slot = p.share != 0 && pc.slot != kNoSlot;
       float* const out_base = to_slot ? nullptr
                               : (p.splits > 1 ? p.partial + (uint64_t)pc.slot * p.m * p.n : p.out);
@@ -196,7 +203,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t tile_row = (uint32_t)(h * BM + q * 32 + lane);
       const uint64_t row = (uint64_t)m0 + tile_row;
       const uint32_t tmem_acc = tmem_base + acc_col(as, h) + ((uint32_t)(q * 32) << 16);
-      for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+      for (int c = half * (width / 2); c < (half + 1) * (width / 2); c += 32) {
         if ((uint64_t)n0 + c >= p.n) break;               // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32(tmem_acc + (uint32_t)c, r);
@@ -267,12 +274,15 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       while (ok && walk.next(pc)) {
         int m0, n0;
         tile_coords(pc.tile, p.tiles_m, p.tiles_n, BN, &m0, &n0, kTileM);
+        // a column half of a tile: half of the B slab, at the start of the stage's B area
+        const int bn_now = pc.half ? BN / 2 : BN;
+        if (pc.half == 2) n0 += BN / 2;
         for (uint32_t kb = pc.kb0, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, 101, p.wait_ns)) { ok = false; break; }
           const uint32_t stage = smem_base + s * C::kStageBytes;
-          mbar_expect_tx(full_raw(s), C::kRawBytes);
+          mbar_expect_tx(full_raw(s), C::kABytes + (pc.half ? C::kBBytes / 2 : C::kBBytes));
           const int k0 = (int)(kb * BK);
           if (!p.a_mn_major) {
             for (int h = 0; h < MT; ++h)                               // boxes {BK k, 128 m}
@@ -283,9 +293,10 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
           const uint32_t bdst = stage + C::kABytes;
           if (!p.b_mn_major) {
-            tma_load_2d(bdst, &map_b, full_raw(s), k0, n0);            // box {BK k, BN n}
+            for (int c = 0; c < bn_now / C::kBBoxRows; ++c)            // boxes {BK k, 128 n}
+              tma_load_2d(bdst + c * (C::kBBoxRows * BK * 4), &map_b, full_raw(s), k0, n0 + C::kBBoxRows * c);
           } else {
-            for (int c = 0; c < BN / 32; ++c)                          // boxes {32 n, BK k}
+            for (int c = 0; c < bn_now / 32; ++c)                      // boxes {32 n, BK k}
               tma_load_2d(bdst + c * C::kBoxBytes, &map_b, full_raw(s), n0 + 32 * c, k0);
           }
         }
@@ -294,7 +305,8 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc_whole = make_idesc(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc_half = make_idesc(BM, BN / 2, p.a_mn_major, p.b_mn_major);
       // K-major: rows of BK floats (128 or 64 bytes, swizzled over that span:
       // layout 2 or 4), 8-row groups 8*BK*4 bytes apart (SBO); a k step of 8 floats
       // is +32 B inside the swizzle span.
@@ -319,6 +331,7 @@ fmatmul_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         ok = mbar_wait(acc_empty(as), (use & 1u) ^ 1u, abort_flag, p.status, 106, p.wait_ns);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t idesc = pc.half ? idesc_half : idesc_whole;   // a column half: 128-column MMAs
         const uint32_t kb_first = pc.kb0;
         for (uint32_t kb = kb_first, kb_end = pc.kb1; kb < kb_end; ++kb, ++it) {
           const int s = it % S;
@@ -620,6 +633,14 @@ static bool wide_store_enabled() {
   return on;
 }
 
+static bool halves_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("POLAR_B200_TC_TAIL_HALVES");
+    return !(e && atoi(e) == 0);
+  }();
+  return on;
+}
+
 template <int BN, int BK, int MT = 1>
 static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* left,
                       const float* right, float* out, int passes, int write_hi, float* ws, uint32_t splits,
@@ -644,7 +665,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
           : make_map(&map_a, left, k, m, BK, BM, false, BK, left_pitch);
   if (rc) return rc;
   // right: stored [n,k] when transposed (K-major: inner k, box {BK, BN}) or [k,n] (MN-major)
-  rc = tr ? make_map(&map_b, right, k, n, BK, BN, false, BK) : make_map(&map_b, right, n, k, 32, BK, true, BK);
+  rc = tr ? make_map(&map_b, right, k, n, BK, C::kBBoxRows, false, BK) : make_map(&map_b, right, n, k, 32, BK, true, BK);
   if (rc) return rc;
   Params p;
   p.m = m; p.n = n; p.k = k; p.out = out;
@@ -663,6 +684,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   p.share = 0;
   p.slots = nullptr;
   p.teams = 0;
+  p.half_from = kNoHalves;
   const StreamPlan plan = (splits == 0 && ws) ? stream_plan(tm, tn, num_kb, BN, MT, (uint64_t)sm_count()) : StreamPlan{0, 0, 0, 0};
   if (plan.teams) {
     // stream mode: equal shares of all slabs, partial tiles through slots, then one summing pass
@@ -687,6 +709,7 @@ static int launch_cfg(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const 
   uint64_t units = tm * tn * splits;
   if (units > 0x7fffffffull) return fail(POLAR_B200_ERR_UNSUPPORTED, "too many tiles");
   unsigned grid = (unsigned)(units < (uint64_t)sm_count() ? units : (uint64_t)sm_count());   // one CTA per SM
+  if (splits == 1 && BN == 256 && halves_enabled()) p.half_from = halves_from(units, grid);
   fmatmul_tc_kernel<BN, BK, MT><<<grid, kThreads, C::kSmemBytes, stream>>>(map_a, map_b, p);
   rc = check_launch("fmatmul_tc");
   if (rc || splits == 1) return rc;
@@ -722,6 +745,11 @@ int launch_tc(int tl, int tr, uint64_t m, uint64_t n, uint64_t k, const float* l
   if (bk == 32)
     return tc::launch_cfg<256, 32>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
   return tc::launch_cfg<256, 16>(tl, tr, m, n, k, left, right, out, passes, write_hi, ws, splits, epilogue, stream, left_pitch, swap_ab);
+}
+
+// Whether a whole-tile launch of `tiles` 256-column tiles on `grid` CTAs cuts its last wave into column halves.
+bool tc_tail_in_halves(uint64_t tiles, uint64_t grid) {
+  return tc::halves_enabled() && tc::halves_from(tiles, grid) != tc::kNoHalves;
 }
 
 // Splits the default configuration (128 x 256 tiles, 16-float slabs) would use.

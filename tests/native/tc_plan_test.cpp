@@ -76,6 +76,32 @@ static void check_cover(uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, uin
   }
 }
 
+// Whole-tile mode with the tail wave cut into column halves: every tile before `from` once and
+// whole, every tile from `from` on as its two halves, each once, on different CTAs; no CTA gets
+// more than ceil(whole tiles / grid) whole tiles plus one half.
+static void check_halves(uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, uint32_t grid) {
+  const uint32_t tiles = tiles_m * tiles_n;
+  const uint32_t from = halves_from(tiles, grid);
+  if (from == kNoHalves) return;
+  CHECK(from % grid == 0 && from < tiles && 2 * (tiles - from) <= grid, "halves_from(%u, %u) = %u", tiles, grid, from);
+  std::vector<int> whole(tiles, 0), left(tiles, 0), right(tiles, 0);
+  for (uint32_t cta = 0; cta < grid; ++cta) {
+    PieceWalk walk(tiles_m, tiles_n, 1, 0, 0, num_kb, cta, grid, from);
+    Piece pc;
+    uint32_t n_whole = 0, n_half = 0;
+    while (walk.next(pc)) {
+      CHECK(pc.tile < tiles && pc.kb0 == 0 && pc.kb1 == num_kb && pc.slot == kNoSlot, "halves: piece of tile %u", pc.tile);
+      if (pc.tile >= tiles) continue;
+      if (pc.half == 0) { ++whole[pc.tile]; ++n_whole; CHECK(pc.tile < from, "halves: tile %u whole in the tail", pc.tile); }
+      else { ++(pc.half == 1 ? left : right)[pc.tile]; ++n_half; CHECK(pc.tile >= from, "halves: tile %u halved too early", pc.tile); }
+    }
+    CHECK(n_whole == from / grid && n_half <= 1, "halves: cta %u got %u whole tiles and %u halves", cta, n_whole, n_half);
+  }
+  for (uint32_t t = 0; t < tiles; ++t)
+    CHECK(t < from ? (whole[t] == 1 && !left[t] && !right[t]) : (!whole[t] && left[t] == 1 && right[t] == 1),
+          "halves: tile %u covered %d/%d/%d", t, whole[t], left[t], right[t]);
+}
+
 int main() {
   const uint64_t sms = 148;
   int cases = 0;
@@ -111,6 +137,17 @@ int main() {
           check_cover(tiles_m, tiles_n, num_kb, splits, 0, 0, grid, 0, "cuts");
           ++cases;
         }
+  // the tail wave in column halves: the first layer of the MLP at an eighth of the batch (32 x 16
+  // tiles of 256 x 256: three waves and 68 tiles), and a sweep
+  CHECK(halves_from(512, 148) == 444, "512 tiles on 148 CTAs: %u", halves_from(512, 148));
+  CHECK(halves_from(1024, 148) == kNoHalves && halves_from(4096, 148) == kNoHalves && halves_from(100, 148) == kNoHalves &&
+        halves_from(296, 148) == kNoHalves, "tails above half a wave, less than a wave, whole waves: no halves");
+  for (uint32_t tiles_m : {1u, 3u, 16u, 32u})
+    for (uint32_t tiles_n : {1u, 5u, 16u, 50u}) {
+      check_halves(tiles_m, tiles_n, 49, (uint32_t)sms);
+      check_halves(tiles_m, tiles_n, 49, 7);
+      ++cases;
+    }
   std::printf("%d cases, %d failures\n", cases, failures);
   return failures ? 1 : 0;
 }

@@ -66,6 +66,7 @@ SHAPES = [
     (2304, 2048, 96),                                       # 144 or 288 tiles: several tiles per persistent CTA
     (4224, 1280, 64),
     (1024, 1024, 2048), (784, 512, 4096),                   # few tiles, long k: the default path cuts k into work units
+    (1280, 4096, 64), (2560, 4000, 48),                     # 160 tiles on 148 SMs: the 12 tiles of the last wave run as column halves
 ]
 
 
