@@ -942,7 +942,7 @@ def main():
     ap.add_argument("--builtins", default="extended", choices=["extended", "reference"],
                     help="mlp: 'extended' runs the fused launches (every output bit-identical to the chain), "
                          "'reference' one launch per reference builtin")
-    ap.add_argument("--collective", default="peer", choices=["peer", "peer-ipc", "nccl"],
+    ap.add_argument("--collective", default="peer", choices=["peer", "peer-ipc", "peer-multicast", "nccl"],
                     help="mlp at N>1 with extended builtins: gradient sum + update as one peer-memory kernel, "
                          "or NCCL all-reduces followed by fadd")
     ap.add_argument("--overlap-exchange", action="store_true",

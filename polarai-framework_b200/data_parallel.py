@@ -99,9 +99,9 @@ class DataParallelExecutor:
     make_program(rows) builds the builtin program for `rows` rows (program.mlp_program,
     program.logreg_program); `sharded` names the inputs whose first dimension is the batch.
     builtins = "extended" applies program.fuse_program (outputs bit-identical to the chain);
-    collective = "peer" asks for the single-kernel exchange over NVLink peer memory - with the sum
-    done inside the switch where symmetric memory has a multicast address, "peer-ipc" for plain peer
-    loads and stores only (the form to use where a rank may leave in mid-run); with
+    collective = "peer" asks for the single-kernel exchange over NVLink peer memory ("peer-ipc": plain
+    peer loads and stores only, the form to use where a rank may leave in mid-run; "peer-multicast":
+    the sum done inside the switch where symmetric memory has a multicast address, else plain); with
     overlap=True the last weight gradient is computed in two blocks of rows and the first block's
     exchange runs on a second stream while the second block is computed
     (program.overlap_gradient_exchange).  Off by default: on B200 the two-block matmul costs
@@ -126,7 +126,7 @@ class DataParallelExecutor:
         self.collective = "none (one rank)"
         if world > 1:
             self.collective = "nccl all-reduce, then fadd updates"
-            if fused and collective in ("peer", "peer-ipc"):
+            if fused and collective in ("peer", "peer-ipc", "peer-multicast"):
                 xprog = fuse_gradient_exchange(program)
                 if overlap:
                     xprog = overlap_gradient_exchange(xprog)
@@ -134,8 +134,15 @@ class DataParallelExecutor:
                 peers = None
                 if xprog.exchanged():
                     try:
-                        peers = PeerGradients({g: xprog.tensors[g] for g in xprog.exchanged()}, rank, world,
-                                              self.device, transport="ipc" if collective == "peer-ipc" else "auto")
+                        shapes = {g: xprog.tensors[g] for g in xprog.exchanged()}
+                        want = {"peer-ipc": "ipc", "peer-multicast": "multicast"}.get(collective, "auto")
+                        try:
+                            peers = PeerGradients(shapes, rank, world, self.device, transport=want)
+                        except RuntimeError:
+                            if want != "multicast":
+                                raise
+                            # no multicast address here (every rank lands here together: the ranks vote)
+                            peers = PeerGradients(shapes, rank, world, self.device, transport="ipc")
                     except Exception as exc:               # noqa: BLE001 - any failure means "not available here"
                         why = f"{type(exc).__name__}: {exc}"
                 # every rank must take the same form: a vote

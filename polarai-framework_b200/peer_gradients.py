@@ -8,11 +8,12 @@ Two ways to get memory that every rank can reach:
  - "ipc": each rank allocates one peer buffer (polar_b200_peer_alloc), exports it as a CUDA IPC
    handle, gathers every rank's handle over the process group and maps the others; the kernel
    reads its slice from every peer and writes the sum to every peer with plain loads and stores.
-"auto" takes the first from four ranks up when every rank can (a vote over the process group),
-else the second: through the switch a rank's links carry its whole gradient vector once in each
-direction (its own copy out to the switch, the sums back), peer to peer (world - 1) / world of it
-twice - a third less at eight ranks, but more at two.  Measured at two ranks: 40 us in the switch,
-26 us peer to peer, both at about 500 GB/s per direction.
+"auto" is the second unless POLAR_B200_PEER_MULTICAST=1 is set, in which case it takes the first
+from eight ranks up when every rank can (a vote over the process group): through the switch a
+rank's links carry its whole gradient vector once in each direction (its own copy out to the
+switch, the sums back), peer to peer (world - 1) / world of it twice - a third less at eight
+ranks, but more at two.  Measured: two ranks 40 us in the switch against 26 us peer to peer, four
+ranks 36.2 against 35.4 us.
 Use "ipc" wherever a rank may leave while the others still run (failure tests): memory bound
 to a multicast object must not lose a participant in mid-run.
 
@@ -81,8 +82,10 @@ class PeerGradients:
             raise ValueError(f"rank {rank} of {world}: at most 16 ranks")
         if transport not in ("auto", "ipc", "multicast"):
             raise ValueError(f"transport {transport!r}: auto, ipc or multicast")
-        if os.environ.get("POLAR_B200_PEER_MULTICAST", "1") == "0" and transport == "auto":
-            transport = "ipc"
+        if transport == "auto":
+            # the in-switch form is opt-in: POLAR_B200_PEER_MULTICAST=1 lets "auto" take it from
+            # eight ranks up (measured equal to peer to peer at four ranks, slower at two)
+            transport = "auto" if os.environ.get("POLAR_B200_PEER_MULTICAST", "0") == "1" else "ipc"
         self.lib = lib()
         self.rank, self.world = rank, world
         self.device = torch.device(device)
@@ -95,7 +98,7 @@ class PeerGradients:
         self.own = None
         self._owns_buffer = False
         with torch.cuda.device(self.device):
-            if all_gather is None and ((transport == "auto" and world >= 4) or (transport == "multicast" and world > 1)):
+            if all_gather is None and ((transport == "auto" and world >= 8) or (transport == "multicast" and world > 1)):
                 self._try_multicast()
                 if self.multicast is None and transport == "multicast":
                     raise RuntimeError("no NVLink multicast for the gradient buffers: " + self.why_not_multicast)
