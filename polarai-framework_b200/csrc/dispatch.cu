@@ -147,12 +147,16 @@ TcChoice tc_choose(uint64_t m, uint64_t n, uint64_t k, bool may_swap) {
       const uint64_t tiles_m = (rows_dim + rows - 1) / rows, tiles_n = (cols_dim + 255) / 256, tiles = tiles_m * tiles_n;
       uint32_t splits = tc_default_splits(rows_dim, cols_dim, k, mt);
       if (swap && splits == 0) splits = 1;             // stream mode stores through slots: whole tiles instead
+      // with cuts of k the exchanged epilogue only writes partial products; measured better at
+      // 2048^3 (206-217 vs 193 TFLOP/s) and worse at 1024^3 (48 vs 58), where stream mode stays
+      if (swap && splits > 1 && rows_dim * cols_dim < (4ull << 20)) continue;
       double eff = 1.0;
-      if (splits == 1 && (double)tiles < 8 * sms) {    // whole waves of tiles
-        double waves = (double)((tiles + (uint64_t)sms - 1) / (uint64_t)sms);
-        // a tail of at most half a wave runs as column halves, which last about 0.6 of a tile
-        if (tc_tail_in_halves(tiles, (uint64_t)sms)) waves -= 0.4;
-        eff = (double)tiles / (waves * sms);
+      const uint64_t units = tiles * (splits ? splits : 1);
+      if (splits >= 1 && (double)units < 8 * sms) {    // whole waves of work units (stream mode balances itself)
+        double waves = (double)((units + (uint64_t)sms - 1) / (uint64_t)sms);
+        // a tail of at most half a wave of whole tiles runs as column halves, which last about 0.6 of a tile
+        if (splits == 1 && tc_tail_in_halves(tiles, (uint64_t)sms)) waves -= 0.4;
+        eff = (double)units / (waves * sms);
       }
       // measured against the 128-row tile: 0.67-0.85 of its cost from k = 16384 up, 0.83-0.88 at
       // k = 784 ... 8192 (256-bit or line-wide stores in the epilogue)
