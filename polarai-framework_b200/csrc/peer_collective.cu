@@ -76,6 +76,9 @@ struct Params {
   // per element (multimem.st): a rank's links carry one slice in and one slice out instead of
   // (world - 1) of each.
   unsigned char* mc;
+  // Threads of each CTA that take part in the slice phase (the first ones); the update phase
+  // uses all of them.
+  uint32_t slice_threads;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -169,7 +172,8 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
     // element per thread, everything in flight - the kernel spends one slice's transfer time
     // loading and then another one storing (46 us of a 16 us transfer at eight ranks).
     constexpr int W = WORLD ? WORLD : kMaxWorld;
-    const uint64_t stride = (uint64_t)gridDim.x * kThreadsNow;
+    const uint32_t st = p.slice_threads;
+    const uint64_t stride = (uint64_t)gridDim.x * st;
     auto load_all = [&](float4 (&v)[W], uint64_t i) {
 #pragma unroll
       for (int r = 0; r < W; ++r)
@@ -191,7 +195,8 @@ __global__ void __launch_bounds__(kThreads) allreduce_fadd_kernel(const Params p
         if (r < (int)world)
           st_peer(reinterpret_cast<float4*>(p.base[r] + POLAR_B200_PEER_CONTROL_BYTES) + i, s);
     };
-    uint64_t i = lo + (uint64_t)blockIdx.x * kThreadsNow + threadIdx.x;
+    // threads beyond the slice phase's share start past the end: they fall through to the barrier
+    uint64_t i = threadIdx.x < st ? lo + (uint64_t)blockIdx.x * st + threadIdx.x : hi;
     if (p.mc) {
       // In the switch: one load returns the sum over all ranks (in the switch's order, the same
       // bits for every rank since only this rank asks for this slice), one store delivers it to
@@ -376,19 +381,22 @@ static int allreduce_fadd_impl(void* const* buffers, void* multicast, uint32_t r
   p.scale_w = scale_w; p.scale_g = scale_g;
   // Every CTA waits on the other ranks, so all of them must be resident at once: at most one
   // per SM, launched cooperatively (the driver then starts the grid only as a whole, also
-  // when other kernels are holding SMs at that moment).  CTA size: about four elements of this
-  // rank's slice per thread (see the kernel), at most 512 threads on channel 0, the exchange
-  // that has the GPU to itself.  The other channels are meant to run BESIDE a tensor-core
+  // when other kernels are holding SMs at that moment).  512 threads per CTA on channel 0, the
+  // exchange that has the GPU to itself; of those, as many take part in the slice phase as give
+  // each about four elements of this rank's slice (see the kernel) - the update phase, plain
+  // HBM traffic, wants them all (with CTAs sized for the slice phase alone it took 16 instead
+  // of 8 us at eight ranks).  The other channels are meant to run BESIDE a tensor-core
   // matmul that already holds 576 threads and most of the registers of every SM: at most 128
   // threads per CTA fit next to it.
-  const unsigned max_threads = channel == 0 ? peer::kThreads : 128;
+  const unsigned threads = channel == 0 ? peer::kThreads : 128;
   uint64_t want = (p.n4 + 63) / 64;
   unsigned grid = (unsigned)(want < (uint64_t)sm_count() ? (want ? want : 1) : (uint64_t)sm_count());
   const uint64_t slice = (p.n4 + world - 1) / world;
   uint64_t per_cta = ((slice + 3) / 4 + grid - 1) / grid;
-  unsigned threads = (unsigned)(((per_cta + 31) / 32) * 32);
-  if (threads < 64) threads = 64;
-  if (threads > max_threads) threads = max_threads;
+  unsigned slice_threads = (unsigned)(((per_cta + 31) / 32) * 32);
+  if (slice_threads < 64) slice_threads = 64;
+  if (slice_threads > threads) slice_threads = threads;
+  p.slice_threads = slice_threads;
   cudaStream_t st = as_stream(stream);
   const void* fn = nullptr;
   switch (world) {
