@@ -12,8 +12,8 @@ Two ways to get memory that every rank can reach:
 from eight ranks up when every rank can (a vote over the process group): through the switch a
 rank's links carry its whole gradient vector once in each direction (its own copy out to the
 switch, the sums back), peer to peer (world - 1) / world of it twice - a third less at eight
-ranks, but more at two.  Measured: two ranks 40 us in the switch against 26 us peer to peer, four
-ranks 36.2 against 35.4 us.
+ranks, but more at two.  Measured (slice phase): two ranks 40 us in the switch against 26 us peer to
+peer, four ranks 36.2 against 35.4 us, eight ranks 35.3 against 40.2 us.
 Use "ipc" wherever a rank may leave while the others still run (failure tests): memory bound
 to a multicast object must not lose a participant in mid-run.
 
